@@ -1,0 +1,111 @@
+"""Shared by the tests: the two tiny configurations, model folders in temporary
+places, the plain implementation's logits, and replay of a schedule of steps."""
+from __future__ import annotations
+
+import functools
+import json
+import tempfile
+from pathlib import Path
+
+import numpy as np
+import torch
+
+import plain_qwen3 as plain
+
+# Two tiny configurations that differ in every size and option.
+TINY_A = dict(architectures=["Qwen3ForCausalLM"], model_type="qwen3", hidden_size=64, num_hidden_layers=2,
+              num_attention_heads=4, num_key_value_heads=2, head_dim=16, intermediate_size=128, vocab_size=256,
+              rope_theta=10000.0, rms_norm_eps=1e-6, tie_word_embeddings=True, max_position_embeddings=256)
+TINY_B = dict(architectures=["Qwen3ForCausalLM"], model_type="qwen3", hidden_size=96, num_hidden_layers=3,
+              num_attention_heads=8, num_key_value_heads=2, head_dim=32, intermediate_size=160, vocab_size=333,
+              rope_theta=1000000.0, rms_norm_eps=1e-5, tie_word_embeddings=False, max_position_embeddings=512)
+TINY = {"A": dict(config=TINY_A, seed=0, std=0.02, page_size=16),
+        "B": dict(config=TINY_B, seed=1, std=0.05, page_size=8)}
+
+# max |engine - plain| allowed, as a fraction of max |plain| over the compared rows
+TOL = {"float32": 2e-5, "bfloat16": 4e-2}
+
+_tmp_root = None
+
+
+def tmp_root() -> Path:
+    global _tmp_root
+    if _tmp_root is None:
+        _tmp_root = tempfile.TemporaryDirectory(prefix="vl_b200_tests_")
+    return Path(_tmp_root.name)
+
+
+@functools.lru_cache(maxsize=None)
+def model_dir(which: str) -> Path:
+    from vllm_lite_b200.weights import write_model_dir
+    spec = TINY[which]
+    d = tmp_root() / f"tiny_{which}"
+    write_model_dir(d, spec["config"], spec["seed"], std=spec["std"])
+    return d
+
+
+@functools.lru_cache(maxsize=None)
+def plain_model(which: str):
+    return plain.read_model_dir(model_dir(which))
+
+
+def tokens_for(which: str, length: int, seed: int):
+    rng = np.random.default_rng(1000 + seed)
+    return [int(t) for t in rng.integers(0, TINY[which]["config"]["vocab_size"], size=length)]
+
+
+_plain_cache = {}
+
+
+def plain_logits(which: str, tokens) -> torch.Tensor:
+    key = (which, tuple(tokens))
+    if key not in _plain_cache:
+        cfg, w = plain_model(which)
+        _plain_cache[key] = plain.forward(cfg, w, list(tokens))
+    return _plain_cache[key]
+
+
+def make_runner(which: str, dtype: str, num_pages: int, page_size=None, max_requests=8):
+    from vllm_lite_b200.engine import ModelRunner, load_model_dir
+    _, plan, weights = load_model_dir(model_dir(which), dtype, "cuda:0")
+    return ModelRunner(plan, weights, dtype=torch.bfloat16 if dtype == "bfloat16" else torch.float32,
+                       device="cuda:0", page_size=page_size or TINY[which]["page_size"], num_pages=num_pages,
+                       max_requests=max_requests)
+
+
+def run_schedule(runner, schedule):
+    """schedule: list of steps; a step is (entries, end) with entries = [(id, tokens, want)].
+    Returns {(id, position): logits row (CPU float32)}."""
+    from vllm_lite_b200.engine import StepEntry
+    fed, rows = {}, {}
+    for entries, end in schedule:
+        out = runner.step([StepEntry(i, t, w) for i, t, w in entries])
+        runner.check_device_errors()
+        out = out.float().cpu()
+        r = 0
+        for i, t, w in entries:
+            base = fed.get(i, 0)
+            for place in w:
+                rows[(i, base + place)] = out[r].clone()
+                r += 1
+            fed[i] = base + len(t)
+        assert r == out.shape[0]
+        for i in end:
+            runner.release(i)
+            fed.pop(i, None)
+        runner.cache.check_invariants()
+    return rows
+
+
+def assert_rows_match(rows, which, requests, dtype, what=""):
+    """rows: {(id, position): row}; requests: {id: tokens}."""
+    assert rows, "nothing was compared"
+    worst = 0.0
+    for (rid, pos), row in rows.items():
+        ref = plain_logits(which, requests[rid])[pos]
+        scale = float(ref.abs().max())
+        err = float((row - ref).abs().max()) / max(scale, 1e-12)
+        worst = max(worst, err)
+        assert err <= TOL[dtype], (f"{what} {which}/{dtype}: request {rid} position {pos}: "
+                                   f"max|diff|/max|ref| = {err:.3e} > {TOL[dtype]:.1e}")
+    return worst

@@ -1,0 +1,178 @@
+"""The engine against the plain implementation under every way of cutting the work:
+each request alone and whole; most of it in one step and the last 32 tokens one by
+one; portions of changing size down to two tokens; and up to four live requests
+mixed, portions of some beside decoded tokens of others, with so few pages that
+they are used again.  In float32 and in bfloat16, on both tiny configurations."""
+import json
+import os
+import subprocess
+import sys
+from pathlib import Path
+
+import numpy as np
+import pytest
+import torch
+
+import helpers as H
+
+pytestmark = pytest.mark.gpu
+ROOT = Path(__file__).resolve().parent.parent
+CASES = [(w, d) for w in ("A", "B") for d in ("float32", "bfloat16")]
+LENGTHS = {"A": [5, 17, 33, 70], "B": [1, 9, 40, 64, 100]}
+
+
+def pages_for(which, tokens):
+    ps = H.TINY[which]["page_size"]
+    return -(-tokens // ps)
+
+
+@pytest.mark.parametrize("which,dtype", CASES)
+def test_whole(which, dtype):
+    runner = H.make_runner(which, dtype, num_pages=pages_for(which, 128))
+    for n, length in enumerate(LENGTHS[which]):
+        toks = H.tokens_for(which, length, n)
+        rows = H.run_schedule(runner, [([("r", toks, list(range(length)))], ["r"])])
+        H.assert_rows_match(rows, which, {"r": toks}, dtype, "whole")
+    assert runner.cache.free_pages() == [pages_for(which, 128)]
+
+
+@pytest.mark.parametrize("which,dtype", CASES)
+def test_last_32_decoded(which, dtype):
+    length = 100
+    toks = H.tokens_for(which, length, 7)
+    runner = H.make_runner(which, dtype, num_pages=pages_for(which, 128))
+    head = length - 32
+    schedule = [([("r", toks[:head], [head - 1])], [])]
+    schedule += [([("r", [toks[p]], [0])], []) for p in range(head, length)]
+    rows = H.run_schedule(runner, schedule)
+    assert len(rows) == 33
+    H.assert_rows_match(rows, which, {"r": toks}, dtype, "decode")
+
+
+@pytest.mark.parametrize("which,dtype", CASES)
+def test_first_tokens(which, dtype):
+    """The very first positions of a sequence, fed one by one from an empty cache."""
+    toks = H.tokens_for(which, 6, 3)
+    runner = H.make_runner(which, dtype, num_pages=4)
+    rows = H.run_schedule(runner, [([("r", [t], [0])], []) for t in toks])
+    H.assert_rows_match(rows, which, {"r": toks}, dtype, "first tokens")
+
+
+@pytest.mark.parametrize("which,dtype", CASES)
+def test_changing_portions(which, dtype):
+    length = 120
+    toks = H.tokens_for(which, length, 11)
+    runner = H.make_runner(which, dtype, num_pages=pages_for(which, 128))
+    sizes = [7, 2, 13, 3, 2, 16, 5, 2, 31, 8, 2, 17, 2, 2, 3]
+    schedule, p, k = [], 0, 0
+    while p < length:
+        n = min(sizes[k % len(sizes)], length - p)
+        k += 1
+        schedule.append(([("r", toks[p:p + n], list(range(n)))], []))
+        p += n
+    rows = H.run_schedule(runner, schedule)
+    assert len(rows) == length
+    H.assert_rows_match(rows, which, {"r": toks}, dtype, "portions")
+
+
+def mixed_schedule(which):
+    """Six requests, at most four live, portions beside decoded tokens; a pool that forces reuse."""
+    lens = {"a": 50, "b": 37, "c": 64, "d": 21, "e": 45, "f": 30}
+    reqs = {k: H.tokens_for(which, n, 20 + i) for i, (k, n) in enumerate(lens.items())}
+    fed = {k: 0 for k in reqs}
+    def take(k, n, want="all"):
+        t = reqs[k][fed[k]:fed[k] + n]
+        fed[k] += len(t)
+        w = list(range(len(t))) if want == "all" else ([len(t) - 1] if want == "last" else [])
+        return (k, t, w)
+    S = []
+    S.append(([take("a", 20), take("b", 30)], []))                                  # two prompt portions
+    S.append(([take("a", 30, "last"), take("c", 9), take("b", 1)], []))            # a ends its prompt, c starts
+    S.append(([take("c", 2), take("d", 21), take("b", 1)], ["a"]))                 # four live; a's pages return
+    S.append(([take("c", 23, "none"), take("e", 13), take("b", 1)], ["d"]))        # e takes pages a held
+    S.append(([take("c", 1), take("e", 1), take("f", 2), take("b", 4)], ["b"]))    # decoded tokens beside portions
+    S.append(([take("c", 1), take("e", 7), take("f", 11)], []))
+    S.append(([take("c", 28), take("e", 24), take("f", 17)], ["c", "e", "f"]))
+    for k in lens:
+        assert fed[k] == lens[k], (k, fed[k])
+    return reqs, S
+
+
+@pytest.mark.parametrize("which,dtype", CASES)
+def test_mixed_with_page_reuse(which, dtype):
+    reqs, schedule = mixed_schedule(which)
+    # live tokens peak at 37 + 50 + 11 (a, b, c) etc.; give just enough pages that reuse is forced
+    ps = H.TINY[which]["page_size"]
+    live_peak, live = 0, {}
+    for entries, end in schedule:
+        for k, t, _ in entries:
+            live[k] = live.get(k, 0) + len(t)
+        live_peak = max(live_peak, sum(-(-n // ps) for n in live.values()))
+        for k in end:
+            live.pop(k)
+    total_pages = sum(-(-len(t) // ps) for t in reqs.values())
+    assert live_peak < total_pages
+    runner = H.make_runner(which, dtype, num_pages=live_peak)
+    rows = H.run_schedule(runner, schedule)
+    H.assert_rows_match(rows, which, reqs, dtype, "mixed")
+    assert runner.cache.free_pages() == [live_peak]
+
+
+@pytest.mark.parametrize("which", ["A", "B"])
+def test_cuts_agree_bitwise_in_float32(which):
+    """The float32 kernels add in an order that depends on positions alone, so a
+    position's logits are bit-for-bit the same however the tokens were cut."""
+    toks = H.tokens_for(which, 60, 5)
+    runner = H.make_runner(which, "float32", num_pages=pages_for(which, 192))
+    whole = H.run_schedule(runner, [([("w", toks, list(range(60)))], ["w"])])
+    other = H.tokens_for(which, 23, 6)
+    cut = H.run_schedule(runner, [
+        ([("o", other[:20], [])], []),
+        ([("x", toks[:17], list(range(17))), ("o", other[20:21], [0])], []),
+        ([("o", other[21:22], [0]), ("x", toks[17:19], [0, 1])], []),
+        ([("x", toks[19:60], list(range(41)))], ["x", "o"])])
+    for p in range(60):
+        assert torch.equal(whole[("w", p)], cut[("x", p)]), f"position {p} differs between cuts"
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_long_decoding(dtype):
+    which = "B"
+    length = 260
+    toks = H.tokens_for(which, length, 31)
+    runner = H.make_runner(which, dtype, num_pages=pages_for(which, 264))
+    schedule = [([("r", toks[:4], [3])], [])] + [([("r", [toks[p]], [0])], []) for p in range(4, length)]
+    rows = H.run_schedule(runner, schedule)
+    H.assert_rows_match(rows, which, {"r": toks}, dtype, "long decode")
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_trace_run_program(dtype, tmp_path):
+    """bin/trace_run as a user calls it: steps on stdin, <step>.f32 files out."""
+    which = "A"
+    toks = H.tokens_for(which, 40, 41)
+    other = H.tokens_for(which, 12, 42)
+    steps = [
+        {"step": 0, "entries": [{"id": "a", "tokens": toks[:25], "want": [0, 24]}], "end": []},
+        {"step": 1, "entries": [{"id": "b", "tokens": other, "want": []}], "end": []},
+        {"step": 2, "entries": [{"id": "a", "tokens": toks[25:27], "want": [0, 1]},
+                                {"id": "b", "tokens": [3], "want": []}], "end": ["b"]},
+        {"step": 3, "entries": [{"id": "a", "tokens": toks[27:], "want": [12]}], "end": ["a"]},
+    ]
+    env = dict(os.environ)
+    proc = subprocess.run([sys.executable, str(ROOT / "bin" / "trace_run"), "--model", str(H.model_dir(which)),
+                           "--dtype", dtype, "--out", str(tmp_path), "--max-tokens", "128"],
+                          input="\n".join(json.dumps(s) for s in steps) + "\n", capture_output=True, text=True,
+                          env=env, timeout=900)
+    assert proc.returncode == 0, proc.stderr[-2000:]
+    assert [l for l in proc.stdout.splitlines() if l.startswith("done")] == [f"done {i}" for i in range(4)]
+    assert not (tmp_path / "1.f32").exists()
+    V = H.TINY[which]["config"]["vocab_size"]
+    ref = H.plain_logits(which, toks)
+    got = {0: [0, 24], 2: [25, 26], 3: [39]}
+    for step, positions in got.items():
+        arr = np.fromfile(tmp_path / f"{step}.f32", dtype="<f4").reshape(-1, V)
+        assert arr.shape[0] == len(positions)
+        for row, pos in zip(arr, positions):
+            err = float(np.abs(row - ref[pos].numpy()).max()) / float(ref[pos].abs().max())
+            assert err <= H.TOL[dtype], (step, pos, err)

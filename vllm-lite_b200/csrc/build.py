@@ -1,0 +1,120 @@
+"""Compiles the engine's CUDA sources for sm_100a with nvcc and loads them.
+
+Each `.cu` file becomes one shared library, built the first time an operation
+from it is used and kept beside the sources under `csrc/_build/` (or, when that
+folder cannot be written, under the system's temporary folder).  The file name
+carries a hash of the source, of the shared header and of the flags, so an
+edited source is rebuilt and a stale library is never loaded.  There is no
+fallback: when a library can be neither found nor built, loading raises.
+"""
+from __future__ import annotations
+
+import ctypes
+import hashlib
+import os
+import shutil
+import subprocess
+import sys
+import tempfile
+import threading
+import time
+from pathlib import Path
+
+CSRC = Path(__file__).resolve().parent
+ARCH_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a"]
+NVCC_FLAGS = ARCH_FLAGS + ["-O3", "-lineinfo", "-std=c++17", "--shared", "-Xcompiler", "-fPIC"]
+SOURCES = ("embed_norm", "rope_cache", "attention", "activation", "gemm_f32", "gemm_bf16", "sampling")
+EXTRA_LIBS = {"gemm_bf16": ["-lcuda"]}
+
+_loaded = {}
+_lock = threading.Lock()
+
+
+class BuildError(RuntimeError):
+    pass
+
+
+def _say(msg):
+    print(f"[vllm-lite_b200] {msg}", file=sys.stderr, flush=True)
+
+
+def find_nvcc() -> str:
+    for cand in (os.environ.get("NVCC"),
+                 os.path.join(os.environ.get("CUDA_HOME", ""), "bin", "nvcc") if os.environ.get("CUDA_HOME") else None,
+                 shutil.which("nvcc"), "/usr/local/cuda/bin/nvcc"):
+        if cand and os.path.isfile(cand) and os.access(cand, os.X_OK):
+            return cand
+    raise BuildError("nvcc not found (looked at $NVCC, $CUDA_HOME/bin, PATH, /usr/local/cuda/bin); "
+                     "the engine has no path without its CUDA libraries")
+
+
+def _digest(name: str) -> str:
+    h = hashlib.sha256()
+    h.update((CSRC / f"{name}.cu").read_bytes())
+    for header in sorted(CSRC.glob("*.cuh")):
+        h.update(header.read_bytes())
+    h.update(" ".join(NVCC_FLAGS + EXTRA_LIBS.get(name, [])).encode())
+    return h.hexdigest()[:12]
+
+
+def _build_dirs():
+    yield CSRC / "_build"
+    yield Path(tempfile.gettempdir()) / f"vllm_lite_b200_build_{os.getuid()}"
+
+
+def library_path(name: str) -> Path:
+    """Path of the up-to-date library of `name`, building it if it is absent."""
+    if not (CSRC / f"{name}.cu").is_file():
+        raise BuildError(f"no CUDA source {name}.cu under {CSRC}")
+    fname = f"{name}.{_digest(name)}.so"
+    for d in _build_dirs():
+        if (d / fname).is_file():
+            return d / fname
+    last = None
+    for d in _build_dirs():
+        try:
+            d.mkdir(parents=True, exist_ok=True)
+            if not os.access(d, os.W_OK):
+                continue
+            return _compile(name, d / fname)
+        except (OSError, BuildError) as e:   # try the next folder; report the last failure
+            last = e
+            if isinstance(e, BuildError) and "nvcc" in str(e) and "not found" in str(e):
+                break
+    raise BuildError(f"could not build {name}.cu: {last}")
+
+
+def _compile(name: str, out: Path) -> Path:
+    nvcc = find_nvcc()
+    tmp = out.with_suffix(f".tmp{os.getpid()}.so")
+    cmd = [nvcc] + NVCC_FLAGS + ["-I", str(CSRC), "-o", str(tmp), str(CSRC / f"{name}.cu")] + EXTRA_LIBS.get(name, [])
+    _say(f"compiling {name}.cu for sm_100a ...")
+    t0 = time.time()
+    proc = subprocess.Popen(cmd, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True,
+                            env={**os.environ, "TMPDIR": tempfile.gettempdir()})
+    while True:
+        try:
+            log, _ = proc.communicate(timeout=20)
+            break
+        except subprocess.TimeoutExpired:
+            _say(f"  still compiling {name}.cu ({time.time() - t0:.0f} s)")
+    if proc.returncode != 0:
+        tmp.unlink(missing_ok=True)
+        raise BuildError(f"nvcc failed on {name}.cu:\n{log}")
+    os.replace(tmp, out)
+    _say(f"built {out.name} in {time.time() - t0:.1f} s")
+    return out
+
+
+def load(name: str) -> ctypes.CDLL:
+    with _lock:
+        lib = _loaded.get(name)
+        if lib is None:
+            lib = ctypes.CDLL(str(library_path(name)))
+            _loaded[name] = lib
+        return lib
+
+
+def build_all(names=SOURCES) -> dict:
+    """Build every library (cross-compiles without a GPU).  Returns name -> path."""
+    return {n: library_path(n) for n in names if (CSRC / f"{n}.cu").is_file()}

@@ -1,0 +1,62 @@
+// Shared helpers of the engine's CUDA kernels (sm_100a).
+//
+// Every exported entry point is `extern "C" int vl_<name>(..., void* stream)`.
+// It returns 0, a positive cudaError_t of the launch, or one of the negative
+// codes below when it refuses its arguments; the Python side turns any
+// non-zero value into an exception.  Kernels never trap: a bad token id or
+// cache slot sets a bit in the caller's error word and the access is skipped.
+#pragma once
+#include <cuda_runtime.h>
+#include <cuda_bf16.h>
+#include <stdint.h>
+
+#define VL_OK 0
+#define VL_ERR_UNSUPPORTED (-2)   // a size the kernel does not take
+#define VL_ERR_ARGUMENT (-3)      // inconsistent arguments
+
+// bits of the device-side error word
+#define VL_DEV_BAD_TOKEN 1u
+#define VL_DEV_BAD_SLOT 2u
+#define VL_DEV_BAD_PAGE 4u
+#define VL_DEV_WAIT_EXPIRED 8u
+
+// dtype codes shared with csrc/ops.py
+#define VL_F32 0
+#define VL_BF16 1
+
+typedef __nv_bfloat16 bf16;
+
+__device__ __forceinline__ float to_f32(float v) { return v; }
+__device__ __forceinline__ float to_f32(bf16 v) { return __bfloat162float(v); }
+template <typename T> __device__ __forceinline__ T from_f32(float v);
+template <> __device__ __forceinline__ float from_f32<float>(float v) { return v; }
+template <> __device__ __forceinline__ bf16 from_f32<bf16>(float v) { return __float2bfloat16_rn(v); }
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    return v;
+}
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+    return v;
+}
+
+// Sum over a block of NT threads (NT a multiple of 32, at most 1024).  The
+// order of additions depends on NT alone, so a row's result does not depend on
+// what else is in the launch.  `scratch` holds 32 floats.
+template <int NT>
+__device__ __forceinline__ float block_sum(float v, float* scratch) {
+    v = warp_sum(v);
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    __syncthreads();
+    if (lane == 0) scratch[warp] = v;
+    __syncthreads();
+    float t = 0.f;
+#pragma unroll
+    for (int w = 0; w < NT / 32; ++w) t += scratch[w];
+    return t;
+}
+
+static inline int vl_launch_status() { return (int)cudaGetLastError(); }

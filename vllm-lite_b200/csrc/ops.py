@@ -1,0 +1,243 @@
+"""Python face of the CUDA kernels: one function per exported entry point.
+
+Tensors are torch CUDA tensors used as plain device buffers; the kernels run on
+torch's current stream.  Arguments are checked here (dtype, contiguity, sizes)
+so that a kernel never sees a pointer that does not match its shape arguments.
+A non-zero return code of an entry point raises `KernelError`.
+"""
+from __future__ import annotations
+
+import ctypes
+from ctypes import c_float, c_int, c_longlong, c_void_p
+
+import torch
+
+from . import build
+
+F32, BF16 = 0, 1
+_DTYPE_CODE = {torch.float32: F32, torch.bfloat16: BF16}
+_ERRORS = {-2: "a size this kernel does not take", -3: "inconsistent arguments"}
+
+
+class KernelError(RuntimeError):
+    pass
+
+
+def dtype_code(dtype) -> int:
+    try:
+        return _DTYPE_CODE[dtype]
+    except KeyError:
+        raise KernelError(f"kernels take float32 and bfloat16, got {dtype}") from None
+
+
+_SIGNATURES = {
+    ("embed_norm", "vl_embed"): [c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_void_p, c_void_p],
+    ("embed_norm", "vl_add_rmsnorm"): [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_float, c_void_p],
+    ("embed_norm", "vl_residual_add"): [c_void_p, c_void_p, c_int, c_longlong, c_void_p],
+    ("embed_norm", "vl_cast"): [c_void_p, c_int, c_void_p, c_int, c_longlong, c_void_p],
+    ("rope_cache", "vl_qk_norm_rope_write"): [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_float, c_void_p, c_int,
+                                              c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_longlong, c_int,
+                                              c_void_p, c_void_p],
+    ("attention", "vl_paged_attention"): [c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int,
+                                          c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int,
+                                          c_float, c_int, c_void_p, c_void_p],
+    ("activation", "vl_silu_mul"): [c_void_p, c_void_p, c_int, c_int, c_int, c_void_p],
+    ("gemm_f32", "vl_gemm_f32_nt"): [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p],
+    ("sampling", "vl_apply_penalties"): [c_void_p, c_longlong, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p,
+                                         c_void_p, c_void_p, c_void_p, c_void_p],
+    ("sampling", "vl_sample"): [c_void_p, c_longlong, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p,
+                                c_void_p, c_void_p, c_void_p],
+}
+_functions = {}
+
+
+def _fn(lib: str, name: str):
+    f = _functions.get((lib, name))
+    if f is None:
+        f = getattr(build.load(lib), name)
+        f.argtypes = _SIGNATURES[(lib, name)]
+        f.restype = c_int
+        _functions[(lib, name)] = f
+    return f
+
+
+def _ptr(t):
+    return None if t is None else t.data_ptr()
+
+
+def _stream():
+    return torch.cuda.current_stream().cuda_stream
+
+
+def _check(code: int, name: str):
+    if code == 0:
+        return
+    if code < 0:
+        raise KernelError(f"{name} refused its arguments: {_ERRORS.get(code, code)}")
+    raise KernelError(f"{name}: CUDA error {code} at launch")
+
+
+def _need(t, dtype, name, ndim=None):
+    if not t.is_cuda:
+        raise KernelError(f"{name} must be a CUDA tensor; the engine has no CPU path")
+    if dtype is not None and t.dtype != dtype:
+        raise KernelError(f"{name} must be {dtype}, got {t.dtype}")
+    if not t.is_contiguous():
+        raise KernelError(f"{name} must be contiguous")
+    if ndim is not None and t.dim() != ndim:
+        raise KernelError(f"{name} must have {ndim} dimensions, got {tuple(t.shape)}")
+
+
+# ---------------------------------------------------------------- embed / norm
+def embed(ids, table, out, err):
+    """out[t, :] = table[ids[t], :] as float32.  ids int32 [T]; out float32 [T, H]."""
+    _need(ids, torch.int32, "ids", 1); _need(table, None, "table", 2); _need(out, torch.float32, "out", 2)
+    T, (V, H) = ids.shape[0], table.shape
+    if out.shape != (T, H):
+        raise KernelError(f"out must be [{T}, {H}], got {tuple(out.shape)}")
+    _check(_fn("embed_norm", "vl_embed")(_ptr(ids), _ptr(table), dtype_code(table.dtype), _ptr(out), T, H, V,
+                                         _ptr(err), _stream()), "vl_embed")
+    return out
+
+
+def add_rmsnorm(x, delta, weight, eps, out, rows=None):
+    """x float32 [T, H] (+= delta when given and rows is None); out[r] = rmsnorm(x[row r] (+ delta)) * weight."""
+    _need(x, torch.float32, "x", 2); _need(weight, torch.float32, "weight", 1); _need(out, None, "out", 2)
+    H = x.shape[1]
+    R = x.shape[0] if rows is None else rows.shape[0]
+    if weight.shape[0] != H or out.shape != (R, H):
+        raise KernelError(f"norm shapes disagree: x {tuple(x.shape)}, weight {tuple(weight.shape)}, out {tuple(out.shape)}")
+    if delta is not None:
+        _need(delta, out.dtype, "delta", 2)
+        if delta.shape != x.shape:
+            raise KernelError(f"delta {tuple(delta.shape)} must match x {tuple(x.shape)}")
+    if rows is not None:
+        _need(rows, torch.int32, "rows", 1)
+    _check(_fn("embed_norm", "vl_add_rmsnorm")(_ptr(x), _ptr(delta), _ptr(rows), _ptr(weight), _ptr(out),
+                                               dtype_code(out.dtype), R, H, float(eps), _stream()), "vl_add_rmsnorm")
+    return out
+
+
+def residual_add(x, delta):
+    _need(x, torch.float32, "x"); _need(delta, None, "delta")
+    if delta.shape != x.shape:
+        raise KernelError("residual_add: shapes differ")
+    _check(_fn("embed_norm", "vl_residual_add")(_ptr(x), _ptr(delta), dtype_code(delta.dtype), x.numel(), _stream()),
+           "vl_residual_add")
+    return x
+
+
+def cast(src, out):
+    _need(src, None, "src"); _need(out, None, "out")
+    if src.numel() != out.numel():
+        raise KernelError("cast: sizes differ")
+    _check(_fn("embed_norm", "vl_cast")(_ptr(src), dtype_code(src.dtype), _ptr(out), dtype_code(out.dtype),
+                                        src.numel(), _stream()), "vl_cast")
+    return out
+
+
+# ---------------------------------------------------------------- rope + cache
+def qk_norm_rope_write(qkv, positions, slots, q_weight, k_weight, eps, inv_freq, rotary_dim,
+                       k_cache, v_cache, num_heads, num_kv_heads, head_dim, err):
+    """In place on the q part of qkv [T, (nq + 2 nkv) hd]; k and v go to the cache
+    [pages, nkv, page_size, hd] at `slots` (int32 [T]; negative: no write)."""
+    _need(qkv, None, "qkv", 2); _need(positions, torch.int32, "positions", 1)
+    T = qkv.shape[0]
+    if qkv.shape[1] != (num_heads + 2 * num_kv_heads) * head_dim or positions.shape[0] != T:
+        raise KernelError(f"qkv {tuple(qkv.shape)} does not match heads {num_heads}+2*{num_kv_heads} x {head_dim}")
+    page_size, num_slots = 1, 0
+    if slots is not None:
+        _need(slots, torch.int32, "slots", 1)
+        _need(k_cache, qkv.dtype, "k_cache", 4); _need(v_cache, qkv.dtype, "v_cache", 4)
+        if k_cache.shape != v_cache.shape or k_cache.shape[1] != num_kv_heads or k_cache.shape[3] != head_dim:
+            raise KernelError(f"cache {tuple(k_cache.shape)} does not match kv heads {num_kv_heads} x {head_dim}")
+        page_size = k_cache.shape[2]
+        num_slots = k_cache.shape[0] * page_size
+    for w, n in ((q_weight, "q_weight"), (k_weight, "k_weight")):
+        if w is not None:
+            _need(w, torch.float32, n, 1)
+            if w.shape[0] != head_dim:
+                raise KernelError(f"{n} must have head_dim={head_dim} entries")
+    if inv_freq is not None:
+        _need(inv_freq, torch.float32, "inv_freq", 1)
+        if inv_freq.shape[0] * 2 != rotary_dim:
+            raise KernelError("inv_freq must have rotary_dim / 2 entries")
+    _check(_fn("rope_cache", "vl_qk_norm_rope_write")(
+        _ptr(qkv), dtype_code(qkv.dtype), _ptr(positions), _ptr(slots), _ptr(q_weight), _ptr(k_weight), float(eps),
+        _ptr(inv_freq), int(rotary_dim if inv_freq is not None else 0), _ptr(k_cache) if slots is not None else None,
+        _ptr(v_cache) if slots is not None else None, T, num_heads, num_kv_heads, head_dim, page_size, num_slots,
+        qkv.shape[1], _ptr(err), _stream()), "vl_qk_norm_rope_write")
+    return qkv
+
+
+# ---------------------------------------------------------------- attention
+def paged_attention(qkv, out, k_cache, v_cache, block_table, req_index, positions,
+                    num_heads, num_kv_heads, head_dim, scale, window, err):
+    """out [T, nq*hd] = attention of the q part of qkv over the pages of each token's request."""
+    _need(qkv, None, "qkv", 2); _need(out, qkv.dtype, "out", 2)
+    _need(k_cache, qkv.dtype, "k_cache", 4); _need(v_cache, qkv.dtype, "v_cache", 4)
+    _need(block_table, torch.int32, "block_table", 2)
+    _need(req_index, torch.int32, "req_index", 1); _need(positions, torch.int32, "positions", 1)
+    T = qkv.shape[0]
+    if out.shape != (T, num_heads * head_dim) or req_index.shape[0] != T or positions.shape[0] != T:
+        raise KernelError("paged_attention: token counts or widths disagree")
+    if qkv.shape[1] < num_heads * head_dim:
+        raise KernelError("paged_attention: qkv rows are narrower than the query heads")
+    if k_cache.shape != v_cache.shape or k_cache.shape[1] != num_kv_heads or k_cache.shape[3] != head_dim:
+        raise KernelError(f"cache {tuple(k_cache.shape)} does not match kv heads {num_kv_heads} x {head_dim}")
+    _check(_fn("attention", "vl_paged_attention")(
+        _ptr(qkv), qkv.shape[1], _ptr(out), dtype_code(qkv.dtype), _ptr(k_cache), _ptr(v_cache),
+        _ptr(block_table), block_table.shape[1], _ptr(req_index), _ptr(positions),
+        T, num_heads, num_kv_heads, head_dim, k_cache.shape[2], k_cache.shape[0],
+        float(scale), int(window or 0), _ptr(err), _stream()), "vl_paged_attention")
+    return out
+
+
+# ---------------------------------------------------------------- feed-forward
+def silu_mul(gate_up, out):
+    _need(gate_up, None, "gate_up", 2); _need(out, gate_up.dtype, "out", 2)
+    T, I2 = gate_up.shape
+    if I2 % 2 or out.shape != (T, I2 // 2):
+        raise KernelError("silu_mul: out must be [T, I] for gate_up [T, 2I]")
+    _check(_fn("activation", "vl_silu_mul")(_ptr(gate_up), _ptr(out), dtype_code(out.dtype), T, I2 // 2, _stream()),
+           "vl_silu_mul")
+    return out
+
+
+# ---------------------------------------------------------------- matrix products
+def gemm_f32(a, w, out):
+    """out[M, N] = a[M, K] @ w[N, K]^T in true float32 (FFMA, fixed order over K)."""
+    _need(a, torch.float32, "a", 2); _need(w, torch.float32, "w", 2); _need(out, torch.float32, "out", 2)
+    M, K = a.shape
+    N = w.shape[0]
+    if w.shape[1] != K or out.shape != (M, N):
+        raise KernelError(f"gemm_f32: shapes disagree a{tuple(a.shape)} w{tuple(w.shape)} out{tuple(out.shape)}")
+    _check(_fn("gemm_f32", "vl_gemm_f32_nt")(_ptr(a), _ptr(w), _ptr(out), M, N, K, K, K, N, _stream()), "vl_gemm_f32_nt")
+    return out
+
+
+# ---------------------------------------------------------------- sampling
+def apply_penalties(logits, seen_off=None, seen_ids=None, repeat=None, presence=None,
+                    bias_off=None, bias_ids=None, bias_vals=None):
+    _need(logits, torch.float32, "logits", 2)
+    R, V = logits.shape
+    _check(_fn("sampling", "vl_apply_penalties")(
+        _ptr(logits), logits.stride(0), R, V, _ptr(seen_off), _ptr(seen_ids), _ptr(repeat), _ptr(presence),
+        _ptr(bias_off), _ptr(bias_ids), _ptr(bias_vals), _stream()), "vl_apply_penalties")
+    return logits
+
+
+def sample(logits, temperature, top_k, top_p, uniform, out_token, out_logprob=None):
+    _need(logits, torch.float32, "logits", 2); _need(out_token, torch.int32, "out_token", 1)
+    R, V = logits.shape
+    for t, dt, n in ((temperature, torch.float32, "temperature"), (top_k, torch.int32, "top_k"),
+                     (top_p, torch.float32, "top_p"), (uniform, torch.float32, "uniform"),
+                     (out_logprob, torch.float32, "out_logprob")):
+        if t is not None:
+            _need(t, dt, n, 1)
+            if t.shape[0] < R:
+                raise KernelError(f"{n} has fewer entries than rows")
+    _check(_fn("sampling", "vl_sample")(
+        _ptr(logits), logits.stride(0), R, V, _ptr(temperature), _ptr(top_k), _ptr(top_p), _ptr(uniform),
+        _ptr(out_token), _ptr(out_logprob), _stream()), "vl_sample")
+    return out_token

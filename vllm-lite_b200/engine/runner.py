@@ -1,0 +1,225 @@
+"""The step function: one batch of (request, its next tokens) through the model.
+
+`ModelRunner.step(entries)` takes any mix of prompt portions and single decoded
+tokens, cut anywhere.  It takes the pages the new tokens need, lays the batch out
+flat (tokens, positions, block tables, cache slots), uploads that in one copy,
+runs only the given tokens from the cache that earlier steps left, and returns
+float32 logits at the wanted places.  The reference's seam has the same inputs
+(crates/traits/src/model.rs:67-75: tokens, positions, block ids, computed counts)
+but runs the entries one by one and returns logits for every position
+(crates/model/src/causal_lm/model/mod.rs:143-164); here the entries are one batch.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass
+from typing import List, Optional, Sequence
+
+import numpy as np
+import torch
+
+from ..cache.manager import CacheLayout, CacheManager, OutOfPages
+from ..cache.storage import CacheStorage
+from ..parts.base import BuildContext, Entry, GroupView, StepBatch, Workspace
+from ..parts.model import CausalLM, cache_needs
+
+
+class StepError(RuntimeError):
+    pass
+
+
+@dataclass
+class StepEntry:
+    request_id: object
+    tokens: Sequence[int]
+    want: Sequence[int] = ()        # places among `tokens` whose logits are asked for
+
+
+_DEVICE_ERRORS = {1: "a token id outside the vocabulary", 2: "a cache slot outside the pool",
+                  4: "a block table entry that names no page", 8: "a wait inside a kernel ran out"}
+
+
+def _align4(n: int) -> int:
+    return (n + 3) & ~3
+
+
+class ModelRunner:
+    def __init__(self, plan, weights: dict, *, dtype=torch.bfloat16, device="cuda:0", page_size: int = 16,
+                 num_pages=1024, max_requests: int = 256):
+        self.device = torch.device(device)
+        if self.device.type != "cuda":
+            raise StepError("the engine runs on a CUDA device only; there is no CPU path")
+        if dtype not in (torch.bfloat16, torch.float32):
+            raise StepError(f"dtype must be bfloat16 or float32, got {dtype}")
+        self.plan = plan
+        self.dtype = dtype
+        self.page_size = int(page_size)
+        torch.cuda.set_device(self.device)
+        self.model = CausalLM(plan, weights, BuildContext(self.device, dtype))
+        self.layout = CacheLayout.from_needs(cache_needs(plan), [c.cache_of for c in plan.order])
+        self.cache = CacheManager(self.layout, self.page_size, num_pages, max_requests)
+        self.storage = CacheStorage(self.layout, self.page_size, num_pages, max_requests, dtype, self.device)
+        self.workspace = Workspace(self.device)
+        self.err = torch.zeros(1, dtype=torch.int32, device=self.device)
+        self._meta_dev = None
+        self._meta_pin = [None, None]
+        self._meta_evt = [None, None]
+        self._flip = 0
+        self.steps = 0
+
+    # ---- requests ---------------------------------------------------------
+    def has_request(self, request_id) -> bool:
+        return request_id in self.cache.requests
+
+    def cached_tokens(self, request_id) -> int:
+        return self.cache.requests[request_id].num_tokens
+
+    def release(self, request_id):
+        """Give back what a finished (or pre-empted) request holds."""
+        if request_id in self.cache.requests:
+            self.cache.free(request_id)
+
+    # ---- the step ---------------------------------------------------------
+    def fits(self, entries: List[StepEntry]) -> bool:
+        need = [0] * len(self.cache.pools)
+        new_requests = 0
+        for e in entries:
+            if e.request_id in self.cache.requests:
+                pn = self.cache.pages_needed(e.request_id, len(e.tokens))
+            else:
+                new_requests += 1
+                pn = [-(-len(e.tokens) // self.page_size)] * len(self.cache.pools)
+            need = [a + b for a, b in zip(need, pn)]
+        return all(n <= p.free_count for n, p in zip(need, self.cache.pools)) and \
+            new_requests <= self.cache.slots.free_count
+
+    def step(self, entries: List[StepEntry]) -> torch.Tensor:
+        """Logits float32 [sum of len(want), vocab] on the device, in the order of
+        the entries and of their `want`.  Raises OutOfPages, with nothing changed,
+        when the pool cannot hold the new tokens."""
+        batch = self.prepare(entries)
+        logits = self.model.forward(batch, self.storage.call_caches)
+        self.finish(batch)
+        return logits
+
+    def prepare(self, entries: List[StepEntry]) -> StepBatch:
+        if not entries:
+            raise StepError("a step needs at least one entry")
+        seen = set()
+        for e in entries:
+            if len(e.tokens) == 0:
+                raise StepError(f"request {e.request_id!r} brings no token")
+            if e.request_id in seen:
+                raise StepError(f"request {e.request_id!r} appears twice in one step")
+            seen.add(e.request_id)
+            for w in e.want:
+                if not 0 <= w < len(e.tokens):
+                    raise StepError(f"request {e.request_id!r} wants place {w} of {len(e.tokens)} tokens")
+        if not self.fits(entries):
+            raise OutOfPages(f"the step needs more pages or slots than are free {self.cache.free_pages()}")
+        host_entries = []
+        for e in entries:
+            if e.request_id not in self.cache.requests:
+                self.cache.admit(e.request_id)
+            start = self.cache.append(e.request_id, len(e.tokens))
+            host_entries.append(Entry(e.request_id, start, len(e.tokens),
+                                      self.cache.requests[e.request_id].state_slot))
+        self.storage.zero_slots(self.cache.take_fresh_slots())
+        return self._layout_batch(entries, host_entries)
+
+    def _layout_batch(self, entries, host_entries) -> StepBatch:
+        B = len(entries)
+        T = sum(h.count for h in host_entries)
+        R = sum(len(e.want) for e in entries)
+        G = len(self.cache.pools)
+        ps = self.page_size
+        tables = [[self.cache.requests[e.request_id].block_tables[g] for e in entries] for g in range(G)]
+        max_blocks = [max(1, max(len(t) for t in tables[g])) for g in range(G)]
+        # section offsets (int32 words), each aligned to 16 bytes
+        off, cursor = {}, 0
+        def section(name, n):
+            nonlocal cursor
+            off[name] = (cursor, n)
+            cursor += _align4(max(n, 1))
+        for name, n in (("tokens", T), ("positions", T), ("req_index", T), ("cu_seqlens", B + 1),
+                        ("state_slots", B), ("logit_rows", R)):
+            section(name, n)
+        for g in range(G):
+            section(f"slots{g}", T)
+            section(f"table{g}", B * max_blocks[g])
+        meta = np.full(cursor, -1, dtype=np.int32)
+        def view(name):
+            o, n = off[name]
+            return meta[o:o + n]
+        tok, pos, req, cu = view("tokens"), view("positions"), view("req_index"), view("cu_seqlens")
+        rows = view("logit_rows")
+        cu[0] = 0
+        t = r = 0
+        for b, (e, h) in enumerate(zip(entries, host_entries)):
+            tok[t:t + h.count] = np.asarray(e.tokens, dtype=np.int64).astype(np.int32)
+            pos[t:t + h.count] = np.arange(h.start, h.start + h.count, dtype=np.int32)
+            req[t:t + h.count] = b
+            for w in e.want:
+                rows[r] = t + w
+                r += 1
+            t += h.count
+            cu[b + 1] = t
+        view("state_slots")[:] = [h.state_slot for h in host_entries]
+        for g in range(G):
+            tb = view(f"table{g}").reshape(B, max_blocks[g])
+            sl = view(f"slots{g}")
+            t = 0
+            for b, h in enumerate(host_entries):
+                tab = np.asarray(tables[g][b], dtype=np.int32)
+                tb[b, :len(tab)] = tab
+                p = np.arange(h.start, h.start + h.count)
+                pages = tab[p // ps]
+                if (pages < 0).any():
+                    raise StepError(f"request {h.request!r} writes into a page that was given back")
+                sl[t:t + h.count] = pages * ps + (p % ps)
+                t += h.count
+        dev = self._upload(meta)
+        def dview(name):
+            o, n = off[name]
+            return dev[o:o + n]
+        groups = []
+        for g in range(G):
+            groups.append(GroupView(page_size=ps, block_table=dview(f"table{g}").view(B, max_blocks[g]),
+                                    slots=dview(f"slots{g}"),
+                                    max_context=max(h.start + h.count for h in host_entries)))
+        return StepBatch(tokens=dview("tokens"), positions=dview("positions"), req_index=dview("req_index"),
+                         cu_seqlens=dview("cu_seqlens"), state_slots=dview("state_slots"),
+                         logit_rows=dview("logit_rows"), groups=groups, entries=host_entries, err=self.err,
+                         workspace=self.workspace, num_tokens=T, num_entries=B,
+                         max_query_len=max(h.count for h in host_entries))
+
+    def _upload(self, meta: np.ndarray) -> torch.Tensor:
+        n = meta.shape[0]
+        i = self._flip
+        self._flip ^= 1
+        if self._meta_evt[i] is not None:
+            self._meta_evt[i].synchronize()
+        if self._meta_pin[i] is None or self._meta_pin[i].numel() < n:
+            self._meta_pin[i] = torch.empty(max(n, 4096) * 2, dtype=torch.int32).pin_memory()
+        if self._meta_dev is None or self._meta_dev.numel() < n:
+            self._meta_dev = torch.empty(max(n, 4096) * 2, dtype=torch.int32, device=self.device)
+        pin = self._meta_pin[i]
+        pin[:n].numpy()[:] = meta
+        self._meta_dev[:n].copy_(pin[:n], non_blocking=True)
+        if self._meta_evt[i] is None:
+            self._meta_evt[i] = torch.cuda.Event()
+        self._meta_evt[i].record()
+        return self._meta_dev[:n]
+
+    def finish(self, batch: StepBatch):
+        """Bookkeeping after the step's kernels are queued: windows move on."""
+        for h in batch.entries:
+            self.cache.release_behind_window(h.request)
+        self.steps += 1
+
+    def check_device_errors(self):
+        """Read the device error word (synchronises); raise if a kernel refused an access."""
+        word = int(self.err.item())
+        if word:
+            self.err.zero_()
+            what = [msg for bit, msg in _DEVICE_ERRORS.items() if word & bit]
+            raise StepError("a kernel skipped an access: " + "; ".join(what))

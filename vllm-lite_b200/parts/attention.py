@@ -1,0 +1,82 @@
+"""Grouped-query attention with per-head norm of q and k before the rotation.
+
+project -> head norm -> rotation -> cache write -> attention over the pages ->
+output projection (crates/model/src/components/attention/rope_gqa.rs:261-305 of
+the reference).  The three projections are bound by their own tensor names and
+stacked at load time into one [q | k | v] matrix, which keeps every output row's
+arithmetic unchanged.  A prompt portion, a continuation and a decoded token are
+the same case: every token's key and value are written first, then each query
+reads positions 0..its own (or its window) from the pages.
+"""
+from __future__ import annotations
+
+import torch
+
+from ..cache.spec import PagedKV
+from .base import sub_weights
+from .linear import Linear
+from .registry import MIXERS, NORMS, POSITIONS
+from .spec import AttentionSpec, TensorDecl
+
+
+@MIXERS.register("gqa_attention")
+class GqaAttention:
+    @staticmethod
+    def declare(spec: AttentionSpec) -> dict:
+        qd, kvd = spec.num_heads * spec.head_dim, spec.num_kv_heads * spec.head_dim
+        d = {"q_proj.weight": TensorDecl((qd, spec.hidden_size)),
+             "k_proj.weight": TensorDecl((kvd, spec.hidden_size)),
+             "v_proj.weight": TensorDecl((kvd, spec.hidden_size)),
+             "o_proj.weight": TensorDecl((spec.hidden_size, qd))}
+        if spec.qk_norm is not None:
+            for side in ("q_norm.", "k_norm."):
+                for name, decl in NORMS.get(spec.qk_norm.kind).declare(spec.qk_norm).items():
+                    d[side + name] = decl
+        if spec.position is not None:
+            for name, decl in POSITIONS.get(spec.position.kind).declare(spec.position).items():
+                d["rotary." + name] = decl
+        return d
+
+    @staticmethod
+    def cache_need(spec: AttentionSpec):
+        return PagedKV(spec.num_kv_heads, spec.head_dim, spec.window)
+
+    def __init__(self, spec: AttentionSpec, weights: dict, ctx):
+        if spec.num_heads % spec.num_kv_heads:
+            raise ValueError(f"{spec.num_kv_heads} kv heads do not divide {spec.num_heads} query heads")
+        if spec.qk_norm is not None and spec.qk_norm.size != spec.head_dim:
+            raise ValueError("the head norm runs over head_dim")
+        self.spec = spec
+        self.dtype = ctx.dtype
+        qkv = torch.cat([weights["q_proj.weight"], weights["k_proj.weight"], weights["v_proj.weight"]], dim=0)
+        self.qkv_proj = Linear(qkv.contiguous())
+        self.o_proj = Linear(weights["o_proj.weight"])
+        self.q_norm = self.k_norm = None
+        if spec.qk_norm is not None:
+            cls = NORMS.get(spec.qk_norm.kind)
+            self.q_norm = cls(spec.qk_norm, sub_weights(weights, "q_norm."), ctx)
+            self.k_norm = cls(spec.qk_norm, sub_weights(weights, "k_norm."), ctx)
+        self.position = None
+        if spec.position is not None:
+            self.position = POSITIONS.get(spec.position.kind)(spec.position, sub_weights(weights, "rotary."), ctx)
+        self.scale = spec.scale if spec.scale is not None else spec.head_dim ** -0.5
+
+    def __call__(self, h, step, cache):
+        from ..csrc import ops
+        s = self.spec
+        group = step.groups[cache.group]
+        qkv = self.qkv_proj(h, step, "attn.qkv")
+        fused = self.position.fused_rotary() if self.position is not None else None
+        if self.position is not None and fused is None:
+            raise NotImplementedError("a position encoding without fused_rotary() must be applied by its own kernel")
+        inv_freq, rot = fused if fused is not None else (None, 0)
+        ops.qk_norm_rope_write(
+            qkv, step.positions, group.slots if cache.writes else None,
+            self.q_norm.weight if self.q_norm is not None else None,
+            self.k_norm.weight if self.k_norm is not None else None,
+            s.qk_norm.eps if s.qk_norm is not None else 0.0,
+            inv_freq, rot, cache.k, cache.v, s.num_heads, s.num_kv_heads, s.head_dim, step.err)
+        out = step.workspace.get(step.tag + "attn.out", (qkv.shape[0], s.num_heads * s.head_dim), self.dtype)
+        from . import attention_dispatch
+        attention_dispatch.run(qkv, out, cache, group, step, s, self.scale)
+        return self.o_proj(out, step, "attn.o")

@@ -1,0 +1,120 @@
+"""What parts are given at build time and at every step, and what each family must offer.
+
+Interfaces (duck-typed; a part is any class registered under its kind):
+
+  every part     declare(spec) -> {relative tensor name: TensorDecl}     static
+                 __init__(spec, weights, ctx)   weights: {relative name: device tensor}
+  norm           __call__(x, delta, step, rows=None) -> h
+                     x float32 [T, H] residual stream; delta (activation dtype) or None is
+                     added into x first (not stored when `rows` picks rows); h is new
+  position       fused_rotary() -> (inv_freq, rotary_dim) or None
+                 apply(qkv, positions, num_heads, num_kv_heads, head_dim, step)  when not fused
+  mixer          cache_need(spec) -> PagedKV | FixedState | None                  static
+                 __call__(h, step, cache) -> [T, hidden] in the activation dtype
+  feed-forward   __call__(h, step) -> [T, hidden]
+  block          __call__(residual, step, cache) -> None   (updates residual.x / residual.pending)
+
+No part learns which model it is in: it sees its own description, its own
+tensors, the step's batch and the cache of its own call.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+from typing import List, Optional
+
+import torch
+
+
+@dataclass
+class BuildContext:
+    device: torch.device
+    dtype: torch.dtype            # activation / model dtype: torch.bfloat16 or torch.float32
+
+
+class Workspace:
+    """Scratch buffers that live across steps, so that a step allocates nothing
+    once its shapes have been seen (and can be captured in a CUDA graph)."""
+
+    def __init__(self, device):
+        self.device = device
+        self._buffers = {}
+
+    def get(self, tag: str, shape, dtype) -> torch.Tensor:
+        n = 1
+        for s in shape:
+            n *= int(s)
+        key = (tag, dtype)
+        buf = self._buffers.get(key)
+        if buf is None or buf.numel() < n:
+            buf = torch.empty(max(n, 1), dtype=dtype, device=self.device)
+            self._buffers[key] = buf
+        return buf[:n].view(*shape)
+
+    def bytes(self) -> int:
+        return sum(b.numel() * b.element_size() for b in self._buffers.values())
+
+
+@dataclass
+class GroupView:
+    """One cache group as a step sees it."""
+    page_size: int
+    block_table: torch.Tensor       # int32 [B, max_blocks], -1 where no page is held
+    slots: torch.Tensor             # int32 [T]: page * page_size + offset of every token of the step
+    max_context: int = 0            # host copy: the longest context among the entries
+
+
+@dataclass
+class Entry:
+    """Host-side description of one request's share of a step."""
+    request: object
+    start: int                      # tokens of the request that are already in the cache
+    count: int                      # tokens it brings in this step
+    state_slot: int = -1
+
+
+@dataclass
+class StepBatch:
+    tokens: torch.Tensor            # int32 [T]
+    positions: torch.Tensor         # int32 [T] absolute position of each token in its request
+    req_index: torch.Tensor         # int32 [T] row of the block tables
+    cu_seqlens: torch.Tensor        # int32 [B + 1]
+    state_slots: torch.Tensor       # int32 [B] per-request state slot
+    logit_rows: torch.Tensor        # int32 [R] token indices whose logits are wanted
+    groups: List[GroupView]
+    entries: List[Entry]
+    err: torch.Tensor               # device error word (uint32 as int32 [1])
+    workspace: Workspace
+    num_tokens: int = 0
+    num_entries: int = 0
+    max_query_len: int = 0
+    tag: str = ""                   # namespace for workspace buffers
+
+
+@dataclass
+class CallCache:
+    """The cache of one entry of the running order.
+
+    Paged: `k`, `v` are [pages, kv_heads, page_size, head_dim]; `group` indexes
+    StepBatch.groups; `writes` is False for a call that reads an earlier call's
+    cache.  Fixed state: `state` is [slots, *shape], indexed by StepBatch.state_slots.
+    """
+    group: int = -1
+    k: Optional[torch.Tensor] = None
+    v: Optional[torch.Tensor] = None
+    writes: bool = True
+    state: Optional[torch.Tensor] = None
+
+
+@dataclass
+class Residual:
+    x: torch.Tensor                           # float32 [T, H]
+    pending: Optional[torch.Tensor] = None    # not yet added into x
+
+
+def sub_weights(weights: dict, prefix: str) -> dict:
+    n = len(prefix)
+    return {k[n:]: v for k, v in weights.items() if k.startswith(prefix)}
+
+
+def prefixed(decls: dict, prefix: str) -> dict:
+    return {prefix + k: v for k, v in decls.items()}

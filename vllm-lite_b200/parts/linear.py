@@ -1,0 +1,36 @@
+"""y = x W^T with the weight stored [out, in] and no bias
+(crates/model/src/components/attention/gqa/norm.rs:21-26 of the reference).
+
+The product runs in the precision of the stored weight: a bfloat16 weight on
+the tensor cores with float32 accumulation, a float32 weight through the true
+float32 kernel (activations are widened for it and the result narrowed back).
+"""
+from __future__ import annotations
+
+import torch
+
+
+class Linear:
+    def __init__(self, weight: torch.Tensor):
+        if weight.dim() != 2 or not weight.is_contiguous():
+            raise ValueError("a linear weight is a contiguous [out, in] matrix")
+        self.weight = weight
+        self.out_features, self.in_features = weight.shape
+
+    def __call__(self, a, step, tag, out_dtype=None):
+        from ..csrc import ops
+        from . import matmul
+        out_dtype = out_dtype or a.dtype
+        M = a.shape[0]
+        ws = step.workspace
+        if self.weight.dtype == torch.float32:
+            if a.dtype != torch.float32:
+                a = ops.cast(a, ws.get(step.tag + tag + ".a32", a.shape, torch.float32))
+            if out_dtype == torch.float32:
+                return ops.gemm_f32(a, self.weight, ws.get(step.tag + tag, (M, self.out_features), torch.float32))
+            y = ops.gemm_f32(a, self.weight, ws.get(step.tag + tag + ".y32", (M, self.out_features), torch.float32))
+            return ops.cast(y, ws.get(step.tag + tag, (M, self.out_features), out_dtype))
+        if a.dtype != self.weight.dtype:
+            raise TypeError(f"activation {a.dtype} does not match weight {self.weight.dtype}")
+        out = ws.get(step.tag + tag, (M, self.out_features), out_dtype)
+        return matmul.gemm_bf16(a, self.weight, out)

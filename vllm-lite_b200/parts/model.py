@@ -1,0 +1,62 @@
+"""A causal language model assembled from a `ModelPlan`:
+embedding -> the calls of the running order -> final norm -> output head
+(crates/model/src/causal_lm/mod.rs:180-221 of the reference).  Only the rows
+whose logits are wanted go through the final norm and the head."""
+from __future__ import annotations
+
+import torch
+
+from .base import BuildContext, CallCache, Residual, prefixed, sub_weights
+from .linear import Linear
+from .registry import BLOCKS, NORMS
+from .spec import ModelPlan, TensorDecl
+
+
+def declare_model(plan: ModelPlan) -> dict:
+    """Every tensor the model binds: {checkpoint name: TensorDecl}."""
+    d = {plan.embed_name: TensorDecl((plan.vocab_size, plan.hidden_size))}
+    for i, block in enumerate(plan.layers):
+        d.update(prefixed(BLOCKS.get(block.kind).declare(block), plan.layer_prefix.format(i)))
+    d.update(prefixed(NORMS.get(plan.final_norm.kind).declare(plan.final_norm), plan.final_norm_prefix))
+    if not plan.tie_word_embeddings:
+        d[plan.head_name] = TensorDecl((plan.vocab_size, plan.hidden_size))
+    return d
+
+
+def cache_needs(plan: ModelPlan) -> list:
+    """The need of every entry of the running order (None for an entry that
+    keeps nothing or that reads another entry's cache)."""
+    needs = []
+    for call in plan.order:
+        block = plan.layers[call.layer]
+        needs.append(None if call.cache_of is not None else BLOCKS.get(block.kind).cache_need(block))
+    return needs
+
+
+class CausalLM:
+    def __init__(self, plan: ModelPlan, weights: dict, ctx: BuildContext):
+        plan.validate()
+        self.plan = plan
+        self.ctx = ctx
+        self.embed_table = weights[plan.embed_name]
+        self.layers = [BLOCKS.get(b.kind)(b, sub_weights(weights, plan.layer_prefix.format(i)), ctx)
+                       for i, b in enumerate(plan.layers)]
+        self.final_norm = NORMS.get(plan.final_norm.kind)(plan.final_norm,
+                                                          sub_weights(weights, plan.final_norm_prefix), ctx)
+        head = self.embed_table if plan.tie_word_embeddings else weights[plan.head_name]
+        self.head = Linear(head)
+
+    def forward(self, step, caches) -> torch.Tensor:
+        """Logits float32 [len(step.logit_rows), vocab]."""
+        from ..csrc import ops
+        ws = step.workspace
+        x = ws.get(step.tag + "residual", (step.num_tokens, self.plan.hidden_size), torch.float32)
+        ops.embed(step.tokens, self.embed_table, x, step.err)
+        residual = Residual(x)
+        for call, cache in zip(self.plan.order, caches):
+            self.layers[call.layer](residual, step, cache)
+        R = step.logit_rows.shape[0]
+        if R == 0:
+            return ws.get(step.tag + "logits", (0, self.plan.vocab_size), torch.float32)
+        h = self.final_norm(residual.x, residual.pending, step, rows=step.logit_rows, tag="final_norm")
+        return self.head(h, step, "logits", out_dtype=torch.float32)
