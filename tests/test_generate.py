@@ -1,0 +1,112 @@
+"""Generation through the Python entry point and the command line."""
+import math
+import subprocess
+import sys
+from pathlib import Path
+
+import numpy as np
+import pytest
+import torch
+
+import helpers as H
+import plain_qwen3 as P
+
+pytestmark = pytest.mark.gpu
+ROOT = Path(__file__).resolve().parent.parent
+
+
+def plain_greedy(which, prompt, n):
+    toks = list(prompt)
+    for _ in range(n):
+        toks.append(P.argmax(H.plain_logits(which, toks)[-1].tolist()))
+    return toks[len(prompt):]
+
+
+def engine(which, dtype="float32", **kw):
+    from vllm_lite_b200 import LLMEngine
+    kw.setdefault("kv_blocks", 64)
+    return LLMEngine(str(H.model_dir(which)), dtype=dtype, block_size=H.TINY[which]["page_size"], **kw)
+
+
+@pytest.mark.parametrize("which,lengths", [("A", [5, 17, 33]), ("B", [1, 9, 40, 64, 100])])
+def test_greedy_generation_matches_the_plain_implementation(which, lengths):
+    prompts = [H.tokens_for(which, n, 50 + i) for i, n in enumerate(lengths)]
+    eng = engine(which, max_num_batched_tokens=48, prefill_chunk_size=13)
+    outs = eng.generate(prompts, max_tokens=16)
+    for p, o in zip(prompts, outs):
+        assert o == plain_greedy(which, p, 16)
+    st = eng.stats()
+    assert st["free_pages"] == [64] and st["finished"] == len(prompts)
+
+
+def test_greedy_generation_bfloat16_follows_the_plain_logits():
+    """bfloat16 may pick another token where two logits are close; every chosen token must be
+    within bfloat16 tolerance of the plain maximum given the tokens chosen so far."""
+    which = "B"
+    prompts = [H.tokens_for(which, n, 60 + i) for i, n in enumerate([9, 40])]
+    outs = engine(which, "bfloat16").generate(prompts, max_tokens=12)
+    for p, o in zip(prompts, outs):
+        toks = list(p)
+        for t in o:
+            row = H.plain_logits(which, toks)[-1]
+            assert float(row.max() - row[t]) <= H.TOL["bfloat16"] * float(row.abs().max()) * 2
+            toks.append(t)
+
+
+def test_preemption_by_recompute_gives_the_same_tokens():
+    which = "B"
+    prompts = [H.tokens_for(which, n, 70 + i) for i, n in enumerate([30, 28, 25])]
+    want = [plain_greedy(which, p, 20) for p in prompts]
+    eng = engine(which, kv_blocks=15, max_model_len=64)            # 120 slots for 3 x ~50 tokens: someone must yield
+    outs = eng.generate(prompts, max_tokens=20)
+    assert eng.stats()["preemptions"] >= 1
+    assert outs == want and eng.stats()["free_pages"] == [15]
+
+
+def test_temperature_sampling_with_a_seed():
+    from vllm_lite_b200 import SamplingParams
+    from vllm_lite_b200.sampling import seeded_uniform
+    which = "B"
+    prompt = H.tokens_for(which, 9, 80)
+    params = SamplingParams(temperature=0.8, seed=1234)
+    a = engine(which).generate([prompt], max_tokens=10, sampling_params=params)[0]
+    b = engine(which).generate([prompt, prompt[:5]], max_tokens=10, sampling_params=params)[0]
+    assert a == b                                                   # same seed, same prompt, whatever the batch
+    c = engine(which).generate([prompt], max_tokens=10, sampling_params=SamplingParams(temperature=0.8, seed=99))[0]
+    assert a != c
+    toks = list(prompt)
+    for step, t in enumerate(a):                                    # each draw is the inverse CDF at u(seed, step)
+        u = seeded_uniform(1234, step)
+        cdf = np.cumsum(P.temperature_probs(H.plain_logits(which, toks)[-1].tolist(), 0.8))
+        lo = cdf[t - 1] if t else 0.0
+        assert lo - 1e-4 <= u <= cdf[t] + 1e-4
+        toks.append(t)
+
+
+def test_stop_sequence_and_step_outputs():
+    from vllm_lite_b200 import SamplingParams
+    which = "A"
+    prompt = H.tokens_for(which, 17, 90)
+    free = plain_greedy(which, prompt, 8)
+    eng = engine(which)
+    sid = eng.add_request(prompt, 8, SamplingParams(stop_token_sequences=[free[2:4]]))
+    outs = []
+    while eng.has_unfinished():
+        outs += eng.step()
+    assert [o.token for o in outs] == free[:4] and outs[-1].finished and outs[-1].finish_reason == "stop"
+    assert all(o.seq_id == sid for o in outs)
+    with pytest.raises(ValueError):
+        eng.add_request([999999], 4)
+
+
+def test_command_line(tmp_path):
+    which = "A"
+    prompt = H.tokens_for(which, 12, 95)
+    cmd = [sys.executable, "-m", "vllm_lite_b200", "--model", str(H.model_dir(which)), "--dtype", "float32",
+           "--kv-blocks", "32", "--max-tokens", "6", "--prompt-ids", ",".join(map(str, prompt)), "--log-level", "warn"]
+    proc = subprocess.run(cmd, capture_output=True, text=True, cwd=ROOT, timeout=900)
+    assert proc.returncode == 0, proc.stderr[-2000:]
+    assert [int(t) for t in proc.stdout.strip().split(",")] == plain_greedy(which, prompt, 6)
+    bad = subprocess.run([sys.executable, "-m", "vllm_lite_b200", "--prompt-ids", "1,2"], capture_output=True, text=True,
+                         cwd=ROOT, env={k: v for k, v in __import__("os").environ.items() if k != "VLLM_MODEL"})
+    assert bad.returncode == 2 and "--model" in bad.stderr

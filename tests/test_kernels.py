@@ -1,0 +1,303 @@
+"""Each CUDA kernel alone against a plain float32 reference of the same operation,
+at sizes other than the engine's tiny configurations: head sizes in steps of 16,
+odd head counts and groups, widths and vocabularies that are no power of two."""
+import math
+
+import numpy as np
+import pytest
+import torch
+
+import plain_qwen3 as P
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda:0"
+DTYPES = [torch.float32, torch.bfloat16]
+
+
+def ops():
+    from vllm_lite_b200.csrc import ops as o
+    return o
+
+
+def err_word():
+    return torch.zeros(1, dtype=torch.int32, device=DEV)
+
+
+def tol(dtype):
+    return dict(atol=2e-5, rtol=2e-5) if dtype == torch.float32 else dict(atol=2e-2, rtol=2e-2)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_embed(dtype):
+    V, Hd = 1000 + 7, 200 + 8
+    table = torch.randn(V, Hd, device=DEV).to(dtype)
+    ids = torch.tensor([0, V - 1, 5, 5, 999], dtype=torch.int32, device=DEV)
+    out = torch.empty(5, Hd, device=DEV)
+    e = err_word()
+    ops().embed(ids, table, out, e)
+    assert torch.equal(out, table[ids.long()].float()) and int(e.item()) == 0
+    bad = torch.tensor([3, V], dtype=torch.int32, device=DEV)
+    out2 = torch.ones(2, Hd, device=DEV)
+    ops().embed(bad, table, out2, e)
+    assert int(e.item()) & 1 and torch.equal(out2[1], torch.zeros(Hd, device=DEV))   # flagged, not read
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("H", [48, 1000, 5120 + 16])
+def test_add_rmsnorm(dtype, H):
+    T, eps = 7, 3e-5
+    x = torch.randn(T, H, device=DEV) * 3
+    delta = torch.randn(T, H, device=DEV).to(dtype)
+    w = (1 + 0.1 * torch.randn(H, device=DEV))
+    ref_x = x + delta.float()
+    ref = P.rms_norm(ref_x.cpu(), w.cpu(), eps)
+    x1, out = x.clone(), torch.empty(T, H, device=DEV, dtype=dtype)
+    ops().add_rmsnorm(x1, delta, w, eps, out)
+    assert torch.equal(x1, ref_x)                                    # the stream now holds the sum
+    assert torch.allclose(out.float().cpu(), ref, **tol(dtype))
+    out0 = torch.empty(T, H, device=DEV, dtype=dtype)                # no pending delta
+    ops().add_rmsnorm(x.clone(), None, w, eps, out0)
+    assert torch.allclose(out0.float().cpu(), P.rms_norm(x.cpu(), w.cpu(), eps), **tol(dtype))
+    rows = torch.tensor([6, 2, 2], dtype=torch.int32, device=DEV)     # picked rows leave the stream alone
+    x2, outr = x.clone(), torch.empty(3, H, device=DEV, dtype=dtype)
+    ops().add_rmsnorm(x2, delta, w, eps, outr, rows=rows)
+    assert torch.equal(x2, x) and torch.allclose(outr.float().cpu(), ref[[6, 2, 2]], **tol(dtype))
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_silu_mul_and_cast(dtype):
+    T, I = 5, 333
+    gu = (torch.randn(T, 2 * I, device=DEV) * 4).to(dtype)
+    out = torch.empty(T, I, device=DEV, dtype=dtype)
+    ops().silu_mul(gu, out)
+    g, u = gu.float()[:, :I], gu.float()[:, I:]
+    assert torch.allclose(out.float(), g / (1 + torch.exp(-g)) * u, **tol(dtype))
+    src = torch.randn(1000, device=DEV)
+    b = torch.empty(1000, device=DEV, dtype=torch.bfloat16)
+    ops().cast(src, b)
+    assert torch.equal(b, src.to(torch.bfloat16))
+    back = torch.empty(1000, device=DEV)
+    ops().cast(b, back)
+    assert torch.equal(back, b.float())
+
+
+@pytest.mark.parametrize("M,N,K", [(1, 333, 96), (70, 130, 257), (200, 64, 1000), (3, 5, 7)])
+def test_gemm_f32_is_true_float32_and_batch_invariant(M, N, K):
+    a, w = torch.randn(M, K, device=DEV), torch.randn(N, K, device=DEV)
+    out = torch.empty(M, N, device=DEV)
+    ops().gemm_f32(a, w, out)
+    ref = (a.double().cpu() @ w.double().cpu().T)
+    assert float((out.cpu().double() - ref).abs().max()) <= 2e-6 * K ** 0.5 * float(ref.abs().max() + 1)
+    # TF32 would err by about 1e-3 relative; this bound is three orders tighter
+    one = torch.empty(1, N, device=DEV)
+    ops().gemm_f32(a[M - 1:M].contiguous(), w, one)
+    assert torch.equal(one[0], out[M - 1])                            # a row alone == the row in the batch
+
+
+def plain_head_norm_rope(x, w, eps, pos, theta, rot):
+    """x [T, heads, hd] -> norm over hd, then rotate the first `rot` features."""
+    y = P.rms_norm(x, w, eps) if w is not None else x
+    if rot:
+        y = torch.cat([P.rope(y[..., :rot], pos, theta), y[..., rot:]], dim=-1)
+    return y
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("nq,nkv,hd,rot,page", [(6, 3, 48, 48, 4), (5, 1, 80, 32, 16), (8, 8, 16, 16, 8), (4, 2, 256, 256, 32)])
+def test_qk_norm_rope_write(dtype, nq, nkv, hd, rot, page):
+    T, pages, theta, eps = 9, 6, 50000.0, 1e-5
+    qkv = torch.randn(T, (nq + 2 * nkv) * hd, device=DEV).to(dtype)
+    pos = torch.tensor([0, 1, 2, 40000, 7, 8, 9, 10, 300], dtype=torch.int32, device=DEV)
+    slot_list = [5, page, 3, 2 * page + 1, -1, pages * page - 1, 0, 7, 2]
+    slots = torch.tensor(slot_list, dtype=torch.int32, device=DEV)
+    qw, kw = 1 + 0.1 * torch.randn(hd, device=DEV), 1 + 0.1 * torch.randn(hd, device=DEV)
+    from vllm_lite_b200.parts.rope import inverse_frequencies
+    inv = torch.from_numpy(inverse_frequencies(rot, theta)).to(DEV)
+    assert np.array_equal(inverse_frequencies(rot, theta), P.rope_inv_freq(rot, theta).numpy())
+    kc = torch.full((pages, nkv, page, hd), 77.0, device=DEV, dtype=dtype)
+    vc = torch.full((pages, nkv, page, hd), 77.0, device=DEV, dtype=dtype)
+    src = qkv.float().cpu()
+    e = err_word()
+    ops().qk_norm_rope_write(qkv, pos, slots, qw, kw, eps, inv, rot, kc, vc, nq, nkv, hd, e)
+    assert int(e.item()) == 0
+    q_ref = plain_head_norm_rope(src[:, :nq * hd].view(T, nq, hd), qw.cpu(), eps, pos.tolist(), theta, rot)
+    k_ref = plain_head_norm_rope(src[:, nq * hd:(nq + nkv) * hd].view(T, nkv, hd), kw.cpu(), eps, pos.tolist(), theta, rot)
+    v_ref = src[:, (nq + nkv) * hd:].view(T, nkv, hd)
+    assert torch.allclose(qkv[:, :nq * hd].float().cpu().view(T, nq, hd), q_ref, **tol(dtype))
+    touched = torch.zeros(pages, page, dtype=torch.bool)
+    for t, s in enumerate(slot_list):
+        if s < 0:
+            continue
+        p, o = divmod(s, page)
+        touched[p, o] = True
+        assert torch.allclose(kc[p, :, o].float().cpu(), k_ref[t], **tol(dtype)), t
+        assert torch.equal(vc[p, :, o].float().cpu(), v_ref[t]), t
+    untouched = ~touched
+    assert bool((kc.float().cpu().permute(0, 2, 1, 3)[untouched] == 77.0).all())     # other slots keep their contents
+    assert bool((vc.float().cpu().permute(0, 2, 1, 3)[untouched] == 77.0).all())
+    # a slot outside the pool is flagged and skipped
+    ops().qk_norm_rope_write(qkv, pos, torch.full((T,), pages * page, dtype=torch.int32, device=DEV),
+                             qw, kw, eps, inv, rot, kc, vc, nq, nkv, hd, e)
+    assert int(e.item()) & 2
+
+
+def paged_reference(q, keys, values, pos, scale, window):
+    """q [nq, hd] at position pos against keys/values [n, nkv, hd] (n > pos)."""
+    nq, nkv = q.shape[0], keys.shape[1]
+    lo = 0 if not window else max(0, pos - window + 1)
+    out = torch.empty_like(q)
+    for h in range(nq):
+        kh = h // (nq // nkv)
+        s = (keys[lo:pos + 1, kh] @ q[h]) * scale
+        p = torch.softmax(s, dim=0)
+        out[h] = p @ values[lo:pos + 1, kh]
+    return out
+
+
+def build_paged(seqs_kv, nkv, hd, page, dtype, shuffle_seed=0):
+    """Scatter each sequence's keys/values into shuffled pages; returns caches and block table."""
+    total_pages = sum(-(-k.shape[0] // page) for k, _ in seqs_kv) + 3
+    perm = np.random.default_rng(shuffle_seed).permutation(total_pages).tolist()
+    kc = torch.full((total_pages, nkv, page, hd), float("nan"), dtype=dtype)
+    vc = torch.full((total_pages, nkv, page, hd), float("nan"), dtype=dtype)
+    max_blocks = max(-(-k.shape[0] // page) for k, _ in seqs_kv)
+    table = torch.full((len(seqs_kv), max_blocks), -1, dtype=torch.int32)
+    for b, (k, v) in enumerate(seqs_kv):
+        for blk in range(-(-k.shape[0] // page)):
+            pg = perm.pop()
+            table[b, blk] = pg
+            n = min(page, k.shape[0] - blk * page)
+            kc[pg, :, :n] = k[blk * page:blk * page + n].transpose(0, 1).to(dtype)
+            vc[pg, :, :n] = v[blk * page:blk * page + n].transpose(0, 1).to(dtype)
+    return kc.to(DEV), vc.to(DEV), table.to(DEV)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("nq,nkv,hd,page,window", [(6, 2, 48, 4, 0), (5, 5, 16, 16, 0), (8, 1, 128, 16, 0),
+                                                   (3, 1, 80, 8, 37), (4, 2, 256, 32, 0)])
+def test_paged_attention_ragged(dtype, nq, nkv, hd, page, window):
+    """A batch of a prompt portion, a continuation and two single tokens, pages shuffled."""
+    torch.manual_seed(nq * 100 + hd)
+    lens = [45, 130, 1, 77]                      # keys present per request
+    new = [45, 20, 1, 1]                         # query tokens of this step per request (the last `new` positions)
+    seqs = [(torch.randn(n, nkv, hd), torch.randn(n, nkv, hd)) for n in lens]
+    kc, vc, table = build_paged(seqs, nkv, hd, page, dtype)
+    rows, req, pos = [], [], []
+    for b, (n, c) in enumerate(zip(lens, new)):
+        for p_ in range(n - c, n):
+            req.append(b); pos.append(p_)
+    T = len(req)
+    q = torch.randn(T, nq, hd)
+    qkv = torch.zeros(T, (nq + 2 * nkv) * hd)
+    qkv[:, :nq * hd] = q.view(T, -1)
+    qkv = qkv.to(DEV).to(dtype)
+    out = torch.empty(T, nq * hd, device=DEV, dtype=dtype)
+    e = err_word()
+    scale = hd ** -0.5
+    ops().paged_attention(qkv, out, kc, vc, table, torch.tensor(req, dtype=torch.int32, device=DEV),
+                          torch.tensor(pos, dtype=torch.int32, device=DEV), nq, nkv, hd, scale, window, e)
+    assert int(e.item()) == 0
+    qd = qkv[:, :nq * hd].float().cpu().view(T, nq, hd)
+    for t in range(T):
+        k, v = seqs[req[t]]
+        ref = paged_reference(qd[t], k.to(dtype).float(), v.to(dtype).float(), pos[t], scale, window)
+        assert torch.allclose(out[t].float().cpu().view(nq, hd), ref, **tol(dtype)), (t, req[t], pos[t])
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("far,window", [(3, 0), (640, 0), (15, 0), (16, 0), (700, 300), (699, 300)])
+def test_attention_finds_one_far_key(dtype, far, window):
+    """One key among a thousand is made to stand out by scaling it and the query; the
+    output must be that key's value (or, when the window excludes it, must not be)."""
+    nq, nkv, hd, page, n = 2, 1, 64, 16, 1000
+    torch.manual_seed(far)
+    k, v = torch.randn(n, nkv, hd) * 0.1, torch.randn(n, nkv, hd)
+    direction = torch.nn.functional.normalize(torch.randn(hd), dim=0)
+    k[far, 0] = direction * 8
+    q = (direction * 40).expand(nq, hd).contiguous()
+    kc, vc, table = build_paged([(k, v)], nkv, hd, page, dtype, shuffle_seed=far)
+    qkv = torch.zeros(1, (nq + 2 * nkv) * hd)
+    qkv[0, :nq * hd] = q.view(-1)
+    qkv = qkv.to(DEV).to(dtype)
+    out = torch.empty(1, nq * hd, device=DEV, dtype=dtype)
+    e = err_word()
+    ops().paged_attention(qkv, out, kc, vc, table, torch.zeros(1, dtype=torch.int32, device=DEV),
+                          torch.tensor([n - 1], dtype=torch.int32, device=DEV), nq, nkv, hd, hd ** -0.5, window, e)
+    got = out.float().cpu().view(nq, hd)
+    target = v[far, 0].to(dtype).float()
+    inside = (not window) or far >= n - window
+    if inside:
+        assert torch.allclose(got[0], target, atol=3e-2) and torch.allclose(got[1], target, atol=3e-2)
+    else:
+        assert float((got[0] - target).abs().max()) > 0.3
+
+
+@pytest.mark.parametrize("V", [333, 5000, 151936])
+def test_sampling_greedy_and_temperature(V):
+    torch.manual_seed(V)
+    R = 6
+    logits = torch.randn(R, V, device=DEV) * 3
+    logits[1, 7] = logits[1, 400 % V] = 50.0                         # a tie: the lowest index wins
+    logits[2, 5] = float("nan")
+    tok = torch.empty(R, dtype=torch.int32, device=DEV)
+    ops().sample(logits, None, None, None, None, tok)
+    host = logits.cpu().tolist()
+    assert tok.cpu().tolist() == [P.argmax([(-math.inf if x != x else x) for x in row]) for row in host]
+    assert tok[1].item() == 7
+    temp = torch.tensor([0.8, 1.0, 0.0, 1.7, 0.3, 1.0], device=DEV)
+    u = torch.tensor([0.0, 0.37, 0.5, 0.93, 0.61, 0.999999], device=DEV)
+    lp = torch.empty(R, device=DEV)
+    ops().sample(logits, temp, torch.zeros(R, dtype=torch.int32, device=DEV), torch.ones(R, device=DEV), u, tok, lp)
+    for r in range(R):
+        t = float(temp[r])
+        got = int(tok[r])
+        if t == 0:
+            assert got == P.argmax([(-math.inf if x != x else x) for x in host[r]])
+            continue
+        c = np.cumsum(P.temperature_probs(host[r], t))
+        lo = c[got - 1] if got > 0 else 0.0
+        # u falls into the chosen token's interval of the CDF (up to fixed-point rounding)
+        assert lo - 1e-5 <= float(u[r]) <= c[got] + 1e-5, (r, got, lo, c[got])
+        assert abs(float(lp[r]) - math.log(P.temperature_probs(host[r], t)[got])) < 1e-3
+
+
+def test_sampling_top_k_top_p_and_penalties():
+    torch.manual_seed(3)
+    V = 1000
+    base = torch.randn(4, V, device=DEV) * 2
+    host = base.cpu().tolist()
+    tok = torch.empty(4, dtype=torch.int32, device=DEV)
+    temp = torch.ones(4, device=DEV)
+    # top-k: whatever u is, the draw lies among the k largest
+    kept_k = [set(np.argsort(host[r])[-5:].tolist()) for r in range(4)]
+    for uval in (0.0, 0.3, 0.77, 0.9999):
+        ops().sample(base, temp, torch.full((4,), 5, dtype=torch.int32, device=DEV), torch.ones(4, device=DEV),
+                     torch.full((4,), uval, device=DEV), tok)
+        assert all(int(tok[r]) in kept_k[r] for r in range(4))
+    # top-p: the draw lies in the plain implementation's nucleus, and every nucleus token can be reached
+    for top_p in (0.1, 0.5, 0.9):
+        keep = [set(P.top_p_keep(host[r], top_p)) for r in range(4)]
+        seen = [set() for _ in range(4)]
+        for uval in np.linspace(0, 0.99999, 97):
+            ops().sample(base, temp, torch.zeros(4, dtype=torch.int32, device=DEV), torch.full((4,), top_p, device=DEV),
+                         torch.full((4,), float(uval), device=DEV), tok)
+            for r in range(4):
+                assert int(tok[r]) in keep[r], (top_p, uval, r)
+                seen[r].add(int(tok[r]))
+        assert all(len(seen[r]) >= min(len(keep[r]), 3) for r in range(4))
+    # penalties and bias, ragged lists
+    logits = base.clone()
+    seen_ids = [[1, 5, 9], [], [0], [2, 3]]
+    off = torch.tensor([0, 3, 3, 4, 6], dtype=torch.int32, device=DEV)
+    ids = torch.tensor([1, 5, 9, 0, 2, 3], dtype=torch.int32, device=DEV)
+    rep = torch.tensor([1.5, 1.0, 2.0, 1.0], device=DEV)
+    pres = torch.tensor([0.0, 0.0, 0.25, 1.0], device=DEV)
+    boff = torch.tensor([0, 0, 2, 2, 2], dtype=torch.int32, device=DEV)
+    bids = torch.tensor([7, V + 5], dtype=torch.int32, device=DEV)
+    bvals = torch.tensor([4.0, 1.0], device=DEV)
+    ops().apply_penalties(logits, off, ids, rep, pres, boff, bids, bvals)
+    for r in range(4):
+        ref = P.apply_presence_penalty(P.apply_repeat_penalty(host[r], seen_ids[r], float(rep[r])), seen_ids[r], float(pres[r]))
+        if r == 1:
+            ref = P.apply_logit_bias(ref, {7: 4.0, V + 5: 1.0})
+        assert torch.allclose(logits[r].cpu(), torch.tensor(ref), atol=1e-6)

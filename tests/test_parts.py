@@ -1,0 +1,191 @@
+"""Each part alone against the plain implementation, a running order that names a
+layer twice and shares a cache, and a toy mixer with state of its own that is
+registered, built and stepped from this file without a change to the framework."""
+from dataclasses import dataclass
+
+import pytest
+import torch
+
+import helpers as H
+import plain_qwen3 as P
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda:0"
+
+
+def make_step(runner_like_workspace, T):
+    from vllm_lite_b200.parts.base import StepBatch, Workspace
+    z = torch.zeros(1, dtype=torch.int32, device=DEV)
+    return StepBatch(tokens=z, positions=z, req_index=z, cu_seqlens=z, state_slots=z, logit_rows=z, groups=[],
+                     entries=[], err=torch.zeros(1, dtype=torch.int32, device=DEV), workspace=Workspace(DEV),
+                     num_tokens=T, num_entries=1)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_norm_and_feed_forward_alone(dtype):
+    from vllm_lite_b200.parts import FEED_FORWARDS, NORMS
+    from vllm_lite_b200.parts.base import BuildContext
+    from vllm_lite_b200.parts.spec import NormSpec, SwiGLUSpec
+    ctx = BuildContext(torch.device(DEV), dtype)
+    T, Hd, I = 11, 72, 200
+    tol = dict(atol=1e-5, rtol=1e-5) if dtype == torch.float32 else dict(atol=3e-2, rtol=3e-2)
+    step = make_step(None, T)
+    w = 1 + 0.1 * torch.randn(Hd)
+    norm = NORMS.get("rms_norm")(NormSpec(Hd, 1e-4), {"weight": w.to(dtype)}, ctx)
+    x = torch.randn(T, Hd, device=DEV)
+    h = norm(x, None, step)
+    assert h.dtype == dtype
+    assert torch.allclose(h.float().cpu(), P.rms_norm(x.cpu(), w.to(dtype).float(), 1e-4), **tol)
+    spec = SwiGLUSpec(Hd, I)
+    decl = FEED_FORWARDS.get("swiglu").declare(spec)
+    assert decl["down_proj.weight"].shape == (Hd, I)
+    weights = {k: (torch.randn(d.shape) * 0.1).to(dtype).to(DEV) for k, d in decl.items()}
+    ffn = FEED_FORWARDS.get("swiglu")(spec, weights, ctx)
+    out = ffn(h, step)
+    ref = P.swiglu(h.float().cpu(), {"mlp." + k: v.float().cpu() for k, v in weights.items()}, "")
+    assert torch.allclose(out.float().cpu(), ref, **tol)
+
+
+def plain_with_order(cfg, w, ids, order, share):
+    """The plain model with a running order: layer indices, and for each call whether it
+    reuses the keys/values of an earlier call (then only its queries are its own)."""
+    cfg = P.normalise_config(cfg)
+    n = len(ids)
+    pos = list(range(n))
+    x = P.embedding(ids, w["model.embed_tokens.weight"])
+    kv = {}
+    nq, nkv, d, eps = cfg["num_attention_heads"], cfg["num_key_value_heads"], cfg["head_dim"], cfg["rms_norm_eps"]
+    for call, (layer, src) in enumerate(zip(order, share)):
+        pre = f"model.layers.{layer}."
+        h = P.rms_norm(x, w[pre + "input_layernorm.weight"], eps)
+        q = P.linear(h, w[pre + "self_attn.q_proj.weight"]).view(n, nq, d)
+        q = P.rope(P.head_norm(q, w[pre + "self_attn.q_norm.weight"], eps), pos, cfg["rope_theta"])
+        if src is None:
+            k = P.linear(h, w[pre + "self_attn.k_proj.weight"]).view(n, nkv, d)
+            k = P.rope(P.head_norm(k, w[pre + "self_attn.k_norm.weight"], eps), pos, cfg["rope_theta"])
+            v = P.linear(h, w[pre + "self_attn.v_proj.weight"]).view(n, nkv, d)
+            kv[call] = (k, v)
+        else:
+            k, v = kv[src]
+        o = P.causal_attention(q, k, v)
+        x = x + P.linear(o.reshape(n, nq * d), w[pre + "self_attn.o_proj.weight"])
+        x = x + P.swiglu(P.rms_norm(x, w[pre + "post_attention_layernorm.weight"], eps), w, pre)
+    return P.linear(P.rms_norm(x, w["model.norm.weight"], eps), w["model.embed_tokens.weight"])
+
+
+def test_order_may_repeat_a_layer_and_share_a_cache():
+    from vllm_lite_b200.config import plan_from_config_json
+    from vllm_lite_b200.engine import ModelRunner, StepEntry, load_model_dir
+    from vllm_lite_b200.parts.spec import LayerCall, ModelPlan
+    _, base, weights = load_model_dir(H.model_dir("A"), "float32", DEV)
+    order = (LayerCall(0), LayerCall(1), LayerCall(1), LayerCall(0, cache_of=0))
+    plan = ModelPlan(**{**base.__dict__, "order": order})
+    runner = ModelRunner(plan, weights, dtype=torch.float32, device=DEV, page_size=16, num_pages=8, max_requests=2)
+    assert len(runner.layout.paged_members[0]) == 3                     # three calls own a cache, one borrows
+    toks = H.tokens_for("A", 40, 5)
+    cfg, w = H.plain_model("A")
+    ref = plain_with_order(cfg, w, toks, [0, 1, 1, 0], [None, None, None, 0])
+    got = torch.cat([runner.step([StepEntry("r", toks[:23], list(range(23)))]),
+                     runner.step([StepEntry("r", toks[23:25], [0, 1])]),
+                     runner.step([StepEntry("r", toks[25:], list(range(15)))])]).cpu()
+    runner.check_device_errors()
+    assert float((got - ref).abs().max()) <= H.TOL["float32"] * float(ref.abs().max())
+    assert not torch.allclose(ref, P.forward(cfg, w, toks), atol=1e-3)   # the order matters
+
+
+# ---- a toy mixer with state of its own, defined here ---------------------------------
+@dataclass(frozen=True)
+class DecaySpec:
+    hidden_size: int
+    decay: float
+    kind: str = "toy_decay"
+
+
+class DecayMixer:
+    """s_t = decay * s_{t-1} + h_t;  out_t = s_t W^T.  The state s is one vector per request."""
+
+    @staticmethod
+    def declare(spec):
+        from vllm_lite_b200.parts.spec import TensorDecl
+        return {"mix.weight": TensorDecl((spec.hidden_size, spec.hidden_size))}
+
+    @staticmethod
+    def cache_need(spec):
+        from vllm_lite_b200.cache import FixedState
+        return FixedState((spec.hidden_size,))
+
+    def __init__(self, spec, weights, ctx):
+        self.spec, self.w, self.dtype = spec, weights["mix.weight"].float(), ctx.dtype
+
+    def __call__(self, h, step, cache):
+        out = torch.empty_like(h)
+        t = 0
+        for entry in step.entries:                        # portions of a request arrive in order
+            s = cache.state[entry.state_slot]
+            for i in range(t, t + entry.count):
+                s = self.spec.decay * s + h[i].float()
+                out[i] = (s @ self.w.T).to(self.dtype)
+            cache.state[entry.state_slot] = s
+            t += entry.count
+        return out
+
+
+def plain_decay_model(cfg, w, ids, decay):
+    """Layer 0: decay mixer + feed-forward; layer 1: the attention block of the plain model."""
+    cfg = P.normalise_config(cfg)
+    x = P.embedding(ids, w["model.embed_tokens.weight"])
+    pre = "model.layers.0."
+    h = P.rms_norm(x, w[pre + "input_layernorm.weight"], cfg["rms_norm_eps"])
+    s, outs = torch.zeros(cfg["hidden_size"]), []
+    for t in range(len(ids)):
+        s = decay * s + h[t]
+        outs.append(s @ w[pre + "self_attn.mix.weight"].T)
+    x = x + torch.stack(outs)
+    x = x + P.swiglu(P.rms_norm(x, w[pre + "post_attention_layernorm.weight"], cfg["rms_norm_eps"]), w, pre)
+    x = P.decoder_block(x, list(range(len(ids))), w, 1, cfg)
+    return P.linear(P.rms_norm(x, w["model.norm.weight"], cfg["rms_norm_eps"]), w["model.embed_tokens.weight"])
+
+
+def test_toy_mixer_with_state_registers_builds_and_steps():
+    from vllm_lite_b200.config import Qwen3Config, plan_from_config_json, register_architecture, unregister_architecture
+    from vllm_lite_b200.engine import ModelRunner, StepEntry, load_model_dir
+    from vllm_lite_b200.parts import MIXERS, declare_model
+    from vllm_lite_b200.parts.spec import BlockSpec, ModelPlan
+    from vllm_lite_b200.weights import random_tensors, write_safetensors
+    import json
+
+    def plan(cfg):
+        base = plan_from_config_json({**H.TINY_A, "architectures": ["Qwen3ForCausalLM"]})[1]
+        toy = BlockSpec(mixer=DecaySpec(cfg.hidden_size, 0.75), ffn=base.layers[0].ffn,
+                        norm1=base.layers[0].norm1, norm2=base.layers[0].norm2)
+        return ModelPlan(**{**base.__dict__, "architecture": "ToyDecayLM", "layers": (toy, base.layers[1])})
+
+    MIXERS.register("toy_decay", DecayMixer)
+    register_architecture("ToyDecayLM", Qwen3Config, plan)
+    try:
+        cfg_json = {**H.TINY_A, "architectures": ["ToyDecayLM"]}
+        d = H.tmp_root() / "toy_decay"
+        d.mkdir(exist_ok=True)
+        (d / "config.json").write_text(json.dumps(cfg_json))
+        _, p = plan_from_config_json(cfg_json)
+        decl = declare_model(p)
+        assert "model.layers.0.self_attn.mix.weight" in decl and "model.layers.0.self_attn.q_proj.weight" not in decl
+        write_safetensors(d / "model.safetensors", random_tensors(decl, 3, std=0.05))
+        _, p, weights = load_model_dir(d, "float32", DEV)
+        runner = ModelRunner(p, weights, dtype=torch.float32, device=DEV, page_size=16, num_pages=8, max_requests=3)
+        assert len(runner.layout.state_groups) == 1 and len(runner.layout.paged_groups) == 1
+        a, b = H.tokens_for("A", 30, 1), H.tokens_for("A", 19, 2)
+        cfg, w = P.read_model_dir(d)
+        ref_a, ref_b = plain_decay_model(cfg, w, a, 0.75), plain_decay_model(cfg, w, b, 0.75)
+        rows = H.run_schedule(runner, [
+            ([("a", a[:11], list(range(11)))], []),
+            ([("a", a[11:13], [0, 1]), ("b", b[:19], list(range(19)))], ["b"]),
+            ([("a", a[13:], list(range(17)))], ["a"]),
+            ([("b2", b, list(range(19)))], ["b2"]),          # b's slot is used again and starts from zero
+        ])
+        for (rid, pos), row in rows.items():
+            ref = ref_a if rid == "a" else ref_b
+            assert float((row - ref[pos]).abs().max()) <= 5e-5 * float(ref.abs().max()), (rid, pos)
+    finally:
+        MIXERS.unregister("toy_decay")
+        unregister_architecture("ToyDecayLM")
