@@ -85,15 +85,17 @@ def test_temperature_sampling_with_a_seed():
 
 def test_stop_sequence_and_step_outputs():
     from vllm_lite_b200 import SamplingParams
-    which = "A"
+    which = "B"
     prompt = H.tokens_for(which, 17, 90)
     free = plain_greedy(which, prompt, 8)
+    stop = free[2:4]
+    expect = next(free[:n] for n in range(2, 9) if free[:n][-2:] == stop)     # the first suffix match ends it
     eng = engine(which)
-    sid = eng.add_request(prompt, 8, SamplingParams(stop_token_sequences=[free[2:4]]))
+    sid = eng.add_request(prompt, 8, SamplingParams(stop_token_sequences=[stop]))
     outs = []
     while eng.has_unfinished():
         outs += eng.step()
-    assert [o.token for o in outs] == free[:4] and outs[-1].finished and outs[-1].finish_reason == "stop"
+    assert [o.token for o in outs] == expect and outs[-1].finished and outs[-1].finish_reason == "stop"
     assert all(o.seq_id == sid for o in outs)
     with pytest.raises(ValueError):
         eng.add_request([999999], 4)

@@ -85,9 +85,9 @@ def test_order_may_repeat_a_layer_and_share_a_cache():
     toks = H.tokens_for("A", 40, 5)
     cfg, w = H.plain_model("A")
     ref = plain_with_order(cfg, w, toks, [0, 1, 1, 0], [None, None, None, 0])
-    got = torch.cat([runner.step([StepEntry("r", toks[:23], list(range(23)))]),
-                     runner.step([StepEntry("r", toks[23:25], [0, 1])]),
-                     runner.step([StepEntry("r", toks[25:], list(range(15)))])]).cpu()
+    got = torch.cat([runner.step([StepEntry("r", toks[:23], list(range(23)))]).cpu(),   # a step's logits live
+                     runner.step([StepEntry("r", toks[23:25], [0, 1])]).cpu(),          # until the next step
+                     runner.step([StepEntry("r", toks[25:], list(range(15)))]).cpu()])
     runner.check_device_errors()
     assert float((got - ref).abs().max()) <= H.TOL["float32"] * float(ref.abs().max())
     assert not torch.allclose(ref, P.forward(cfg, w, toks), atol=1e-3)   # the order matters

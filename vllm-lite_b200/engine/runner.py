@@ -94,8 +94,9 @@ class ModelRunner:
 
     def step(self, entries: List[StepEntry]) -> torch.Tensor:
         """Logits float32 [sum of len(want), vocab] on the device, in the order of
-        the entries and of their `want`.  Raises OutOfPages, with nothing changed,
-        when the pool cannot hold the new tokens."""
+        the entries and of their `want`.  The tensor is a view of a buffer that the
+        next step writes again: copy what must outlive it.  Raises OutOfPages, with
+        nothing changed, when the pool cannot hold the new tokens."""
         batch = self.prepare(entries)
         logits = self.model.forward(batch, self.storage.call_caches)
         self.finish(batch)
