@@ -1,1 +1,263 @@
-"""placeholder"""
+"""Decode and prefill throughput of the engine at Qwen3-8B layer sizes on one B200.
+
+    python bench.py [--gpus 1] [--steps K] [--warmup W] [--batch 8] [--context 4096] [--layers 36]
+
+Prints ONE JSON line.  `value` is decoded tokens per second of K decode steps at the
+given batch, timed on the device with CUDA events (weights, 16 GB, are far larger than
+L2, so every step reads them from HBM).  `e2e` is the same metric through the Python
+entry point (`LLMEngine.step`): host token ids in through pinned memory, sampled ids
+back to the host, every step.  `prefill` is one 2,048-token prompt, `points` are decode
+at batch 1 and 64, `roofline` relates the decode step to the bytes it must read.
+Weights are random (seeded), prompts are seeded uniform token ids.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+from pathlib import Path
+
+ROOT = Path(__file__).resolve().parent
+sys.path.insert(0, str(ROOT))
+
+QWEN3_8B = dict(architectures=["Qwen3ForCausalLM"], model_type="qwen3", hidden_size=4096, num_hidden_layers=36,
+                num_attention_heads=32, num_key_value_heads=8, head_dim=128, intermediate_size=12288,
+                vocab_size=151936, rope_theta=1000000.0, rms_norm_eps=1e-6, tie_word_embeddings=False,
+                max_position_embeddings=40960)
+METRIC = "decode tok/s at batch 8 (Qwen3-8B, bf16)"
+PREFILL_TOKENS = 2048
+
+
+def peaks():
+    p = ROOT / "MEASURED_PEAKS.json"
+    if p.is_file():
+        d = json.loads(p.read_text())
+        return dict(hbm_gbs=d["hbm_gbs"], bf16_tflops=d["bf16_tflops"], source="measured")
+    return dict(hbm_gbs=6650.0, bf16_tflops=1590.0, source="fallback")
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while a region is timed."""
+    QUERY = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+             "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self):
+        self.samples, self.proc, self.thread = [], None, None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", "-i", "0", f"--query-gpu={self.QUERY}",
+                                          "--format=csv,noheader,nounits", "-lms", "100"],
+                                         stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+        except OSError:
+            return self
+        def pump():
+            for line in self.proc.stdout:
+                self.samples.append((time.time(), line.strip()))
+        self.thread = threading.Thread(target=pump, daemon=True)
+        self.thread.start()
+        return self
+
+    def stop(self):
+        if self.proc is not None:
+            self.proc.terminate()
+            try:
+                self.proc.wait(timeout=5)
+            except subprocess.TimeoutExpired:
+                self.proc.kill()
+
+    def summary(self, t0, t1):
+        rows = [l.split(", ") for t, l in self.samples if t0 <= t <= t1] or [l.split(", ") for _, l in self.samples]
+        rows = [r for r in rows if len(r) == 6 and r[0].isdigit()]
+        if not rows:
+            return None
+        mhz = sorted(int(r[0]) for r in rows)
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        reasons = [n for i, n in enumerate(names) if any(r[2 + i].strip().lower() == "active" for r in rows)]
+        return {"sm_mhz": mhz[len(mhz) // 2], "sm_max_mhz": int(rows[0][1]), "reasons": reasons, "samples": len(rows)}
+
+
+def model_bytes_and_flops(cfg, layers):
+    H, I, V = cfg["hidden_size"], cfg["intermediate_size"], cfg["vocab_size"]
+    nq, nkv, hd = cfg["num_attention_heads"], cfg["num_key_value_heads"], cfg["head_dim"]
+    per_layer = (nq + 2 * nkv) * hd * H + H * nq * hd + 3 * H * I          # matrix elements of one layer
+    norms = layers * (2 * H + 2 * hd) + H
+    weight_bytes = 2 * (layers * per_layer + V * H) + 4 * norms            # bf16 matrices, every one read once
+    kv_bytes_per_token = layers * 2 * nkv * hd * 2
+    T = PREFILL_TOKENS
+    prefill_flops = 2 * T * layers * per_layer + layers * 4 * nq * hd * (T * (T + 1) // 2) + 2 * V * H
+    return weight_bytes, kv_bytes_per_token, prefill_flops
+
+
+def reference_arm():
+    print(json.dumps({"impl": "reference", "unavailable":
+                      "pplmx/vllm-lite is a Rust workspace (no setup.py or pyproject.toml; pip reports 'not "
+                      "installable') and no cargo/rustc toolchain or crate registry exists offline"}))
+    return 0
+
+
+def decode_run(runner, sampler, batch, context, warmup, steps, fill, vocab, tag):
+    """W + K decode steps of `batch` requests that end at `context` tokens each.
+    Returns (ms per step, kernel launches per step, mean context over the timed steps)."""
+    import torch
+    from vllm_lite_b200.csrc import ops
+    from vllm_lite_b200.engine import StepEntry
+    from vllm_lite_b200.sampling import SamplingParams
+    start_len = context - (warmup + steps)
+    ids = [f"{tag}{i}" for i in range(batch)]
+    gen = torch.Generator().manual_seed(1234)
+    for rid in ids:
+        if fill == "prefill":                           # the cache holds what a real prompt leaves
+            prompt = torch.randint(0, vocab, (start_len,), generator=gen).tolist()
+            for lo in range(0, start_len, PREFILL_TOKENS):
+                runner.step([StepEntry(rid, prompt[lo:lo + PREFILL_TOKENS], [])])
+        else:                                           # pages are taken; their contents are random numbers
+            runner.cache.admit(rid)
+            runner.cache.append(rid, start_len)
+    greedy = [SamplingParams()] * batch
+    def one(step):
+        entries = [StepEntry(rid, [(7 * i + 13 * step) % vocab], [0]) for i, rid in enumerate(ids)]
+        logits = runner.step(entries)
+        sampler.sample(logits, greedy, [()] * batch)
+    for s in range(warmup):
+        one(s)
+    torch.cuda.synchronize()
+    n0 = ops.launch_count
+    t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    t0.record()
+    for s in range(steps):
+        one(warmup + s)
+    t1.record()
+    torch.cuda.synchronize()
+    ms = t0.elapsed_time(t1) / steps
+    launches = (ops.launch_count - n0) / steps
+    runner.check_device_errors()
+    for rid in ids:
+        runner.release(rid)
+    return ms, launches, start_len + warmup + (steps - 1) / 2 + 1
+
+
+def prefill_run(runner, vocab, repeats=3):
+    import torch
+    from vllm_lite_b200.engine import StepEntry
+    gen = torch.Generator().manual_seed(99)
+    times = []
+    for r in range(repeats + 1):
+        prompt = torch.randint(0, vocab, (PREFILL_TOKENS,), generator=gen).tolist()
+        torch.cuda.synchronize()
+        t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        t0.record()
+        runner.step([StepEntry("prefill", prompt, [PREFILL_TOKENS - 1])])
+        t1.record()
+        torch.cuda.synchronize()
+        runner.release("prefill")
+        if r:                                            # the first run warms up
+            times.append(t0.elapsed_time(t1))
+    times.sort()
+    return times[len(times) // 2]
+
+
+def e2e_run(engine, batch, context, warmup, steps, vocab):
+    """The same decode steps through LLMEngine.step: host ids in, sampled ids out, every step."""
+    import torch
+    gen = torch.Generator().manual_seed(4321)
+    prompt_len = context - (warmup + steps) - 2 * batch - 2
+    for _ in range(batch):
+        engine.add_request(torch.randint(0, vocab, (prompt_len,), generator=gen).tolist(), max_tokens=1 << 20)
+        while any(s.remaining > 1 for s in engine.scheduler.running) or engine.scheduler.waiting:
+            engine.step()
+    for _ in range(warmup):
+        engine.step()
+    torch.cuda.synchronize()
+    h2d0, t0 = engine.runner.uploaded_bytes, time.perf_counter()
+    produced = 0
+    for _ in range(steps):
+        produced += len(engine.step())
+    torch.cuda.synchronize()
+    dt = time.perf_counter() - t0
+    h2d = (engine.runner.uploaded_bytes - h2d0) / steps
+    for seq in list(engine.scheduler.running):
+        engine.cancel_request(seq.seq_id)
+    assert produced == batch * steps, (produced, batch, steps)
+    return produced / dt, h2d, 4 * batch
+
+
+def main(argv=None):
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=64)
+    ap.add_argument("--warmup", type=int, default=8)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--batch", type=int, default=8)
+    ap.add_argument("--context", type=int, default=4096)
+    ap.add_argument("--layers", type=int, default=QWEN3_8B["num_hidden_layers"])
+    ap.add_argument("--no-points", action="store_true", help="skip the batch 1 / 64 points and the prefill")
+    args = ap.parse_args(argv)
+    if args.impl == "reference":
+        return reference_arm()
+    if args.gpus != 1:
+        print(f"bench.py: this engine runs on one GPU; --gpus {args.gpus} is not built")
+        return 2
+    warmup = max(args.warmup, 3)
+
+    import torch
+    from vllm_lite_b200.csrc import ops
+    from vllm_lite_b200.engine import LLMEngine, random_model
+    cfg = dict(QWEN3_8B, num_hidden_layers=args.layers)
+    vocab = cfg["vocab_size"]
+    _, plan, weights = random_model(cfg, seed=0, dtype="bfloat16", device="cuda:0")
+    big = args.batch if args.no_points else max(args.batch, 64)
+    pages = big * (-(-args.context // 16) + 1) + PREFILL_TOKENS // 16 + 64
+    engine = LLMEngine(plan=plan, weights=weights, dtype="bfloat16", kv_blocks=pages, block_size=16, max_batch_size=big,
+                       max_num_batched_tokens=PREFILL_TOKENS, prefill_chunk_size=PREFILL_TOKENS,
+                       max_model_len=args.context + 64)
+    del weights
+    runner, sampler = engine.runner, engine.sampler
+    for t in runner.storage.paged:                        # pages that no prompt wrote hold random numbers
+        t.normal_()
+    weight_bytes, kv_per_token, prefill_flops = model_bytes_and_flops(cfg, args.layers)
+    pk = peaks()
+
+    clocks = ClockSampler().start()
+    w0 = time.time()
+    ms, launches, mean_ctx = decode_run(runner, sampler, args.batch, args.context, warmup, args.steps, "prefill", vocab, "d")
+    w1 = time.time()
+    e2e_tps, h2d, d2h = e2e_run(engine, args.batch, args.context, warmup, args.steps, vocab)
+    clocks.stop()
+    value = args.batch * 1000.0 / ms
+    step_bytes = weight_bytes + args.batch * mean_ctx * kv_per_token
+    achieved = step_bytes / (ms * 1e-3) / 1e9
+    out = {
+        "metric": METRIC, "value": round(value, 1), "unit": "tokens/s", "n_gpus": 1, "steps": args.steps,
+        "warmup": warmup, "ms_per_step": round(ms, 4), "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "bf16", "data": "synthetic (random weights N(0,0.02), uniform token ids)",
+        "config": {"model": "Qwen3-8B layer sizes", "layers": args.layers, "layers_full": QWEN3_8B["num_hidden_layers"],
+                   "hidden": cfg["hidden_size"], "heads": cfg["num_attention_heads"], "kv_heads": cfg["num_key_value_heads"],
+                   "head_dim": cfg["head_dim"], "intermediate": cfg["intermediate_size"], "vocab": vocab,
+                   "global_batch": args.batch, "seq_len": args.context, "block_size": 16, "parallelism": "single GPU",
+                   "kv_fill": "real prefill", "l2": "inputs (weights 16 GB) larger than L2, no flush",
+                   "peaks": pk["source"]},
+        "clocks": clocks.summary(w0, w1),
+        "e2e": {"value": round(e2e_tps, 1), "unit": "tokens/s", "h2d_bytes_per_step": int(h2d), "d2h_bytes_per_step": d2h},
+        "gpu_launches": int(round(launches * args.steps)),
+        "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": pk["hbm_gbs"], "unit": "GB/s",
+                     "frac": round(achieved / pk["hbm_gbs"], 4)},
+    }
+    if not args.no_points:
+        pms = prefill_run(runner, vocab)
+        out["prefill"] = {"value": round(PREFILL_TOKENS / pms * 1000.0, 1), "tokens": PREFILL_TOKENS, "ms": round(pms, 3),
+                          "frac": round(prefill_flops / (pms * 1e-3) / (pk["bf16_tflops"] * 1e12), 4)}
+        ms1, _, _ = decode_run(runner, sampler, 1, args.context, warmup, args.steps, "prefill", vocab, "s")
+        ms64, _, _ = decode_run(runner, sampler, 64, args.context, warmup, args.steps, "random", vocab, "l")
+        out["points"] = {"decode_b1": round(1000.0 / ms1, 1), "decode_b64": round(64 * 1000.0 / ms64, 1)}
+        out["config"]["kv_fill_b64"] = "random numbers"
+    print(json.dumps(out))
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

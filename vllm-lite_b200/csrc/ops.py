@@ -49,6 +49,7 @@ _SIGNATURES = {
                                 c_void_p, c_void_p, c_void_p],
 }
 _functions = {}
+launch_count = 0          # kernels of this library launched so far (graph replays add theirs)
 
 
 def _fn(lib: str, name: str):
@@ -70,7 +71,9 @@ def _stream():
 
 
 def _check(code: int, name: str):
+    global launch_count
     if code == 0:
+        launch_count += 1
         return
     if code < 0:
         raise KernelError(f"{name} refused its arguments: {_ERRORS.get(code, code)}")

@@ -45,10 +45,10 @@ class LLMEngine:
             if model is None:
                 raise ValueError("give a model folder (or plan and weights)")
             _, plan, weights = load_model_dir(model, self.dtype, device)
-        self.runner = ModelRunner(plan, weights, dtype=self.dtype, device=device, page_size=block_size,
-                                  num_pages=kv_blocks, max_requests=max_batch_size)
         if max_model_len is None:
             max_model_len = plan.max_position_embeddings
+        self.runner = ModelRunner(plan, weights, dtype=self.dtype, device=device, page_size=block_size,
+                                  num_pages=kv_blocks, max_requests=max_batch_size, max_context=max_model_len)
         self.scheduler = Scheduler(self.runner.cache, SchedulerConfig(
             max_num_seqs=max_batch_size, max_num_batched_tokens=max_num_batched_tokens,
             prefill_chunk_size=prefill_chunk_size, max_model_len=max_model_len))

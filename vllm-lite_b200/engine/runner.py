@@ -44,7 +44,8 @@ def _align4(n: int) -> int:
 
 class ModelRunner:
     def __init__(self, plan, weights: dict, *, dtype=torch.bfloat16, device="cuda:0", page_size: int = 16,
-                 num_pages=1024, max_requests: int = 256):
+                 num_pages=1024, max_requests: int = 256, decode_graphs: bool = True,
+                 max_context: Optional[int] = None):
         self.device = torch.device(device)
         if self.device.type != "cuda":
             raise StepError("the engine runs on a CUDA device only; there is no CPU path")
@@ -65,6 +66,15 @@ class ModelRunner:
         self._meta_evt = [None, None]
         self._flip = 0
         self.steps = 0
+        # Decode-only steps (one token per request) are replayed from CUDA graphs, one per
+        # batch-size bucket, when every part of the model launches only stream-ordered kernels.
+        self.decode_graphs = bool(decode_graphs) and getattr(self.model, "graph_safe", False)
+        self.max_context = int(max_context or plan.max_position_embeddings)
+        self._graphs = {}
+        self._graph_meta = {}
+        self.graph_replays = 0
+        self._graph_launches = {}
+        self.uploaded_bytes = 0
 
     # ---- requests ---------------------------------------------------------
     def has_request(self, request_id) -> bool:
@@ -98,9 +108,36 @@ class ModelRunner:
         next step writes again: copy what must outlive it.  Raises OutOfPages, with
         nothing changed, when the pool cannot hold the new tokens."""
         batch = self.prepare(entries)
-        logits = self.model.forward(batch, self.storage.call_caches)
+        if batch.graph_bucket:
+            logits = self._forward_graph(batch)[:sum(len(e.want) for e in entries)]
+        else:
+            logits = self.model.forward(batch, self.storage.call_caches)
         self.finish(batch)
         return logits
+
+    def _forward_graph(self, batch: StepBatch) -> torch.Tensor:
+        """Rows of padded requests come after the real ones, so the caller slices them off."""
+        key = (batch.graph_bucket, len(batch.logit_rows))
+        entry = self._graphs.get(key)
+        if entry is None:
+            # first sight of this bucket: run it as it is (also sizes the workspace), then record
+            logits = self.model.forward(batch, self.storage.call_caches)
+            torch.cuda.current_stream().synchronize()
+            from ..csrc import ops
+            before = ops.launch_count
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph):
+                static_logits = self.model.forward(batch, self.storage.call_caches)
+            self._graph_launches[key] = ops.launch_count - before
+            ops.launch_count = before                  # recording launches nothing
+            self._graphs[key] = (graph, static_logits)
+            return logits
+        graph, static_logits = entry
+        graph.replay()
+        from ..csrc import ops
+        ops.launch_count += self._graph_launches[key]
+        self.graph_replays += 1
+        return static_logits
 
     def prepare(self, entries: List[StepEntry]) -> StepBatch:
         if not entries:
@@ -125,16 +162,33 @@ class ModelRunner:
             host_entries.append(Entry(e.request_id, start, len(e.tokens),
                                       self.cache.requests[e.request_id].state_slot))
         self.storage.zero_slots(self.cache.take_fresh_slots())
-        return self._layout_batch(entries, host_entries)
+        return self._layout_batch(entries, host_entries, self._graph_bucket(entries, host_entries))
 
-    def _layout_batch(self, entries, host_entries) -> StepBatch:
-        B = len(entries)
-        T = sum(h.count for h in host_entries)
-        R = sum(len(e.want) for e in entries)
+    def _graph_bucket(self, entries, host_entries) -> int:
+        """Padded batch size of a decode-only step that can be replayed from a graph, else 0."""
+        if not self.decode_graphs or any(h.count != 1 for h in host_entries):
+            return 0
+        if any(len(e.want) != 1 for e in entries) or any(h.start + 1 > self.max_context for h in host_entries):
+            return 0
+        bucket = 1
+        while bucket < len(entries):
+            bucket *= 2
+        return bucket
+
+    def _layout_batch(self, entries, host_entries, bucket: int = 0) -> StepBatch:
+        real_B = len(entries)
+        real_T = sum(h.count for h in host_entries)
+        real_R = sum(len(e.want) for e in entries)
+        # a graph step is padded to its bucket with tokens at position -1: they read no key,
+        # write no cache slot, and their rows are cut off by the caller
+        B, T, R = (bucket, bucket, bucket) if bucket else (real_B, real_T, real_R)
         G = len(self.cache.pools)
         ps = self.page_size
         tables = [[self.cache.requests[e.request_id].block_tables[g] for e in entries] for g in range(G)]
-        max_blocks = [max(1, max(len(t) for t in tables[g])) for g in range(G)]
+        if bucket:
+            max_blocks = [-(-self.max_context // ps)] * G
+        else:
+            max_blocks = [max(1, max(len(t) for t in tables[g])) for g in range(G)]
         # section offsets (int32 words), each aligned to 16 bytes
         off, cursor = {}, 0
         def section(name, n):
@@ -153,6 +207,10 @@ class ModelRunner:
             return meta[o:o + n]
         tok, pos, req, cu = view("tokens"), view("positions"), view("req_index"), view("cu_seqlens")
         rows = view("logit_rows")
+        if bucket:
+            tok[:], req[:], cu[:] = 0, 0, real_T
+            rows[:] = np.arange(bucket)
+            view("state_slots")[:] = 0
         cu[0] = 0
         t = r = 0
         for b, (e, h) in enumerate(zip(entries, host_entries)):
@@ -164,7 +222,7 @@ class ModelRunner:
                 r += 1
             t += h.count
             cu[b + 1] = t
-        view("state_slots")[:] = [h.state_slot for h in host_entries]
+        view("state_slots")[:real_B] = [h.state_slot for h in host_entries]
         for g in range(G):
             tb = view(f"table{g}").reshape(B, max_blocks[g])
             sl = view(f"slots{g}")
@@ -178,7 +236,7 @@ class ModelRunner:
                     raise StepError(f"request {h.request!r} writes into a page that was given back")
                 sl[t:t + h.count] = pages * ps + (p % ps)
                 t += h.count
-        dev = self._upload(meta)
+        dev = self._upload(meta, bucket)
         def dview(name):
             o, n = off[name]
             return dev[o:o + n]
@@ -191,9 +249,10 @@ class ModelRunner:
                          cu_seqlens=dview("cu_seqlens"), state_slots=dview("state_slots"),
                          logit_rows=dview("logit_rows"), groups=groups, entries=host_entries, err=self.err,
                          workspace=self.workspace, num_tokens=T, num_entries=B,
-                         max_query_len=max(h.count for h in host_entries))
+                         max_query_len=max(h.count for h in host_entries),
+                         tag=f"g{bucket}." if bucket else "", graph_bucket=bucket)
 
-    def _upload(self, meta: np.ndarray) -> torch.Tensor:
+    def _upload(self, meta: np.ndarray, bucket: int = 0) -> torch.Tensor:
         n = meta.shape[0]
         i = self._flip
         self._flip ^= 1
@@ -205,11 +264,18 @@ class ModelRunner:
             self._meta_dev = torch.empty(max(n, 4096) * 2, dtype=torch.int32, device=self.device)
         pin = self._meta_pin[i]
         pin[:n].numpy()[:] = meta
-        self._meta_dev[:n].copy_(pin[:n], non_blocking=True)
+        if bucket:                                  # a graph reads its batch from a buffer of its own
+            dev = self._graph_meta.get(bucket)
+            if dev is None:
+                dev = self._graph_meta[bucket] = torch.empty(n, dtype=torch.int32, device=self.device)
+        else:
+            dev = self._meta_dev
+        dev[:n].copy_(pin[:n], non_blocking=True)
+        self.uploaded_bytes += 4 * n
         if self._meta_evt[i] is None:
             self._meta_evt[i] = torch.cuda.Event()
         self._meta_evt[i].record()
-        return self._meta_dev[:n]
+        return dev[:n]
 
     def finish(self, batch: StepBatch):
         """Bookkeeping after the step's kernels are queued: windows move on."""

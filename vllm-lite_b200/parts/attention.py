@@ -21,6 +21,8 @@ from .spec import AttentionSpec, TensorDecl
 
 @MIXERS.register("gqa_attention")
 class GqaAttention:
+    graph_safe = True          # launches only stream-ordered kernels: a step can be captured in a CUDA graph
+
     @staticmethod
     def declare(spec: AttentionSpec) -> dict:
         qd, kvd = spec.num_heads * spec.head_dim, spec.num_kv_heads * spec.head_dim

@@ -13,6 +13,9 @@ Interfaces (duck-typed; a part is any class registered under its kind):
                  __call__(h, step, cache) -> [T, hidden] in the activation dtype
   feed-forward   __call__(h, step) -> [T, hidden]
   block          __call__(residual, step, cache) -> None   (updates residual.x / residual.pending)
+  mixers and feed-forwards may set `graph_safe = True` when their forward only launches
+  stream-ordered kernels on static buffers (no host reads, no Python over the entries);
+  decode steps of a model whose parts all say so are replayed from CUDA graphs
 
 No part learns which model it is in: it sees its own description, its own
 tensors, the step's batch and the cache of its own call.
@@ -88,6 +91,7 @@ class StepBatch:
     num_entries: int = 0
     max_query_len: int = 0
     tag: str = ""                   # namespace for workspace buffers
+    graph_bucket: int = 0           # padded batch size when the step is replayed from a CUDA graph
 
 
 @dataclass

@@ -34,6 +34,7 @@ class PreNormBlock:
         self.mixer = MIXERS.get(spec.mixer.kind)(spec.mixer, sub_weights(weights, MIXER), ctx)
         self.norm2 = NORMS.get(spec.norm2.kind)(spec.norm2, sub_weights(weights, NORM2), ctx)
         self.ffn = FEED_FORWARDS.get(spec.ffn.kind)(spec.ffn, sub_weights(weights, FFN), ctx)
+        self.graph_safe = bool(getattr(self.mixer, "graph_safe", False) and getattr(self.ffn, "graph_safe", False))
 
     def __call__(self, residual, step, cache):
         h = self.norm1(residual.x, residual.pending, step, tag="norm1")

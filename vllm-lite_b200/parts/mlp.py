@@ -12,6 +12,8 @@ from .spec import SwiGLUSpec, TensorDecl
 
 @FEED_FORWARDS.register("swiglu")
 class SwiGLU:
+    graph_safe = True
+
     @staticmethod
     def declare(spec: SwiGLUSpec) -> dict:
         return {"gate_proj.weight": TensorDecl((spec.intermediate_size, spec.hidden_size)),

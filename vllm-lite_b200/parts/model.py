@@ -45,6 +45,7 @@ class CausalLM:
                                                           sub_weights(weights, plan.final_norm_prefix), ctx)
         head = self.embed_table if plan.tie_word_embeddings else weights[plan.head_name]
         self.head = Linear(head)
+        self.graph_safe = all(getattr(layer, "graph_safe", False) for layer in self.layers)
 
     def forward(self, step, caches) -> torch.Tensor:
         """Logits float32 [len(step.logit_rows), vocab]."""
