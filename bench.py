@@ -167,7 +167,8 @@ def e2e_run(engine, batch, context, warmup, steps, vocab):
     gen = torch.Generator().manual_seed(4321)
     prompt_len = context - (warmup + steps) - 2 * batch - 2
     for _ in range(batch):
-        engine.add_request(torch.randint(0, vocab, (prompt_len,), generator=gen).tolist(), max_tokens=1 << 20)
+        engine.add_request(torch.randint(0, vocab, (prompt_len,), generator=gen).tolist(),
+                           max_tokens=engine.scheduler.config.max_model_len - prompt_len)
         while any(s.remaining > 1 for s in engine.scheduler.running) or engine.scheduler.waiting:
             engine.step()
     for _ in range(warmup):
