@@ -204,9 +204,49 @@ def test_paged_attention_ragged(dtype, nq, nkv, hd, page, window):
         assert torch.allclose(out[t].float().cpu().view(nq, hd), ref, **tol(dtype)), (t, req[t], pos[t])
 
 
+def run_attention(kernel, qkv, out, kc, vc, table, req, pos, nq, nkv, hd, scale, window, e):
+    if kernel == "paged":
+        return ops().paged_attention(qkv, out, kc, vc, table, req, pos, nq, nkv, hd, scale, window, e)
+    ctx = int(pos.max()) + 1
+    S, n_acc, n_ml = ops().decode_attention_scratch(qkv.shape[0], nq, hd, ctx)
+    pa = torch.full((n_acc,), float("nan"), device=DEV)
+    pm = torch.full((n_ml,), float("nan"), device=DEV)
+    return ops().decode_attention(qkv, out, kc, vc, table, req, pos, nq, nkv, hd, scale, window, ctx, pa, pm, e)
+
+
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("far,window", [(3, 0), (640, 0), (15, 0), (16, 0), (700, 300), (699, 300)])
-def test_attention_finds_one_far_key(dtype, far, window):
+@pytest.mark.parametrize("nq,nkv,hd,page,window", [(6, 2, 48, 4, 0), (5, 5, 16, 16, 0), (32, 8, 128, 16, 0),
+                                                   (3, 1, 80, 8, 300), (16, 2, 256, 32, 0), (7, 1, 64, 16, 0)])
+def test_decode_attention_split(dtype, nq, nkv, hd, page, window):
+    """Single tokens of requests of very different lengths (one token, a chunk's edge, several
+    chunks), pages shuffled; a padded token at position -1 yields zeros."""
+    torch.manual_seed(nq * 10 + hd)
+    lens = [1, 255, 256, 257, 700, 1030]
+    seqs = [(torch.randn(n, nkv, hd), torch.randn(n, nkv, hd)) for n in lens]
+    kc, vc, table = build_paged(seqs, nkv, hd, page, dtype)
+    T = len(lens) + 1
+    req = torch.tensor(list(range(len(lens))) + [0], dtype=torch.int32, device=DEV)
+    pos = torch.tensor([n - 1 for n in lens] + [-1], dtype=torch.int32, device=DEV)
+    qkv = torch.zeros(T, (nq + 2 * nkv) * hd)
+    qkv[:, :nq * hd] = torch.randn(T, nq * hd)
+    qkv = qkv.to(DEV).to(dtype)
+    out = torch.full((T, nq * hd), 5.0, device=DEV, dtype=dtype)
+    e = err_word()
+    scale = hd ** -0.5
+    run_attention("decode", qkv, out, kc, vc, table, req, pos, nq, nkv, hd, scale, window, e)
+    assert int(e.item()) == 0
+    qd = qkv[:, :nq * hd].float().cpu().view(T, nq, hd)
+    for t, n in enumerate(lens):
+        k, v = seqs[t]
+        ref = paged_reference(qd[t], k.to(dtype).float(), v.to(dtype).float(), n - 1, scale, window)
+        assert torch.allclose(out[t].float().cpu().view(nq, hd), ref, **tol(dtype)), (t, n)
+    assert bool((out[T - 1] == 0).all())
+
+
+@pytest.mark.parametrize("kernel", ["paged", "decode"])
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("far,window", [(3, 0), (640, 0), (15, 0), (16, 0), (255, 0), (256, 0), (700, 300), (699, 300)])
+def test_attention_finds_one_far_key(kernel, dtype, far, window):
     """One key among a thousand is made to stand out by scaling it and the query; the
     output must be that key's value (or, when the window excludes it, must not be)."""
     nq, nkv, hd, page, n = 2, 1, 64, 16, 1000
@@ -221,8 +261,8 @@ def test_attention_finds_one_far_key(dtype, far, window):
     qkv = qkv.to(DEV).to(dtype)
     out = torch.empty(1, nq * hd, device=DEV, dtype=dtype)
     e = err_word()
-    ops().paged_attention(qkv, out, kc, vc, table, torch.zeros(1, dtype=torch.int32, device=DEV),
-                          torch.tensor([n - 1], dtype=torch.int32, device=DEV), nq, nkv, hd, hd ** -0.5, window, e)
+    run_attention(kernel, qkv, out, kc, vc, table, torch.zeros(1, dtype=torch.int32, device=DEV),
+                  torch.tensor([n - 1], dtype=torch.int32, device=DEV), nq, nkv, hd, hd ** -0.5, window, e)
     got = out.float().cpu().view(nq, hd)
     target = v[far, 0].to(dtype).float()
     inside = (not window) or far >= n - window

@@ -171,3 +171,300 @@ extern "C" int vl_paged_attention(const void* q, int q_stride, void* out, int dt
                                             num_pages, scale, window, err);
     return VL_ERR_UNSUPPORTED;
 }
+
+// ---------------------------------------------------------------------------------------
+// Decode attention with the key range split across blocks.
+//
+// vl_decode_attention: for steps in which every request brings few tokens (decoding).
+// A block serves one token, up to GT query heads that share a KV head (so a key is read
+// once for all of them) and one chunk of `chunk` key positions; chunk c covers the
+// absolute positions [c*chunk, (c+1)*chunk), so which keys meet in a block depends on
+// positions alone.  Inside, 16 groups of 8 lanes own the keys whose position is the
+// group's number modulo 16; a lane holds 16-byte pieces of the rows.  The groups' running
+// softmax states are merged by a fixed butterfly, the blocks' partial results by a second
+// kernel in chunk order.  Partials are float32 scratch memory given by the caller:
+//   part_acc [T, nq, S, hd] (unnormalised), part_ml [T, nq, S, 2] (maximum, sum).
+// ---------------------------------------------------------------------------------------
+#define DEC_THREADS 128
+
+template <typename T> struct Vec16;
+template <> struct Vec16<float> {
+    static constexpr int N = 4;
+    uint4 raw;
+    __device__ __forceinline__ void load(const float* p) { raw = *reinterpret_cast<const uint4*>(p); }
+    __device__ __forceinline__ void zero() { raw = make_uint4(0, 0, 0, 0); }
+    __device__ __forceinline__ float get(int i) const {
+        const unsigned w = i == 0 ? raw.x : i == 1 ? raw.y : i == 2 ? raw.z : raw.w;
+        return __uint_as_float(w);
+    }
+};
+template <> struct Vec16<bf16> {
+    static constexpr int N = 8;
+    uint4 raw;
+    __device__ __forceinline__ void load(const bf16* p) { raw = *reinterpret_cast<const uint4*>(p); }
+    __device__ __forceinline__ void zero() { raw = make_uint4(0, 0, 0, 0); }
+    __device__ __forceinline__ float get(int i) const {
+        const unsigned w = (i >> 1) == 0 ? raw.x : (i >> 1) == 1 ? raw.y : (i >> 1) == 2 ? raw.z : raw.w;
+        return __uint_as_float((i & 1) ? (w & 0xffff0000u) : (w << 16));   // bfloat16 is the top half of a float
+    }
+};
+
+template <typename T> __device__ __forceinline__ float att_exp(float x);
+template <> __device__ __forceinline__ float att_exp<float>(float x) { return expf(x); }
+template <> __device__ __forceinline__ float att_exp<bf16>(float x) { return __expf(x); }
+
+template <typename T, int NPASS, int GT>
+__global__ void __launch_bounds__(DEC_THREADS)
+decode_attention_split_kernel(const T* __restrict__ q, int q_stride,
+                              const T* __restrict__ kcache, const T* __restrict__ vcache,
+                              const int* __restrict__ block_table, int max_blocks,
+                              const int* __restrict__ req_index, const int* __restrict__ positions,
+                              int nq, int nkv, int hd, int page_size, int num_pages, float scale, int window,
+                              int chunk, int S, float* __restrict__ part_acc, float* __restrict__ part_ml,
+                              unsigned* err) {
+    constexpr int EPV = Vec16<T>::N;
+    __shared__ float s_acc[DEC_THREADS / 32][GT][ATT_MAX_HD];
+    __shared__ float s_m[DEC_THREADS / 32][GT], s_l[DEC_THREADS / 32][GT];
+    const int split = blockIdx.x, t = blockIdx.z;
+    const int g = nq / nkv;
+    const int tiles = (g + GT - 1) / GT;
+    const int kvh = blockIdx.y / tiles, tile = blockIdx.y - kvh * tiles;
+    const int h0 = kvh * g + tile * GT;
+    const int nvalid = min(GT, g - tile * GT);
+    const int pos = positions[t];
+    if (pos < 0) return;
+    const int lo = (window > 0 && pos - window + 1 > 0) ? pos - window + 1 : 0;
+    const int c0 = max(split * chunk, lo);
+    const int c1 = min((split + 1) * chunk, pos + 1);
+    if (c0 >= c1) return;
+    const int tid = threadIdx.x, gi = tid >> 3, l = tid & 7, warp = tid >> 5;
+    const int nvec = hd / EPV;                           // 16-byte pieces per row
+    const int* table = block_table + (size_t)req_index[t] * max_blocks;
+
+    float qv[GT][NPASS][EPV], acc[GT][NPASS][EPV], m[GT], lsum[GT];
+#pragma unroll
+    for (int hh = 0; hh < GT; ++hh) {
+        m[hh] = -INFINITY; lsum[hh] = 0.f;
+#pragma unroll
+        for (int p = 0; p < NPASS; ++p) {
+            Vec16<T> v; v.zero();
+            const int c = l + 8 * p;
+            if (hh < nvalid && c < nvec) v.load(q + (size_t)t * q_stride + (size_t)(h0 + hh) * hd + c * EPV);
+#pragma unroll
+            for (int i = 0; i < EPV; ++i) { qv[hh][p][i] = v.get(i) * scale; acc[hh][p][i] = 0.f; }
+        }
+    }
+    for (int jb = (c0 / ATT_GROUPS) * ATT_GROUPS; jb < c1; jb += ATT_GROUPS) {
+        const int j = jb + gi;
+        bool valid = (j >= c0) && (j < c1);
+        size_t base = 0;
+        if (valid) {
+            const int blk = j / page_size;
+            const int page = blk < max_blocks ? table[blk] : -1;
+            if (page < 0 || page >= num_pages) {
+                if (l == 0) atomicOr(err, VL_DEV_BAD_PAGE);
+                valid = false;
+            } else {
+                base = (((size_t)page * nkv + kvh) * page_size + (j - blk * page_size)) * hd;
+            }
+        }
+        Vec16<T> kr[NPASS], vr[NPASS];
+#pragma unroll
+        for (int p = 0; p < NPASS; ++p) {
+            kr[p].zero(); vr[p].zero();
+            const int c = l + 8 * p;
+            if (valid && c < nvec) {
+                kr[p].load(kcache + base + c * EPV);
+                vr[p].load(vcache + base + c * EPV);
+            }
+        }
+        float dot[GT];
+#pragma unroll
+        for (int hh = 0; hh < GT; ++hh) {
+            float d = 0.f;
+#pragma unroll
+            for (int p = 0; p < NPASS; ++p)
+#pragma unroll
+                for (int i = 0; i < EPV; ++i) d = fmaf(qv[hh][p][i], kr[p].get(i), d);
+            d += __shfl_xor_sync(0xffffffffu, d, 4);
+            d += __shfl_xor_sync(0xffffffffu, d, 2);
+            d += __shfl_xor_sync(0xffffffffu, d, 1);
+            dot[hh] = d;
+        }
+        if (valid) {
+#pragma unroll
+            for (int hh = 0; hh < GT; ++hh) {
+                const float s = dot[hh];
+                const float mn = fmaxf(m[hh], s);
+                const float corr = att_exp<T>(m[hh] - mn);
+                const float pr = att_exp<T>(s - mn);
+                lsum[hh] = lsum[hh] * corr + pr;
+                m[hh] = mn;
+#pragma unroll
+                for (int p = 0; p < NPASS; ++p)
+#pragma unroll
+                    for (int i = 0; i < EPV; ++i) acc[hh][p][i] = fmaf(pr, vr[p].get(i), acc[hh][p][i] * corr);
+            }
+        }
+    }
+    // merge the 4 groups of a warp (lanes l, l+8, l+16, l+24 hold the same pieces)
+#pragma unroll
+    for (int hh = 0; hh < GT; ++hh) {
+#pragma unroll
+        for (int o = 8; o <= 16; o <<= 1) {
+            const float mo = __shfl_xor_sync(0xffffffffu, m[hh], o);
+            const float lo_ = __shfl_xor_sync(0xffffffffu, lsum[hh], o);
+            const float mn = fmaxf(m[hh], mo);
+            const float wa = (m[hh] == -INFINITY) ? 0.f : att_exp<T>(m[hh] - mn);
+            const float wb = (mo == -INFINITY) ? 0.f : att_exp<T>(mo - mn);
+            lsum[hh] = lsum[hh] * wa + lo_ * wb;
+#pragma unroll
+            for (int p = 0; p < NPASS; ++p)
+#pragma unroll
+                for (int i = 0; i < EPV; ++i) {
+                    const float ao = __shfl_xor_sync(0xffffffffu, acc[hh][p][i], o);
+                    acc[hh][p][i] = acc[hh][p][i] * wa + ao * wb;
+                }
+            m[hh] = mn;
+        }
+        if (gi % 4 == 0) {
+#pragma unroll
+            for (int p = 0; p < NPASS; ++p) {
+                const int c = l + 8 * p;
+                if (c < nvec) {
+#pragma unroll
+                    for (int i = 0; i < EPV; ++i) s_acc[warp][hh][c * EPV + i] = acc[hh][p][i];
+                }
+            }
+            if (l == 0) { s_m[warp][hh] = m[hh]; s_l[warp][hh] = lsum[hh]; }
+        }
+    }
+    __syncthreads();
+    // merge the warps in order and write the block's partial result
+    for (int idx = tid; idx < nvalid * hd; idx += DEC_THREADS) {
+        const int hh = idx / hd, e = idx - hh * hd;
+        float M = -INFINITY;
+#pragma unroll
+        for (int w = 0; w < DEC_THREADS / 32; ++w) M = fmaxf(M, s_m[w][hh]);
+        float o = 0.f, L = 0.f;
+#pragma unroll
+        for (int w = 0; w < DEC_THREADS / 32; ++w) {
+            const float wgt = (s_m[w][hh] == -INFINITY) ? 0.f : att_exp<T>(s_m[w][hh] - M);
+            o += s_acc[w][hh][e] * wgt;
+            L += s_l[w][hh] * wgt;
+        }
+        const size_t row = ((size_t)t * nq + (h0 + hh)) * S + split;
+        part_acc[row * hd + e] = o;
+        if (e == 0) { part_ml[row * 2] = M; part_ml[row * 2 + 1] = L; }
+    }
+}
+
+template <typename T>
+__global__ void decode_attention_merge_kernel(const float* __restrict__ part_acc, const float* __restrict__ part_ml,
+                                              const int* __restrict__ positions, T* __restrict__ out,
+                                              int nq, int hd, int chunk, int S, int window) {
+    const int t = blockIdx.x, h = blockIdx.y;
+    const int pos = positions[t];
+    T* op = out + ((size_t)t * nq + h) * hd;
+    if (pos < 0) {
+        for (int e = threadIdx.x; e < hd; e += blockDim.x) op[e] = from_f32<T>(0.f);
+        return;
+    }
+    const int lo = (window > 0 && pos - window + 1 > 0) ? pos - window + 1 : 0;
+    const int s0 = lo / chunk, s1 = pos / chunk;
+    const size_t row0 = ((size_t)t * nq + h) * S;
+    float M = -INFINITY;
+    for (int s = s0; s <= s1; ++s) M = fmaxf(M, part_ml[(row0 + s) * 2]);
+    float L = 0.f;
+    for (int s = s0; s <= s1; ++s) {
+        const float ms = part_ml[(row0 + s) * 2];
+        L += (ms == -INFINITY) ? 0.f : part_ml[(row0 + s) * 2 + 1] * att_exp<T>(ms - M);
+    }
+    const float invL = L > 0.f ? 1.0f / L : 0.f;
+    for (int e = threadIdx.x; e < hd; e += blockDim.x) {
+        float o = 0.f;
+        for (int s = s0; s <= s1; ++s) {
+            const float ms = part_ml[(row0 + s) * 2];
+            if (ms != -INFINITY) o += part_acc[(row0 + s) * hd + e] * att_exp<T>(ms - M);
+        }
+        op[e] = from_f32<T>(o * invL);
+    }
+}
+
+template <typename T, int NPASS>
+static int launch_decode_split(int GT, dim3 grid, cudaStream_t s, const T* q, int q_stride, const T* kc, const T* vc,
+                               const int* bt, int max_blocks, const int* req, const int* pos, int nq, int nkv, int hd,
+                               int page_size, int num_pages, float scale, int window, int chunk, int S,
+                               float* pacc, float* pml, unsigned* err) {
+#define DEC_CASE(G)                                                                                        \
+    case G:                                                                                                \
+        decode_attention_split_kernel<T, NPASS, G><<<grid, DEC_THREADS, 0, s>>>(                           \
+            q, q_stride, kc, vc, bt, max_blocks, req, pos, nq, nkv, hd, page_size, num_pages, scale,       \
+            window, chunk, S, pacc, pml, err);                                                             \
+        break;
+    switch (GT) { DEC_CASE(1) DEC_CASE(2) DEC_CASE(4) default: return VL_ERR_UNSUPPORTED; }
+#undef DEC_CASE
+    return vl_launch_status();
+}
+
+template <typename T>
+static int decode_attention_typed(const T* q, int q_stride, T* out, const T* kc, const T* vc, const int* bt,
+                                  int max_blocks, const int* req, const int* pos, int T_, int nq, int nkv, int hd,
+                                  int page_size, int num_pages, float scale, int window, int chunk, int S,
+                                  float* pacc, float* pml, unsigned* err, cudaStream_t s) {
+    constexpr int EPV = Vec16<T>::N;
+    const int g = nq / nkv;
+    // heads per block: as many of the group as keep a lane's registers (hd / 8 values per head) in bounds
+    int GT = g >= 4 ? 4 : (g >= 2 ? 2 : 1);
+    while (GT > 1 && GT * (hd / 8) > 64) GT >>= 1;
+    const int tiles = (g + GT - 1) / GT;
+    const int npass = (hd / EPV + 7) / 8;
+    dim3 grid(S, nkv * tiles, T_);
+    int rc;
+#define DEC_PASS(P)                                                                                         \
+    case P:                                                                                                 \
+        rc = launch_decode_split<T, P>(GT, grid, s, q, q_stride, kc, vc, bt, max_blocks, req, pos, nq, nkv, \
+                                       hd, page_size, num_pages, scale, window, chunk, S, pacc, pml, err);  \
+        break;
+    if (npass * EPV > 32) return VL_ERR_UNSUPPORTED;      // head_dim beyond 256
+    switch (npass) {
+        DEC_PASS(1) DEC_PASS(2) DEC_PASS(3) DEC_PASS(4)
+        default:
+            if constexpr (EPV == 4) {
+                switch (npass) { DEC_PASS(5) DEC_PASS(6) DEC_PASS(7) DEC_PASS(8) default: return VL_ERR_UNSUPPORTED; }
+            } else {
+                return VL_ERR_UNSUPPORTED;
+            }
+    }
+#undef DEC_PASS
+    if (rc != 0) return rc;
+    decode_attention_merge_kernel<T><<<dim3(T_, nq), 128, 0, s>>>(pacc, pml, pos, out, nq, hd, chunk, S, window);
+    return vl_launch_status();
+}
+
+// Scratch: part_acc holds T*nq*S*hd floats and part_ml T*nq*S*2 floats, S = ceil(max_context / chunk),
+// where max_context bounds positions + 1 of every token of the step.
+extern "C" int vl_decode_attention(const void* q, int q_stride, void* out, int dtype,
+                                   const void* kcache, const void* vcache,
+                                   const int* block_table, int max_blocks,
+                                   const int* req_index, const int* positions,
+                                   int T, int nq, int nkv, int hd, int page_size, int num_pages,
+                                   float scale, int window, int chunk, int S,
+                                   float* part_acc, float* part_ml, unsigned* err, void* stream) {
+    if (T <= 0) return VL_OK;
+    if (hd <= 0 || hd % 16 || hd > ATT_MAX_HD) return VL_ERR_UNSUPPORTED;
+    if (nq <= 0 || nkv <= 0 || nq % nkv || page_size <= 0 || max_blocks <= 0) return VL_ERR_ARGUMENT;
+    if (chunk <= 0 || chunk % ATT_GROUPS || S <= 0 || S > 65535 || T > 65535) return VL_ERR_ARGUMENT;
+    cudaStream_t s = (cudaStream_t)stream;
+    if (dtype == VL_F32)
+        return decode_attention_typed<float>((const float*)q, q_stride, (float*)out, (const float*)kcache,
+                                             (const float*)vcache, block_table, max_blocks, req_index, positions,
+                                             T, nq, nkv, hd, page_size, num_pages, scale, window, chunk, S,
+                                             part_acc, part_ml, err, s);
+    if (dtype == VL_BF16)
+        return decode_attention_typed<bf16>((const bf16*)q, q_stride, (bf16*)out, (const bf16*)kcache,
+                                            (const bf16*)vcache, block_table, max_blocks, req_index, positions,
+                                            T, nq, nkv, hd, page_size, num_pages, scale, window, chunk, S,
+                                            part_acc, part_ml, err, s);
+    return VL_ERR_UNSUPPORTED;
+}

@@ -102,6 +102,12 @@ def _compile(name: str, out: Path) -> Path:
         tmp.unlink(missing_ok=True)
         raise BuildError(f"nvcc failed on {name}.cu:\n{log}")
     os.replace(tmp, out)
+    for stale in out.parent.glob(f"{name}.*.so"):          # libraries of earlier versions of this source
+        if stale != out and ".tmp" not in stale.name:
+            try:
+                stale.unlink()
+            except OSError:
+                pass
     _say(f"built {out.name} in {time.time() - t0:.1f} s")
     return out
 

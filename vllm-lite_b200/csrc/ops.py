@@ -41,6 +41,9 @@ _SIGNATURES = {
     ("attention", "vl_paged_attention"): [c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int,
                                           c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int,
                                           c_float, c_int, c_void_p, c_void_p],
+    ("attention", "vl_decode_attention"): [c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int,
+                                           c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int,
+                                           c_float, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p],
     ("activation", "vl_silu_mul"): [c_void_p, c_void_p, c_int, c_int, c_int, c_void_p],
     ("gemm_f32", "vl_gemm_f32_nt"): [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p],
     ("sampling", "vl_apply_penalties"): [c_void_p, c_longlong, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p,
@@ -193,6 +196,45 @@ def paged_attention(qkv, out, k_cache, v_cache, block_table, req_index, position
         _ptr(block_table), block_table.shape[1], _ptr(req_index), _ptr(positions),
         T, num_heads, num_kv_heads, head_dim, k_cache.shape[2], k_cache.shape[0],
         float(scale), int(window or 0), _ptr(err), _stream()), "vl_paged_attention")
+    return out
+
+
+DECODE_CHUNK = 256        # key positions per block of the split decode kernel
+
+
+def decode_attention_scratch(num_tokens, num_heads, head_dim, max_context, chunk=DECODE_CHUNK):
+    """(splits, floats of part_acc, floats of part_ml) that `decode_attention` needs."""
+    S = max(1, -(-int(max_context) // chunk))
+    return S, num_tokens * num_heads * S * head_dim, num_tokens * num_heads * S * 2
+
+
+def decode_attention(qkv, out, k_cache, v_cache, block_table, req_index, positions, num_heads, num_kv_heads,
+                     head_dim, scale, window, max_context, part_acc, part_ml, err, chunk=DECODE_CHUNK):
+    """Same function as `paged_attention`, for steps of few tokens per request: the key range of
+    a token is split over blocks of `chunk` positions and merged.  `max_context` bounds
+    position + 1 of every token; part_acc / part_ml are float32 scratch (see
+    `decode_attention_scratch`)."""
+    _need(qkv, None, "qkv", 2); _need(out, qkv.dtype, "out", 2)
+    _need(k_cache, qkv.dtype, "k_cache", 4); _need(v_cache, qkv.dtype, "v_cache", 4)
+    _need(block_table, torch.int32, "block_table", 2)
+    _need(req_index, torch.int32, "req_index", 1); _need(positions, torch.int32, "positions", 1)
+    _need(part_acc, torch.float32, "part_acc"); _need(part_ml, torch.float32, "part_ml")
+    T = qkv.shape[0]
+    if out.shape != (T, num_heads * head_dim) or req_index.shape[0] != T or positions.shape[0] != T:
+        raise KernelError("decode_attention: token counts or widths disagree")
+    if k_cache.shape != v_cache.shape or k_cache.shape[1] != num_kv_heads or k_cache.shape[3] != head_dim:
+        raise KernelError(f"cache {tuple(k_cache.shape)} does not match kv heads {num_kv_heads} x {head_dim}")
+    S, need_acc, need_ml = decode_attention_scratch(T, num_heads, head_dim, max_context, chunk)
+    if part_acc.numel() < need_acc or part_ml.numel() < need_ml:
+        raise KernelError(f"decode_attention: scratch too small ({part_acc.numel()} < {need_acc})")
+    _check(_fn("attention", "vl_decode_attention")(
+        _ptr(qkv), qkv.shape[1], _ptr(out), dtype_code(qkv.dtype), _ptr(k_cache), _ptr(v_cache),
+        _ptr(block_table), block_table.shape[1], _ptr(req_index), _ptr(positions),
+        T, num_heads, num_kv_heads, head_dim, k_cache.shape[2], k_cache.shape[0],
+        float(scale), int(window or 0), chunk, S, _ptr(part_acc), _ptr(part_ml), _ptr(err), _stream()),
+        "vl_decode_attention")
+    global launch_count
+    launch_count += 1           # two kernels: the split pass and the merge
     return out
 
 

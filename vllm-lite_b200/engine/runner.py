@@ -117,7 +117,7 @@ class ModelRunner:
 
     def _forward_graph(self, batch: StepBatch) -> torch.Tensor:
         """Rows of padded requests come after the real ones, so the caller slices them off."""
-        key = (batch.graph_bucket, len(batch.logit_rows))
+        key = (batch.graph_bucket, batch.groups[0].max_context if batch.groups else 0)
         entry = self._graphs.get(key)
         if entry is None:
             # first sight of this bucket: run it as it is (also sizes the workspace), then record
@@ -241,16 +241,21 @@ class ModelRunner:
             o, n = off[name]
             return dev[o:o + n]
         groups = []
+        longest = max(h.start + h.count for h in host_entries)
+        if bucket:                       # a graph is recorded for a bound on the context, not for its value
+            bound = 1024
+            while bound < longest:
+                bound *= 2
+            longest = min(bound, self.max_context)
         for g in range(G):
             groups.append(GroupView(page_size=ps, block_table=dview(f"table{g}").view(B, max_blocks[g]),
-                                    slots=dview(f"slots{g}"),
-                                    max_context=max(h.start + h.count for h in host_entries)))
+                                    slots=dview(f"slots{g}"), max_context=longest))
         return StepBatch(tokens=dview("tokens"), positions=dview("positions"), req_index=dview("req_index"),
                          cu_seqlens=dview("cu_seqlens"), state_slots=dview("state_slots"),
                          logit_rows=dview("logit_rows"), groups=groups, entries=host_entries, err=self.err,
                          workspace=self.workspace, num_tokens=T, num_entries=B,
                          max_query_len=max(h.count for h in host_entries),
-                         tag=f"g{bucket}." if bucket else "", graph_bucket=bucket)
+                         tag=f"g{bucket}.{longest}." if bucket else "", graph_bucket=bucket)
 
     def _upload(self, meta: np.ndarray, bucket: int = 0) -> torch.Tensor:
         n = meta.shape[0]
