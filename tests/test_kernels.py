@@ -94,6 +94,26 @@ def test_gemm_f32_is_true_float32_and_batch_invariant(M, N, K):
     assert torch.equal(one[0], out[M - 1])                            # a row alone == the row in the batch
 
 
+@pytest.mark.parametrize("out_dtype", [torch.bfloat16, torch.float32])
+@pytest.mark.parametrize("M,N,K", [(1, 333, 96), (8, 6144, 4096), (9, 50, 200), (33, 1000, 264), (64, 160, 4096),
+                                   (5, 17, 8), (16, 4096, 12288)])
+def test_gemm_bf16_small_m(M, N, K, out_dtype):
+    torch.manual_seed(M * N)
+    a = torch.randn(M, K, device=DEV).to(torch.bfloat16)
+    w = (torch.randn(N, K, device=DEV) * 0.05).to(torch.bfloat16)
+    out = torch.full((M, N), float("nan"), device=DEV, dtype=out_dtype)
+    ops().gemm_bf16_small_m(a, w, out)
+    ref = a.double() @ w.double().T
+    scale = float(ref.abs().max())
+    if out_dtype == torch.float32:                        # exact products, float32 sums
+        assert float((out.double() - ref).abs().max()) <= 1e-5 * scale * (K ** 0.5)
+    else:
+        assert float((out.double() - ref).abs().max()) <= 2 ** -8 * scale + 1e-6
+    one = torch.empty(1, N, device=DEV, dtype=out_dtype)
+    ops().gemm_bf16_small_m(a[M - 1:].contiguous(), w, one)
+    assert torch.equal(one[0], out[M - 1])                # a row alone == the row among others
+
+
 def plain_head_norm_rope(x, w, eps, pos, theta, rot):
     """x [T, heads, hd] -> norm over hd, then rotate the first `rot` features."""
     y = P.rms_norm(x, w, eps) if w is not None else x

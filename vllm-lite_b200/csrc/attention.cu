@@ -213,6 +213,42 @@ template <typename T> __device__ __forceinline__ float att_exp(float x);
 template <> __device__ __forceinline__ float att_exp<float>(float x) { return expf(x); }
 template <> __device__ __forceinline__ float att_exp<bf16>(float x) { return __expf(x); }
 
+// ---- asynchronous bulk copies (TMA, untiled) with mbarrier completion -----------------------
+__device__ __forceinline__ unsigned smem_u32(const void* p) { return (unsigned)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ void mbar_init(unsigned long long* bar, unsigned count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
+}
+__device__ __forceinline__ void mbar_fence_init() { asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory"); }
+__device__ __forceinline__ void mbar_arrive_expect_tx(unsigned long long* bar, unsigned bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(unsigned long long* bar, unsigned parity) {
+    unsigned ok;
+    asm volatile(
+        "{\n .reg .pred p;\n mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n selp.u32 %0, 1, 0, p;\n}"
+        : "=r"(ok) : "r"(smem_u32(bar)), "r"(parity) : "memory");
+    return ok != 0;
+}
+// Both addresses 16-byte aligned, bytes a multiple of 16.
+__device__ __forceinline__ void bulk_copy_g2s(void* dst, const void* src, unsigned bytes, unsigned long long* bar) {
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                 ::"r"(smem_u32(dst)), "l"(src), "r"(bytes), "r"(smem_u32(bar)) : "memory");
+}
+// A wait gives up after this many polls (a fraction of a second): the block then records
+// VL_DEV_WAIT_EXPIRED and leaves instead of hanging the device.
+#define MBAR_SPIN_LIMIT (1 << 22)
+__device__ __forceinline__ bool mbar_wait_bounded(unsigned long long* bar, unsigned parity) {
+    for (int i = 0; i < MBAR_SPIN_LIMIT; ++i)
+        if (mbar_try_wait(bar, parity)) return true;
+    return false;
+}
+
+#define DEC_STAGE_KEYS 32
+#define DEC_MAX_STAGES 4
+
+// Keys and values of DEC_STAGE_KEYS consecutive positions are one stage of a ring in shared
+// memory, filled by bulk copies of the page pieces that cover them (a page piece of one KV head
+// is contiguous: rows x head_dim).  Thread 0 issues the copies; everybody consumes.
 template <typename T, int NPASS, int GT>
 __global__ void __launch_bounds__(DEC_THREADS)
 decode_attention_split_kernel(const T* __restrict__ q, int q_stride,
@@ -220,11 +256,13 @@ decode_attention_split_kernel(const T* __restrict__ q, int q_stride,
                               const int* __restrict__ block_table, int max_blocks,
                               const int* __restrict__ req_index, const int* __restrict__ positions,
                               int nq, int nkv, int hd, int page_size, int num_pages, float scale, int window,
-                              int chunk, int S, float* __restrict__ part_acc, float* __restrict__ part_ml,
-                              unsigned* err) {
+                              int chunk, int S, int nstages, float* __restrict__ part_acc,
+                              float* __restrict__ part_ml, unsigned* err) {
     constexpr int EPV = Vec16<T>::N;
+    extern __shared__ __align__(128) unsigned char dec_smem[];
     __shared__ float s_acc[DEC_THREADS / 32][GT][ATT_MAX_HD];
     __shared__ float s_m[DEC_THREADS / 32][GT], s_l[DEC_THREADS / 32][GT];
+    __shared__ __align__(8) unsigned long long full_bar[DEC_MAX_STAGES];
     const int split = blockIdx.x, t = blockIdx.z;
     const int g = nq / nkv;
     const int tiles = (g + GT - 1) / GT;
@@ -240,6 +278,48 @@ decode_attention_split_kernel(const T* __restrict__ q, int q_stride,
     const int tid = threadIdx.x, gi = tid >> 3, l = tid & 7, warp = tid >> 5;
     const int nvec = hd / EPV;                           // 16-byte pieces per row
     const int* table = block_table + (size_t)req_index[t] * max_blocks;
+    const size_t tile_elems = (size_t)DEC_STAGE_KEYS * hd;         // one of K or V of a stage
+    T* ring = reinterpret_cast<T*>(dec_smem);
+
+    const int st0 = c0 / DEC_STAGE_KEYS, st1 = (c1 - 1) / DEC_STAGE_KEYS;
+    if (tid == 0) {
+        for (int i = 0; i < nstages; ++i) mbar_init(&full_bar[i], 1);
+        mbar_fence_init();
+    }
+    __syncthreads();
+
+    // thread 0: fill ring slot `buf` with the keys/values of stage `st`
+    auto issue = [&](int st, int buf) {
+        const int first = st * DEC_STAGE_KEYS;
+        const int last = min(first + DEC_STAGE_KEYS, pos + 1);           // positions beyond pos are never read
+        unsigned total = 0;
+        for (int p0 = first; p0 < last;) {
+            const int blk = p0 / page_size;
+            const int end = min(last, (blk + 1) * page_size);
+            const int page = blk < max_blocks ? table[blk] : -1;
+            if (page >= 0 && page < num_pages) total += 2u * (unsigned)((end - p0) * hd * (int)sizeof(T));
+            p0 = end;
+        }
+        mbar_arrive_expect_tx(&full_bar[buf], total);
+        T* kdst = ring + (size_t)buf * 2 * tile_elems;
+        T* vdst = kdst + tile_elems;
+        for (int p0 = first; p0 < last;) {
+            const int blk = p0 / page_size;
+            const int end = min(last, (blk + 1) * page_size);
+            const int page = blk < max_blocks ? table[blk] : -1;
+            if (page >= 0 && page < num_pages) {
+                const size_t src = (((size_t)page * nkv + kvh) * page_size + (p0 - blk * page_size)) * hd;
+                const unsigned bytes = (unsigned)((end - p0) * hd * (int)sizeof(T));
+                bulk_copy_g2s(kdst + (size_t)(p0 - first) * hd, kcache + src, bytes, &full_bar[buf]);
+                bulk_copy_g2s(vdst + (size_t)(p0 - first) * hd, vcache + src, bytes, &full_bar[buf]);
+            } else {
+                atomicOr(err, VL_DEV_BAD_PAGE);
+            }
+            p0 = end;
+        }
+    };
+    if (tid == 0)
+        for (int i = 0; i < nstages && st0 + i <= st1; ++i) issue(st0 + i, i);
 
     float qv[GT][NPASS][EPV], acc[GT][NPASS][EPV], m[GT], lsum[GT];
 #pragma unroll
@@ -254,58 +334,68 @@ decode_attention_split_kernel(const T* __restrict__ q, int q_stride,
             for (int i = 0; i < EPV; ++i) { qv[hh][p][i] = v.get(i) * scale; acc[hh][p][i] = 0.f; }
         }
     }
-    for (int jb = (c0 / ATT_GROUPS) * ATT_GROUPS; jb < c1; jb += ATT_GROUPS) {
-        const int j = jb + gi;
-        bool valid = (j >= c0) && (j < c1);
-        size_t base = 0;
-        if (valid) {
-            const int blk = j / page_size;
-            const int page = blk < max_blocks ? table[blk] : -1;
-            if (page < 0 || page >= num_pages) {
-                if (l == 0) atomicOr(err, VL_DEV_BAD_PAGE);
-                valid = false;
-            } else {
-                base = (((size_t)page * nkv + kvh) * page_size + (j - blk * page_size)) * hd;
+    for (int st = st0; st <= st1; ++st) {
+        const int it = st - st0;
+        const int buf = it % nstages;
+        const bool arrived = mbar_wait_bounded(&full_bar[buf], (unsigned)((it / nstages) & 1));
+        if (__syncthreads_or(!arrived)) {                 // the copy never came: flag it and leave
+            if (tid == 0) {
+                atomicOr(err, VL_DEV_WAIT_EXPIRED);
+                // give the copies that are still in flight a bounded time to land before the block's
+                // shared memory is handed to another block
+                for (int k = 1; k < nstages && st + k <= st1; ++k)
+                    mbar_wait_bounded(&full_bar[(it + k) % nstages], (unsigned)(((it + k) / nstages) & 1));
             }
+            return;
         }
-        Vec16<T> kr[NPASS], vr[NPASS];
+        const T* kt = ring + (size_t)buf * 2 * tile_elems;
+        const T* vt = kt + tile_elems;
 #pragma unroll
-        for (int p = 0; p < NPASS; ++p) {
-            kr[p].zero(); vr[p].zero();
-            const int c = l + 8 * p;
-            if (valid && c < nvec) {
-                kr[p].load(kcache + base + c * EPV);
-                vr[p].load(vcache + base + c * EPV);
+        for (int half = 0; half < DEC_STAGE_KEYS / ATT_GROUPS; ++half) {
+            const int r = half * ATT_GROUPS + gi;          // row of the stage
+            const int j = st * DEC_STAGE_KEYS + r;
+            const bool valid = (j >= c0) && (j < c1);
+            Vec16<T> kr[NPASS], vr[NPASS];
+#pragma unroll
+            for (int p = 0; p < NPASS; ++p) {
+                kr[p].zero(); vr[p].zero();
+                const int c = l + 8 * p;
+                if (valid && c < nvec) {
+                    kr[p].load(kt + (size_t)r * hd + c * EPV);
+                    vr[p].load(vt + (size_t)r * hd + c * EPV);
+                }
             }
-        }
-        float dot[GT];
-#pragma unroll
-        for (int hh = 0; hh < GT; ++hh) {
-            float d = 0.f;
-#pragma unroll
-            for (int p = 0; p < NPASS; ++p)
-#pragma unroll
-                for (int i = 0; i < EPV; ++i) d = fmaf(qv[hh][p][i], kr[p].get(i), d);
-            d += __shfl_xor_sync(0xffffffffu, d, 4);
-            d += __shfl_xor_sync(0xffffffffu, d, 2);
-            d += __shfl_xor_sync(0xffffffffu, d, 1);
-            dot[hh] = d;
-        }
-        if (valid) {
+            float dot[GT];
 #pragma unroll
             for (int hh = 0; hh < GT; ++hh) {
-                const float s = dot[hh];
-                const float mn = fmaxf(m[hh], s);
-                const float corr = att_exp<T>(m[hh] - mn);
-                const float pr = att_exp<T>(s - mn);
-                lsum[hh] = lsum[hh] * corr + pr;
-                m[hh] = mn;
+                float d = 0.f;
 #pragma unroll
                 for (int p = 0; p < NPASS; ++p)
 #pragma unroll
-                    for (int i = 0; i < EPV; ++i) acc[hh][p][i] = fmaf(pr, vr[p].get(i), acc[hh][p][i] * corr);
+                    for (int i = 0; i < EPV; ++i) d = fmaf(qv[hh][p][i], kr[p].get(i), d);
+                d += __shfl_xor_sync(0xffffffffu, d, 4);
+                d += __shfl_xor_sync(0xffffffffu, d, 2);
+                d += __shfl_xor_sync(0xffffffffu, d, 1);
+                dot[hh] = d;
+            }
+            if (valid) {
+#pragma unroll
+                for (int hh = 0; hh < GT; ++hh) {
+                    const float sc = dot[hh];
+                    const float mn = fmaxf(m[hh], sc);
+                    const float corr = att_exp<T>(m[hh] - mn);
+                    const float pr = att_exp<T>(sc - mn);
+                    lsum[hh] = lsum[hh] * corr + pr;
+                    m[hh] = mn;
+#pragma unroll
+                    for (int p = 0; p < NPASS; ++p)
+#pragma unroll
+                        for (int i = 0; i < EPV; ++i) acc[hh][p][i] = fmaf(pr, vr[p].get(i), acc[hh][p][i] * corr);
+                }
             }
         }
+        __syncthreads();                                   // everybody is done with this slot
+        if (tid == 0 && st + nstages <= st1) issue(st + nstages, buf);
     }
     // merge the 4 groups of a warp (lanes l, l+8, l+16, l+24 hold the same pieces)
 #pragma unroll
@@ -396,12 +486,20 @@ static int launch_decode_split(int GT, dim3 grid, cudaStream_t s, const T* q, in
                                const int* bt, int max_blocks, const int* req, const int* pos, int nq, int nkv, int hd,
                                int page_size, int num_pages, float scale, int window, int chunk, int S,
                                float* pacc, float* pml, unsigned* err) {
+    const size_t stage_bytes = 2 * (size_t)DEC_STAGE_KEYS * hd * sizeof(T);
+    int nstages = (int)((96 * 1024) / stage_bytes);
+    nstages = nstages > DEC_MAX_STAGES ? DEC_MAX_STAGES : (nstages < 2 ? 2 : nstages);
+    const size_t smem = stage_bytes * nstages;
 #define DEC_CASE(G)                                                                                        \
-    case G:                                                                                                \
-        decode_attention_split_kernel<T, NPASS, G><<<grid, DEC_THREADS, 0, s>>>(                           \
-            q, q_stride, kc, vc, bt, max_blocks, req, pos, nq, nkv, hd, page_size, num_pages, scale,       \
-            window, chunk, S, pacc, pml, err);                                                             \
-        break;
+    case G: {                                                                                              \
+        auto kern = decode_attention_split_kernel<T, NPASS, G>;                                            \
+        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
+        if (e != cudaSuccess) return (int)e;                                                               \
+        kern<<<grid, DEC_THREADS, smem, s>>>(q, q_stride, kc, vc, bt, max_blocks, req, pos, nq, nkv, hd,   \
+                                             page_size, num_pages, scale, window, chunk, S, nstages, pacc, \
+                                             pml, err);                                                    \
+        break;                                                                                             \
+    }
     switch (GT) { DEC_CASE(1) DEC_CASE(2) DEC_CASE(4) default: return VL_ERR_UNSUPPORTED; }
 #undef DEC_CASE
     return vl_launch_status();

@@ -24,7 +24,7 @@ CSRC = Path(__file__).resolve().parent
 ARCH_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a"]
 NVCC_FLAGS = ARCH_FLAGS + ["-O3", "-lineinfo", "-std=c++17", "--shared", "-Xcompiler", "-fPIC"]
 SOURCES = ("embed_norm", "rope_cache", "attention", "activation", "gemm_f32", "gemm_bf16", "sampling")
-EXTRA_LIBS = {"gemm_bf16": ["-lcuda"]}
+EXTRA_LIBS = {}
 
 _loaded = {}
 _lock = threading.Lock()

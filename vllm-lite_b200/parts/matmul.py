@@ -1,8 +1,8 @@
 """bfloat16 matrix product out[M, N] = a[M, K] @ w[N, K]^T with float32 accumulation.
 
-The reference hands its matrix products to its tensor library's GEMM, and so
-does this file for now: the library product (cuBLAS through torch) is the
-stand-in until the engine's own tensor-core kernel takes a shape.
+Few rows (a decode step) go to the engine's weight-streaming tensor-core kernel.
+Many rows go to the library product (cuBLAS through torch): the reference hands
+its matrix products to its tensor library's GEMM in the same way.
 """
 from __future__ import annotations
 
@@ -10,7 +10,10 @@ import torch
 
 
 def gemm_bf16(a, w, out):
+    from ..csrc import ops
+    M, K = a.shape
+    if ops.gemm_bf16_small_m_ok(M, K):
+        return ops.gemm_bf16_small_m(a, w, out)
     if out.dtype == torch.bfloat16:
         return torch.mm(a, w.t(), out=out)
-    # float32 result from bfloat16 operands (the logits)
-    return torch.mm(a, w.t(), out_dtype=torch.float32, out=out)
+    return torch.mm(a, w.t(), out_dtype=torch.float32, out=out)      # float32 logits from bfloat16 operands
