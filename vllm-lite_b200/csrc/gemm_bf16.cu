@@ -3,17 +3,18 @@
 //
 // vl_gemm_bf16_small_m: for the few rows of a decode step (M <= 64).  The product is bound by
 // reading W once from HBM, so the kernel is built around that stream: a block owns 16 rows of W,
-// its 4 warps take the 32-wide slices of K in turn, every lane reads 16 contiguous bytes of two
+// its 8 warps take the 32-wide slices of K in turn, every lane reads 16 contiguous bytes of two
 // rows of W and of one row of A per slice, and the tensor cores multiply them
 // (mma.sync m16n8k16, W as the 16-row operand, 8 rows of A as the other).  The instruction pairs
 // operand elements by their index along K and never mixes rows, so the 8 values a lane holds may
 // stand for any 8 of the 16 positions of a slice as long as both operands use the same
-// assignment; that is what lets each lane load whole 16-byte pieces.  The 4 warps' partial sums
+// assignment; that is what lets each lane load whole 16-byte pieces.  The 8 warps' partial sums
 // are added in warp order, so the result does not depend on the launch.
 // K must be a multiple of 8 (16-byte rows); any M <= 64 and any N.
 #include "common.cuh"
 
-#define GS_THREADS 128
+#define GS_THREADS 256
+#define GS_WARPS (GS_THREADS / 32)
 #define GS_ROWS 16
 
 __device__ __forceinline__ uint4 ldg_stream16(const void* p) {
@@ -48,13 +49,13 @@ gemm_bf16_small_m_kernel(const bf16* __restrict__ A, const bf16* __restrict__ W,
         for (int i = 0; i < 4; ++i) acc[j][i] = 0.f;
     const uint4 zero = make_uint4(0, 0, 0, 0);
     const int steps = (K + 31) / 32;
-    constexpr int UNROLL = MT >= 4 ? 2 : 4;
-    for (int s0 = warp; s0 < steps; s0 += 4 * UNROLL) {
+    constexpr int UNROLL = MT == 1 ? 8 : (MT == 2 ? 4 : 2);
+    for (int s0 = warp; s0 < steps; s0 += GS_WARPS * UNROLL) {
         uint4 wl[UNROLL], wh[UNROLL], av[UNROLL][MT];
 #pragma unroll
         for (int u = 0; u < UNROLL; ++u) {
-            const int k = (s0 + 4 * u) * 32 + 8 * t;
-            const bool in = (s0 + 4 * u) < steps && k < K;
+            const int k = (s0 + GS_WARPS * u) * 32 + 8 * t;
+            const bool in = (s0 + GS_WARPS * u) < steps && k < K;
             wl[u] = (in && ok_lo) ? ldg_stream16(w_lo + k) : zero;
             wh[u] = (in && ok_hi) ? ldg_stream16(w_hi + k) : zero;
 #pragma unroll

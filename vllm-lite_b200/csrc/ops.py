@@ -263,7 +263,7 @@ def gemm_f32(a, w, out):
     return out
 
 
-SMALL_M = 64              # most rows the weight-streaming product takes
+SMALL_M = 16              # most rows the weight-streaming product is used for (the kernel takes up to 64)
 
 
 def gemm_bf16_small_m_ok(M, K) -> bool:
