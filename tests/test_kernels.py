@@ -192,10 +192,10 @@ def build_paged(seqs_kv, nkv, hd, page, dtype, shuffle_seed=0):
     return kc.to(DEV), vc.to(DEV), table.to(DEV)
 
 
-@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("kernel,dtype", [("paged", torch.float32), ("paged", torch.bfloat16), ("flash", torch.bfloat16)])
 @pytest.mark.parametrize("nq,nkv,hd,page,window", [(6, 2, 48, 4, 0), (5, 5, 16, 16, 0), (8, 1, 128, 16, 0),
                                                    (3, 1, 80, 8, 37), (4, 2, 256, 32, 0)])
-def test_paged_attention_ragged(dtype, nq, nkv, hd, page, window):
+def test_paged_attention_ragged(kernel, dtype, nq, nkv, hd, page, window):
     """A batch of a prompt portion, a continuation and two single tokens, pages shuffled."""
     torch.manual_seed(nq * 100 + hd)
     lens = [45, 130, 1, 77]                      # keys present per request
@@ -214,8 +214,17 @@ def test_paged_attention_ragged(dtype, nq, nkv, hd, page, window):
     out = torch.empty(T, nq * hd, device=DEV, dtype=dtype)
     e = err_word()
     scale = hd ** -0.5
-    ops().paged_attention(qkv, out, kc, vc, table, torch.tensor(req, dtype=torch.int32, device=DEV),
-                          torch.tensor(pos, dtype=torch.int32, device=DEV), nq, nkv, hd, scale, window, e)
+    if kernel == "flash":                       # tiles of up to 64 tokens per request, as the engine cuts them
+        tiles, t0 = [], 0
+        for b, (n, c) in enumerate(zip(lens, new)):
+            for lo_ in range(0, c, 64):
+                tiles.append([b, t0 + lo_, min(64, c - lo_), n - c + lo_])
+            t0 += c
+        ops().flash_prefill(qkv, out, kc, vc, table, torch.tensor(tiles, dtype=torch.int32, device=DEV),
+                            nq, nkv, hd, scale, window, e)
+    else:
+        ops().paged_attention(qkv, out, kc, vc, table, torch.tensor(req, dtype=torch.int32, device=DEV),
+                              torch.tensor(pos, dtype=torch.int32, device=DEV), nq, nkv, hd, scale, window, e)
     assert int(e.item()) == 0
     qd = qkv[:, :nq * hd].float().cpu().view(T, nq, hd)
     for t in range(T):
@@ -227,17 +236,29 @@ def test_paged_attention_ragged(dtype, nq, nkv, hd, page, window):
 def run_attention(kernel, qkv, out, kc, vc, table, req, pos, nq, nkv, hd, scale, window, e):
     if kernel == "paged":
         return ops().paged_attention(qkv, out, kc, vc, table, req, pos, nq, nkv, hd, scale, window, e)
+    if kernel == "flash_prefill":          # every token a tile of its own
+        tiles = torch.tensor([[int(req[i]), i, 1, int(pos[i])] for i in range(qkv.shape[0]) if int(pos[i]) >= 0],
+                             dtype=torch.int32, device=DEV)
+        return ops().flash_prefill(qkv, out, kc, vc, table, tiles, nq, nkv, hd, scale, window, e)
     ctx = int(pos.max()) + 1
     S, n_acc, n_ml = ops().decode_attention_scratch(qkv.shape[0], nq, hd, ctx)
     pa = torch.full((n_acc,), float("nan"), device=DEV)
     pm = torch.full((n_ml,), float("nan"), device=DEV)
-    return ops().decode_attention(qkv, out, kc, vc, table, req, pos, nq, nkv, hd, scale, window, ctx, pa, pm, e)
+    fn = ops().flash_decode if kernel == "flash_decode" else ops().decode_attention
+    return fn(qkv, out, kc, vc, table, req, pos, nq, nkv, hd, scale, window, ctx, pa, pm, e)
 
 
-@pytest.mark.parametrize("dtype", DTYPES)
+def attention_cases():
+    """(kernel, dtype): the tensor-core kernels exist in bfloat16 only."""
+    return [("paged", torch.float32), ("paged", torch.bfloat16), ("decode", torch.float32), ("decode", torch.bfloat16),
+            ("flash_decode", torch.bfloat16), ("flash_prefill", torch.bfloat16)]
+
+
+@pytest.mark.parametrize("kernel,dtype", [c for c in attention_cases() if c[0] != "paged"])
 @pytest.mark.parametrize("nq,nkv,hd,page,window", [(6, 2, 48, 4, 0), (5, 5, 16, 16, 0), (32, 8, 128, 16, 0),
-                                                   (3, 1, 80, 8, 300), (16, 2, 256, 32, 0), (7, 1, 64, 16, 0)])
-def test_decode_attention_split(dtype, nq, nkv, hd, page, window):
+                                                   (3, 1, 80, 8, 300), (16, 2, 256, 32, 0), (7, 1, 64, 16, 0),
+                                                   (40, 2, 32, 16, 0)])
+def test_decode_attention_split(kernel, dtype, nq, nkv, hd, page, window):
     """Single tokens of requests of very different lengths (one token, a chunk's edge, several
     chunks), pages shuffled; a padded token at position -1 yields zeros."""
     torch.manual_seed(nq * 10 + hd)
@@ -253,19 +274,20 @@ def test_decode_attention_split(dtype, nq, nkv, hd, page, window):
     out = torch.full((T, nq * hd), 5.0, device=DEV, dtype=dtype)
     e = err_word()
     scale = hd ** -0.5
-    run_attention("decode", qkv, out, kc, vc, table, req, pos, nq, nkv, hd, scale, window, e)
+    run_attention(kernel, qkv, out, kc, vc, table, req, pos, nq, nkv, hd, scale, window, e)
     assert int(e.item()) == 0
     qd = qkv[:, :nq * hd].float().cpu().view(T, nq, hd)
     for t, n in enumerate(lens):
         k, v = seqs[t]
         ref = paged_reference(qd[t], k.to(dtype).float(), v.to(dtype).float(), n - 1, scale, window)
         assert torch.allclose(out[t].float().cpu().view(nq, hd), ref, **tol(dtype)), (t, n)
-    assert bool((out[T - 1] == 0).all())
+    if kernel != "flash_prefill":
+        assert bool((out[T - 1] == 0).all())
 
 
-@pytest.mark.parametrize("kernel", ["paged", "decode"])
-@pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("far,window", [(3, 0), (640, 0), (15, 0), (16, 0), (255, 0), (256, 0), (700, 300), (699, 300)])
+@pytest.mark.parametrize("kernel,dtype", attention_cases())
+@pytest.mark.parametrize("far,window", [(3, 0), (640, 0), (15, 0), (16, 0), (63, 0), (64, 0), (255, 0), (256, 0),
+                                        (700, 300), (699, 300)])
 def test_attention_finds_one_far_key(kernel, dtype, far, window):
     """One key among a thousand is made to stand out by scaling it and the query; the
     output must be that key's value (or, when the window excludes it, must not be)."""

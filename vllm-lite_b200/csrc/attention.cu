@@ -292,12 +292,13 @@ decode_attention_split_kernel(const T* __restrict__ q, int q_stride,
     auto issue = [&](int st, int buf) {
         const int first = st * DEC_STAGE_KEYS;
         const int last = min(first + DEC_STAGE_KEYS, pos + 1);           // positions beyond pos are never read
+        const int need = (c0 / page_size) * page_size;                   // pages wholly below the range may be gone
         unsigned total = 0;
         for (int p0 = first; p0 < last;) {
             const int blk = p0 / page_size;
             const int end = min(last, (blk + 1) * page_size);
             const int page = blk < max_blocks ? table[blk] : -1;
-            if (page >= 0 && page < num_pages) total += 2u * (unsigned)((end - p0) * hd * (int)sizeof(T));
+            if (end > need && page >= 0 && page < num_pages) total += 2u * (unsigned)((end - p0) * hd * (int)sizeof(T));
             p0 = end;
         }
         mbar_arrive_expect_tx(&full_bar[buf], total);
@@ -307,7 +308,9 @@ decode_attention_split_kernel(const T* __restrict__ q, int q_stride,
             const int blk = p0 / page_size;
             const int end = min(last, (blk + 1) * page_size);
             const int page = blk < max_blocks ? table[blk] : -1;
-            if (page >= 0 && page < num_pages) {
+            if (end <= need) {
+                // below the range: nothing to fetch
+            } else if (page >= 0 && page < num_pages) {
                 const size_t src = (((size_t)page * nkv + kvh) * page_size + (p0 - blk * page_size)) * hd;
                 const unsigned bytes = (unsigned)((end - p0) * hd * (int)sizeof(T));
                 bulk_copy_g2s(kdst + (size_t)(p0 - first) * hd, kcache + src, bytes, &full_bar[buf]);
@@ -537,6 +540,20 @@ static int decode_attention_typed(const T* q, int q_stride, T* out, const T* kc,
 #undef DEC_PASS
     if (rc != 0) return rc;
     decode_attention_merge_kernel<T><<<dim3(T_, nq), 128, 0, s>>>(pacc, pml, pos, out, nq, hd, chunk, S, window);
+    return vl_launch_status();
+}
+
+// Merges per-chunk partial results (of vl_decode_attention's first pass or of vl_flash_decode).
+extern "C" int vl_decode_attention_merge(const float* part_acc, const float* part_ml, const int* positions, void* out,
+                                         int dtype, int T, int nq, int hd, int chunk, int S, int window, void* stream) {
+    if (T <= 0) return VL_OK;
+    cudaStream_t s = (cudaStream_t)stream;
+    if (dtype == VL_F32)
+        decode_attention_merge_kernel<float><<<dim3(T, nq), 128, 0, s>>>(part_acc, part_ml, positions, (float*)out, nq, hd, chunk, S, window);
+    else if (dtype == VL_BF16)
+        decode_attention_merge_kernel<bf16><<<dim3(T, nq), 128, 0, s>>>(part_acc, part_ml, positions, (bf16*)out, nq, hd, chunk, S, window);
+    else
+        return VL_ERR_UNSUPPORTED;
     return vl_launch_status();
 }
 

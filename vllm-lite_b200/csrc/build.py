@@ -24,6 +24,9 @@ CSRC = Path(__file__).resolve().parent
 ARCH_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a"]
 NVCC_FLAGS = ARCH_FLAGS + ["-O3", "-lineinfo", "-std=c++17", "--shared", "-Xcompiler", "-fPIC"]
 SOURCES = ("embed_norm", "rope_cache", "attention", "activation", "gemm_f32", "gemm_bf16", "sampling")
+# sources compiled once per value of a constant; the values here are what build_all() prepares,
+# any other allowed value is compiled when a model first needs it
+VARIANTS = {"flash_attn": [{"FA_HD": 128}, {"FA_HD": 64}, {"FA_HD": 32}, {"FA_HD": 16}]}
 EXTRA_LIBS = {}
 
 _loaded = {}
@@ -48,12 +51,18 @@ def find_nvcc() -> str:
                      "the engine has no path without its CUDA libraries")
 
 
-def _digest(name: str) -> str:
+def _variant(defines) -> str:
+    """Part of a library's file name that tells its compile-time constants, e.g. 'FA_HD128'."""
+    return "_".join(f"{k}{v}" for k, v in sorted((defines or {}).items()))
+
+
+def _digest(name: str, defines=None) -> str:
     h = hashlib.sha256()
     h.update((CSRC / f"{name}.cu").read_bytes())
     for header in sorted(CSRC.glob("*.cuh")):
         h.update(header.read_bytes())
     h.update(" ".join(NVCC_FLAGS + EXTRA_LIBS.get(name, [])).encode())
+    h.update(_variant(defines).encode())
     return h.hexdigest()[:12]
 
 
@@ -62,11 +71,13 @@ def _build_dirs():
     yield Path(tempfile.gettempdir()) / f"vllm_lite_b200_build_{os.getuid()}"
 
 
-def library_path(name: str) -> Path:
-    """Path of the up-to-date library of `name`, building it if it is absent."""
+def library_path(name: str, defines=None) -> Path:
+    """Path of the up-to-date library of `name` (compiled with -D<key>=<value> for `defines`),
+    building it if it is absent."""
     if not (CSRC / f"{name}.cu").is_file():
         raise BuildError(f"no CUDA source {name}.cu under {CSRC}")
-    fname = f"{name}.{_digest(name)}.so"
+    stem = name + ("." + _variant(defines) if defines else "")
+    fname = f"{stem}.{_digest(name, defines)}.so"
     for d in _build_dirs():
         if (d / fname).is_file():
             return d / fname
@@ -76,7 +87,7 @@ def library_path(name: str) -> Path:
             d.mkdir(parents=True, exist_ok=True)
             if not os.access(d, os.W_OK):
                 continue
-            return _compile(name, d / fname)
+            return _compile(name, d / fname, stem, defines)
         except (OSError, BuildError) as e:   # try the next folder; report the last failure
             last = e
             if isinstance(e, BuildError) and "nvcc" in str(e) and "not found" in str(e):
@@ -84,11 +95,13 @@ def library_path(name: str) -> Path:
     raise BuildError(f"could not build {name}.cu: {last}")
 
 
-def _compile(name: str, out: Path) -> Path:
+def _compile(name: str, out: Path, stem: str, defines=None) -> Path:
     nvcc = find_nvcc()
     tmp = out.with_suffix(f".tmp{os.getpid()}.so")
-    cmd = [nvcc] + NVCC_FLAGS + ["-I", str(CSRC), "-o", str(tmp), str(CSRC / f"{name}.cu")] + EXTRA_LIBS.get(name, [])
-    _say(f"compiling {name}.cu for sm_100a ...")
+    dflags = [f"-D{k}={v}" for k, v in sorted((defines or {}).items())]
+    cmd = ([nvcc] + NVCC_FLAGS + dflags + ["-I", str(CSRC), "-o", str(tmp), str(CSRC / f"{name}.cu")]
+           + EXTRA_LIBS.get(name, []))
+    _say(f"compiling {name}.cu {' '.join(dflags)} for sm_100a ...".replace("  ", " "))
     t0 = time.time()
     proc = subprocess.Popen(cmd, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True,
                             env={**os.environ, "TMPDIR": tempfile.gettempdir()})
@@ -102,8 +115,8 @@ def _compile(name: str, out: Path) -> Path:
         tmp.unlink(missing_ok=True)
         raise BuildError(f"nvcc failed on {name}.cu:\n{log}")
     os.replace(tmp, out)
-    for stale in out.parent.glob(f"{name}.*.so"):          # libraries of earlier versions of this source
-        if stale != out and ".tmp" not in stale.name:
+    for stale in out.parent.glob(f"{stem}.*.so"):          # libraries of earlier versions of this source
+        if stale != out and ".tmp" not in stale.name and stale.name.count(".") == out.name.count("."):
             try:
                 stale.unlink()
             except OSError:
@@ -112,15 +125,20 @@ def _compile(name: str, out: Path) -> Path:
     return out
 
 
-def load(name: str) -> ctypes.CDLL:
+def load(name: str, defines=None) -> ctypes.CDLL:
+    key = (name, _variant(defines))
     with _lock:
-        lib = _loaded.get(name)
+        lib = _loaded.get(key)
         if lib is None:
-            lib = ctypes.CDLL(str(library_path(name)))
-            _loaded[name] = lib
+            lib = ctypes.CDLL(str(library_path(name, defines)))
+            _loaded[key] = lib
         return lib
 
 
 def build_all(names=SOURCES) -> dict:
     """Build every library (cross-compiles without a GPU).  Returns name -> path."""
-    return {n: library_path(n) for n in names if (CSRC / f"{n}.cu").is_file()}
+    out = {n: library_path(n) for n in names if (CSRC / f"{n}.cu").is_file()}
+    for n, variants in VARIANTS.items():
+        for d in variants:
+            out[f"{n}.{_variant(d)}"] = library_path(n, d)
+    return out

@@ -1,0 +1,434 @@
+// bfloat16 attention over the paged cache on the tensor cores (mma.sync m16n8k16, float32
+// accumulation), compiled for one head size: -DFA_HD=<head_dim>, a multiple of 16 up to 256.
+//
+// The function is that of csrc/attention.cu: a query at absolute position p of a request reads
+// the keys lo..p of that request from its pages (lo = 0 or p - window + 1),
+//     s_j = (q . k_j) * scale;  p = softmax_j(s);  o = sum_j p_j v_j,
+// query head h reads KV head h / (nq / nkv).  Scores, running maximum, sum and output are
+// float32; the probabilities are rounded to bfloat16 for the second product.
+//
+// vl_flash_prefill: a block owns up to 64 consecutive tokens of one request and one query head
+//   (4 warps x 16 rows) and walks that request's keys in tiles of 64, K and V tiles double
+//   buffered in shared memory by cp.async.  The host passes the list of token tiles.
+// vl_flash_decode: a block owns one token, one KV head with all its query heads as rows, and one
+//   chunk of `chunk` key positions; its 4 warps take 16 keys each of every 64-key tile and their
+//   partial results are merged in warp order.  The per-chunk partials go to the same scratch
+//   layout as vl_decode_attention's and are merged by vl_decode_attention_merge.
+// Rows of shared-memory tiles are padded by 16 bytes, which makes every 8-row ldmatrix access
+// hit 8 different banks groups for any head size.
+#include "common.cuh"
+
+#ifndef FA_HD
+#define FA_HD 128
+#endif
+
+namespace {
+constexpr int HD = FA_HD;
+constexpr int LDS = HD + 8;            // padded row length in elements
+constexpr int KSTEPS = HD / 16;        // k-steps of Q K^T
+constexpr int DTILES = HD / 8;         // n-tiles of the output
+constexpr int CPR = HD / 8;            // 16-byte chunks per row
+constexpr int BM = 64, BN = 64, NTHREADS = 128;
+static_assert(HD % 16 == 0 && HD >= 16 && HD <= 256, "head_dim must be a multiple of 16 up to 256");
+
+__device__ __forceinline__ unsigned smem_addr(const void* p) { return (unsigned)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ void cp_async16(void* dst, const void* src, bool valid) {
+    const int n = valid ? 16 : 0;      // 0 bytes read: the 16 bytes are filled with zeros
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(smem_addr(dst)), "l"(src), "r"(n) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N> __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
+
+__device__ __forceinline__ void ldmatrix_x4(unsigned (&r)[4], const void* p) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(smem_addr(p)));
+}
+__device__ __forceinline__ void ldmatrix_x4_trans(unsigned (&r)[4], const void* p) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(smem_addr(p)));
+}
+__device__ __forceinline__ void mma16816(float (&c)[4], const unsigned (&a)[4], unsigned b0, unsigned b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                 : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+                 : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ unsigned pack_bf16(float lo, float hi) {
+    __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<unsigned*>(&v);
+}
+
+// Copies the keys (or values) of positions [j0, j0 + rows) of one request and KV head into a
+// padded tile.  Positions outside [first, last] are filled with zeros and never looked up (their
+// pages may not exist, or may have been given back once a window passed them).
+__device__ __forceinline__ void load_kv_tile(bf16* tile, const bf16* cache, const int* table, int max_blocks,
+                                             int j0, int rows, int first, int last, int kvh, int nkv, int page_size,
+                                             int num_pages, unsigned* err) {
+    for (int idx = threadIdx.x; idx < rows * CPR; idx += NTHREADS) {
+        const int r = idx / CPR, c = idx - r * CPR;
+        const int j = j0 + r;
+        const bf16* src = cache;
+        bool valid = j >= first && j <= last;
+        if (valid) {
+            const int blk = j / page_size;
+            const int page = blk < max_blocks ? table[blk] : -1;
+            if (page < 0 || page >= num_pages) {
+                if (c == 0) atomicOr(err, VL_DEV_BAD_PAGE);
+                valid = false;
+            } else {
+                src = cache + (((size_t)page * nkv + kvh) * page_size + (j - blk * page_size)) * HD + c * 8;
+            }
+        }
+        cp_async16(tile + (size_t)r * LDS + c * 8, src, valid);
+    }
+}
+}  // namespace
+
+// tiles[i] = {row of the block table, index of the tile's first token in the step, tokens, position of the first}
+extern "C" __global__ void __launch_bounds__(NTHREADS)
+flash_prefill_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restrict__ out,
+                     const bf16* __restrict__ kcache, const bf16* __restrict__ vcache,
+                     const int* __restrict__ block_table, int max_blocks, const int4* __restrict__ tiles,
+                     int nq, int nkv, int page_size, int num_pages, float scale_log2, int window, unsigned* err) {
+    extern __shared__ __align__(128) unsigned char fa_smem[];
+    bf16* Qs = reinterpret_cast<bf16*>(fa_smem);                 // [BM][LDS]
+    bf16* Ks = Qs + BM * LDS;                                    // [2][BN][LDS]
+    bf16* Vs = Ks + 2 * BN * LDS;                                // [2][BN][LDS]
+    const int4 tile = tiles[blockIdx.x];
+    const int req = tile.x, tok0 = tile.y, count = tile.z, pos0 = tile.w;
+    const int h = blockIdx.y, kvh = h / (nq / nkv);
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, t = lane & 3;
+    const int* table = block_table + (size_t)req * max_blocks;
+    const int hi = pos0 + count - 1;                             // the last key any row reads
+    const int lo = (window > 0 && pos0 - window + 1 > 0) ? pos0 - window + 1 : 0;
+    const int kt_lo = lo / BN, kt_hi = hi / BN;
+
+    for (int idx = tid; idx < BM * CPR; idx += NTHREADS) {       // the query tile (rows beyond count: zeros)
+        const int r = idx / CPR, c = idx - r * CPR;
+        const bool valid = r < count;
+        const bf16* src = valid ? q + (size_t)(tok0 + r) * q_stride + (size_t)h * HD + c * 8 : q;
+        cp_async16(Qs + (size_t)r * LDS + c * 8, src, valid);
+    }
+    load_kv_tile(Ks, kcache, table, max_blocks, kt_lo * BN, BN, lo, hi, kvh, nkv, page_size, num_pages, err);
+    load_kv_tile(Vs, vcache, table, max_blocks, kt_lo * BN, BN, lo, hi, kvh, nkv, page_size, num_pages, err);
+    cp_async_commit();
+
+    float o[DTILES][4], m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};
+#pragma unroll
+    for (int d = 0; d < DTILES; ++d) { o[d][0] = o[d][1] = o[d][2] = o[d][3] = 0.f; }
+    unsigned qf[KSTEPS][4];
+    const int row0 = warp * 16;                                  // this warp's rows of the tile
+    const int pos_a = pos0 + row0 + g, pos_b = pos_a + 8;        // positions of the lane's two rows
+    const bool row_a = row0 + g < count, row_b = row0 + g + 8 < count;
+
+    for (int kt = kt_lo; kt <= kt_hi; ++kt) {
+        const int buf = (kt - kt_lo) & 1;
+        if (kt + 1 <= kt_hi) {
+            load_kv_tile(Ks + (buf ^ 1) * BN * LDS, kcache, table, max_blocks, (kt + 1) * BN, BN, lo, hi, kvh, nkv,
+                         page_size, num_pages, err);
+            load_kv_tile(Vs + (buf ^ 1) * BN * LDS, vcache, table, max_blocks, (kt + 1) * BN, BN, lo, hi, kvh, nkv,
+                         page_size, num_pages, err);
+            cp_async_commit();
+            cp_async_wait<1>();
+        } else {
+            cp_async_wait<0>();
+        }
+        __syncthreads();
+        if (kt == kt_lo) {
+#pragma unroll
+            for (int ks = 0; ks < KSTEPS; ++ks)
+                ldmatrix_x4(qf[ks], Qs + (size_t)(row0 + (lane & 7) + 8 * ((lane >> 3) & 1)) * LDS + ks * 16 + 8 * (lane >> 4));
+        }
+        const bf16* Kt = Ks + buf * BN * LDS;
+        const bf16* Vt = Vs + buf * BN * LDS;
+        float s[BN / 8][4];
+#pragma unroll
+        for (int n = 0; n < BN / 8; ++n) { s[n][0] = s[n][1] = s[n][2] = s[n][3] = 0.f; }
+#pragma unroll
+        for (int ks = 0; ks < KSTEPS; ++ks) {
+#pragma unroll
+            for (int np = 0; np < BN / 16; ++np) {               // two key n-tiles per ldmatrix.x4
+                unsigned kb[4];
+                ldmatrix_x4(kb, Kt + (size_t)(np * 16 + (lane & 7) + 8 * (lane >> 4)) * LDS + ks * 16 + 8 * ((lane >> 3) & 1));
+                mma16816(s[2 * np], qf[ks], kb[0], kb[1]);
+                mma16816(s[2 * np + 1], qf[ks], kb[2], kb[3]);
+            }
+        }
+        // mask and online softmax (scores are kept in units of log2: s * scale * log2(e))
+        const int j_base = kt * BN + 2 * t;
+        const bool need_mask = (kt * BN + BN - 1 > pos0 + row0) || (window > 0) || !row_a || !row_b;
+        float mx[2] = {-INFINITY, -INFINITY};
+#pragma unroll
+        for (int n = 0; n < BN / 8; ++n) {
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                float v = s[n][e] * scale_log2;
+                if (need_mask) {
+                    const int j = j_base + n * 8 + (e & 1);
+                    const int p = (e < 2) ? pos_a : pos_b;
+                    const bool rv = (e < 2) ? row_a : row_b;
+                    if (!rv || j > p || (window > 0 && j <= p - window)) v = -INFINITY;
+                }
+                s[n][e] = v;
+                mx[e >> 1] = fmaxf(mx[e >> 1], v);
+            }
+        }
+        float corr[2], base[2];
+#pragma unroll
+        for (int r = 0; r < 2; ++r) {
+            mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 1));
+            mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 2));
+            const float mn = fmaxf(m_run[r], mx[r]);
+            base[r] = (mn == -INFINITY) ? 0.f : mn;              // a row with no key yet: exp2(-inf - 0) = 0
+            corr[r] = exp2f(m_run[r] - base[r]);
+            m_run[r] = mn;
+            l_run[r] *= corr[r];
+        }
+        float ls[2] = {0.f, 0.f};
+        unsigned pf[BN / 16][4];
+#pragma unroll
+        for (int n = 0; n < BN / 8; ++n) {
+            const float p0 = exp2f(s[n][0] - base[0]), p1 = exp2f(s[n][1] - base[0]);
+            const float p2 = exp2f(s[n][2] - base[1]), p3 = exp2f(s[n][3] - base[1]);
+            ls[0] += p0 + p1;
+            ls[1] += p2 + p3;
+            pf[n >> 1][(n & 1) * 2] = pack_bf16(p0, p1);
+            pf[n >> 1][(n & 1) * 2 + 1] = pack_bf16(p2, p3);
+        }
+        l_run[0] += ls[0];
+        l_run[1] += ls[1];
+#pragma unroll
+        for (int d = 0; d < DTILES; ++d) {
+            o[d][0] *= corr[0]; o[d][1] *= corr[0]; o[d][2] *= corr[1]; o[d][3] *= corr[1];
+        }
+#pragma unroll
+        for (int kb16 = 0; kb16 < BN / 16; ++kb16) {
+#pragma unroll
+            for (int dp = 0; dp < DTILES / 2; ++dp) {            // two d n-tiles per ldmatrix.x4.trans
+                unsigned vb[4];
+                ldmatrix_x4_trans(vb, Vt + (size_t)(kb16 * 16 + (lane & 7) + 8 * ((lane >> 3) & 1)) * LDS + dp * 16 + 8 * (lane >> 4));
+                mma16816(o[2 * dp], pf[kb16], vb[0], vb[1]);
+                mma16816(o[2 * dp + 1], pf[kb16], vb[2], vb[3]);
+            }
+        }
+        __syncthreads();                                         // the tile may be overwritten next round
+    }
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+        l_run[r] += __shfl_xor_sync(0xffffffffu, l_run[r], 1);
+        l_run[r] += __shfl_xor_sync(0xffffffffu, l_run[r], 2);
+    }
+    const float inv_a = l_run[0] > 0.f ? 1.f / l_run[0] : 0.f, inv_b = l_run[1] > 0.f ? 1.f / l_run[1] : 0.f;
+    if (row_a) {
+        bf16* op = out + ((size_t)(tok0 + row0 + g) * nq + h) * HD + 2 * t;
+#pragma unroll
+        for (int d = 0; d < DTILES; ++d) *reinterpret_cast<unsigned*>(op + d * 8) = pack_bf16(o[d][0] * inv_a, o[d][1] * inv_a);
+    }
+    if (row_b) {
+        bf16* op = out + ((size_t)(tok0 + row0 + g + 8) * nq + h) * HD + 2 * t;
+#pragma unroll
+        for (int d = 0; d < DTILES; ++d) *reinterpret_cast<unsigned*>(op + d * 8) = pack_bf16(o[d][2] * inv_b, o[d][3] * inv_b);
+    }
+}
+
+extern "C" int vl_flash_head_dim() { return HD; }
+
+extern "C" int vl_flash_prefill(const void* q, int q_stride, void* out, const void* kcache, const void* vcache,
+                                const int* block_table, int max_blocks, const int* tiles, int num_tiles,
+                                int nq, int nkv, int hd, int page_size, int num_pages, float scale, int window,
+                                unsigned* err, void* stream) {
+    if (num_tiles <= 0) return VL_OK;
+    if (hd != HD) return VL_ERR_UNSUPPORTED;
+    if (nq <= 0 || nkv <= 0 || nq % nkv || page_size <= 0 || max_blocks <= 0 || q_stride % 8) return VL_ERR_ARGUMENT;
+    if (nq > 65535) return VL_ERR_UNSUPPORTED;
+    const size_t smem = (size_t)(BM + 4 * BN) * LDS * sizeof(bf16);
+    cudaError_t e = cudaFuncSetAttribute(flash_prefill_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return (int)e;
+    flash_prefill_kernel<<<dim3(num_tiles, nq), NTHREADS, smem, (cudaStream_t)stream>>>(
+        (const bf16*)q, q_stride, (bf16*)out, (const bf16*)kcache, (const bf16*)vcache, block_table, max_blocks,
+        (const int4*)tiles, nq, nkv, page_size, num_pages, scale * 1.4426950408889634f, window, err);
+    return vl_launch_status();
+}
+
+// ---------------------------------------------------------------------------------------------
+// decode: one token, one KV head (rows = its query heads), one chunk of key positions per block
+// ---------------------------------------------------------------------------------------------
+namespace {
+constexpr int DEC_NST = (HD <= 128) ? 3 : 2;         // stages of 64 keys (K and V) in the ring
+constexpr int DEC_ROWS = 16;                         // query heads per block (rows of the tensor-core tile)
+}
+
+extern "C" __global__ void __launch_bounds__(NTHREADS)
+flash_decode_kernel(const bf16* __restrict__ q, int q_stride,
+                    const bf16* __restrict__ kcache, const bf16* __restrict__ vcache,
+                    const int* __restrict__ block_table, int max_blocks,
+                    const int* __restrict__ req_index, const int* __restrict__ positions,
+                    int nq, int nkv, int page_size, int num_pages, float scale_log2, int window,
+                    int chunk, int S, float* __restrict__ part_acc, float* __restrict__ part_ml, unsigned* err) {
+    extern __shared__ __align__(128) unsigned char fa_smem[];
+    bf16* Qs = reinterpret_cast<bf16*>(fa_smem);                 // [16][LDS]
+    bf16* ring = Qs + DEC_ROWS * LDS;                            // [NST][2][BN][LDS]
+    __shared__ float s_m[4][DEC_ROWS], s_l[4][DEC_ROWS];
+    const int split = blockIdx.x, tok = blockIdx.z;
+    const int grp = nq / nkv;
+    const int htiles = (grp + DEC_ROWS - 1) / DEC_ROWS;
+    const int kvh = blockIdx.y / htiles, htile = blockIdx.y - kvh * htiles;
+    const int h0 = kvh * grp + htile * DEC_ROWS;
+    const int nvalid = min(DEC_ROWS, grp - htile * DEC_ROWS);
+    const int pos = positions[tok];
+    if (pos < 0) return;
+    const int lo = (window > 0 && pos - window + 1 > 0) ? pos - window + 1 : 0;
+    const int c0 = max(split * chunk, lo);
+    const int c1 = min((split + 1) * chunk, pos + 1);
+    if (c0 >= c1) return;
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, t = lane & 3;
+    const int* table = block_table + (size_t)req_index[tok] * max_blocks;
+    const int st0 = c0 / BN, st1 = (c1 - 1) / BN;
+
+    for (int idx = tid; idx < DEC_ROWS * CPR; idx += NTHREADS) {
+        const int r = idx / CPR, c = idx - r * CPR;
+        const bool valid = r < nvalid;
+        const bf16* src = valid ? q + (size_t)tok * q_stride + (size_t)(h0 + r) * HD + c * 8 : q;
+        cp_async16(Qs + (size_t)r * LDS + c * 8, src, valid);
+    }
+    auto load_stage = [&](int st, int buf) {
+        bf16* kt = ring + (size_t)buf * 2 * BN * LDS;
+        load_kv_tile(kt, kcache, table, max_blocks, st * BN, BN, c0, pos, kvh, nkv, page_size, num_pages, err);
+        load_kv_tile(kt + BN * LDS, vcache, table, max_blocks, st * BN, BN, c0, pos, kvh, nkv, page_size, num_pages, err);
+    };
+#pragma unroll
+    for (int i = 0; i < DEC_NST - 1; ++i) {
+        if (st0 + i <= st1) load_stage(st0 + i, i);
+        cp_async_commit();
+    }
+    float o[DTILES][4], m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};
+#pragma unroll
+    for (int d = 0; d < DTILES; ++d) { o[d][0] = o[d][1] = o[d][2] = o[d][3] = 0.f; }
+    unsigned qf[KSTEPS][4];
+
+    for (int st = st0; st <= st1; ++st) {
+        const int it = st - st0;
+        cp_async_wait<DEC_NST - 2>();
+        __syncthreads();
+        if (st + DEC_NST - 1 <= st1) load_stage(st + DEC_NST - 1, (it + DEC_NST - 1) % DEC_NST);
+        cp_async_commit();
+        if (it == 0) {
+#pragma unroll
+            for (int ks = 0; ks < KSTEPS; ++ks)
+                ldmatrix_x4(qf[ks], Qs + (size_t)((lane & 7) + 8 * ((lane >> 3) & 1)) * LDS + ks * 16 + 8 * (lane >> 4));
+        }
+        const bf16* Kt = ring + (size_t)(it % DEC_NST) * 2 * BN * LDS;
+        const bf16* Vt = Kt + BN * LDS;
+        const int kr0 = warp * 16;                               // this warp's 16 keys of the tile
+        float s[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
+#pragma unroll
+        for (int ks = 0; ks < KSTEPS; ++ks) {
+            unsigned kb[4];
+            ldmatrix_x4(kb, Kt + (size_t)(kr0 + (lane & 7) + 8 * (lane >> 4)) * LDS + ks * 16 + 8 * ((lane >> 3) & 1));
+            mma16816(s[0], qf[ks], kb[0], kb[1]);
+            mma16816(s[1], qf[ks], kb[2], kb[3]);
+        }
+        float mx[2] = {-INFINITY, -INFINITY};
+#pragma unroll
+        for (int n = 0; n < 2; ++n)
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                const int j = st * BN + kr0 + n * 8 + 2 * t + (e & 1);
+                const float v = (j >= c0 && j < c1) ? s[n][e] * scale_log2 : -INFINITY;
+                s[n][e] = v;
+                mx[e >> 1] = fmaxf(mx[e >> 1], v);
+            }
+        float corr[2], base[2];
+#pragma unroll
+        for (int r = 0; r < 2; ++r) {
+            mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 1));
+            mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 2));
+            const float mn = fmaxf(m_run[r], mx[r]);
+            base[r] = (mn == -INFINITY) ? 0.f : mn;
+            corr[r] = exp2f(m_run[r] - base[r]);
+            m_run[r] = mn;
+            l_run[r] *= corr[r];
+        }
+        unsigned pf[4];
+        {
+            const float p00 = exp2f(s[0][0] - base[0]), p01 = exp2f(s[0][1] - base[0]);
+            const float p02 = exp2f(s[0][2] - base[1]), p03 = exp2f(s[0][3] - base[1]);
+            const float p10 = exp2f(s[1][0] - base[0]), p11 = exp2f(s[1][1] - base[0]);
+            const float p12 = exp2f(s[1][2] - base[1]), p13 = exp2f(s[1][3] - base[1]);
+            l_run[0] += p00 + p01 + p10 + p11;
+            l_run[1] += p02 + p03 + p12 + p13;
+            pf[0] = pack_bf16(p00, p01); pf[1] = pack_bf16(p02, p03);
+            pf[2] = pack_bf16(p10, p11); pf[3] = pack_bf16(p12, p13);
+        }
+#pragma unroll
+        for (int dp = 0; dp < DTILES / 2; ++dp) {
+            unsigned vb[4];
+            ldmatrix_x4_trans(vb, Vt + (size_t)(kr0 + (lane & 7) + 8 * ((lane >> 3) & 1)) * LDS + dp * 16 + 8 * (lane >> 4));
+            o[2 * dp][0] *= corr[0]; o[2 * dp][1] *= corr[0]; o[2 * dp][2] *= corr[1]; o[2 * dp][3] *= corr[1];
+            o[2 * dp + 1][0] *= corr[0]; o[2 * dp + 1][1] *= corr[0]; o[2 * dp + 1][2] *= corr[1]; o[2 * dp + 1][3] *= corr[1];
+            mma16816(o[2 * dp], pf, vb[0], vb[1]);
+            mma16816(o[2 * dp + 1], pf, vb[2], vb[3]);
+        }
+    }
+    cp_async_wait<0>();
+    __syncthreads();                                             // the ring is free: it now carries the warps' outputs
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+        l_run[r] += __shfl_xor_sync(0xffffffffu, l_run[r], 1);
+        l_run[r] += __shfl_xor_sync(0xffffffffu, l_run[r], 2);
+    }
+    float* sO = reinterpret_cast<float*>(ring);                  // [4][16][HD + 4]
+    constexpr int OLD = HD + 4;
+#pragma unroll
+    for (int d = 0; d < DTILES; ++d) {
+        float* pa = sO + ((size_t)warp * DEC_ROWS + g) * OLD + d * 8 + 2 * t;
+        pa[0] = o[d][0]; pa[1] = o[d][1];
+        pa[8 * OLD] = o[d][2]; pa[8 * OLD + 1] = o[d][3];
+    }
+    if (t == 0) {
+        s_m[warp][g] = m_run[0]; s_l[warp][g] = l_run[0];
+        s_m[warp][g + 8] = m_run[1]; s_l[warp][g + 8] = l_run[1];
+    }
+    __syncthreads();
+    for (int idx = tid; idx < nvalid * HD; idx += NTHREADS) {
+        const int r = idx / HD, e = idx - r * HD;
+        float M = -INFINITY;
+#pragma unroll
+        for (int w = 0; w < 4; ++w) M = fmaxf(M, s_m[w][r]);
+        float acc = 0.f, L = 0.f;
+#pragma unroll
+        for (int w = 0; w < 4; ++w) {
+            const float wgt = (s_m[w][r] == -INFINITY) ? 0.f : exp2f(s_m[w][r] - M);
+            acc += sO[((size_t)w * DEC_ROWS + r) * OLD + e] * wgt;
+            L += s_l[w][r] * wgt;
+        }
+        const size_t row = ((size_t)tok * nq + (h0 + r)) * S + split;
+        part_acc[row * HD + e] = acc;
+        if (e == 0) {
+            part_ml[row * 2] = M * 0.6931471805599453f;          // the merge kernel works in natural-log units
+            part_ml[row * 2 + 1] = L;
+        }
+    }
+}
+
+// Scratch as for vl_decode_attention: part_acc [T, nq, S, hd], part_ml [T, nq, S, 2] float32,
+// S = ceil(max_context / chunk); follow with vl_decode_attention_merge.
+extern "C" int vl_flash_decode(const void* q, int q_stride, const void* kcache, const void* vcache,
+                               const int* block_table, int max_blocks, const int* req_index, const int* positions,
+                               int T, int nq, int nkv, int hd, int page_size, int num_pages, float scale, int window,
+                               int chunk, int S, float* part_acc, float* part_ml, unsigned* err, void* stream) {
+    if (T <= 0) return VL_OK;
+    if (hd != HD) return VL_ERR_UNSUPPORTED;
+    if (nq <= 0 || nkv <= 0 || nq % nkv || page_size <= 0 || max_blocks <= 0 || q_stride % 8) return VL_ERR_ARGUMENT;
+    if (chunk <= 0 || chunk % BN || S <= 0 || S > 65535 || T > 65535) return VL_ERR_ARGUMENT;
+    const int grp = nq / nkv;
+    const int htiles = (grp + DEC_ROWS - 1) / DEC_ROWS;
+    const size_t ring = (size_t)DEC_NST * 2 * BN * LDS * sizeof(bf16);
+    const size_t merge = (size_t)4 * DEC_ROWS * (HD + 4) * sizeof(float);
+    const size_t smem = (size_t)DEC_ROWS * LDS * sizeof(bf16) + (ring > merge ? ring : merge);
+    cudaError_t e = cudaFuncSetAttribute(flash_decode_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return (int)e;
+    flash_decode_kernel<<<dim3(S, nkv * htiles, T), NTHREADS, smem, (cudaStream_t)stream>>>(
+        (const bf16*)q, q_stride, (const bf16*)kcache, (const bf16*)vcache, block_table, max_blocks, req_index,
+        positions, nq, nkv, page_size, num_pages, scale * 1.4426950408889634f, window, chunk, S, part_acc, part_ml, err);
+    return vl_launch_status();
+}

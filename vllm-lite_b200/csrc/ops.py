@@ -44,6 +44,13 @@ _SIGNATURES = {
     ("attention", "vl_decode_attention"): [c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int,
                                            c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int,
                                            c_float, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p],
+    ("attention", "vl_decode_attention_merge"): [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int,
+                                                 c_int, c_int, c_void_p],
+    ("flash_attn", "vl_flash_prefill"): [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int,
+                                         c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_void_p, c_void_p],
+    ("flash_attn", "vl_flash_decode"): [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p,
+                                        c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_int, c_int,
+                                        c_void_p, c_void_p, c_void_p, c_void_p],
     ("activation", "vl_silu_mul"): [c_void_p, c_void_p, c_int, c_int, c_int, c_void_p],
     ("gemm_f32", "vl_gemm_f32_nt"): [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p],
     ("gemm_bf16", "vl_gemm_bf16_small_m"): [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
@@ -57,13 +64,14 @@ _functions = {}
 launch_count = 0          # kernels of this library launched so far (graph replays add theirs)
 
 
-def _fn(lib: str, name: str):
-    f = _functions.get((lib, name))
+def _fn(lib: str, name: str, defines=None):
+    key = (lib, name, build._variant(defines))
+    f = _functions.get(key)
     if f is None:
-        f = getattr(build.load(lib), name)
+        f = getattr(build.load(lib, defines), name)
         f.argtypes = _SIGNATURES[(lib, name)]
         f.restype = c_int
-        _functions[(lib, name)] = f
+        _functions[key] = f
     return f
 
 
@@ -237,6 +245,60 @@ def decode_attention(qkv, out, k_cache, v_cache, block_table, req_index, positio
         "vl_decode_attention")
     global launch_count
     launch_count += 1           # two kernels: the split pass and the merge
+    return out
+
+
+def flash_supported(dtype, head_dim) -> bool:
+    """The tensor-core attention kernels take bfloat16 and head sizes in steps of 16 up to 256."""
+    return dtype == torch.bfloat16 and head_dim % 16 == 0 and 16 <= head_dim <= 256
+
+
+def _flash_checks(qkv, k_cache, v_cache, block_table, num_heads, num_kv_heads, head_dim):
+    _need(qkv, torch.bfloat16, "qkv", 2)
+    _need(k_cache, torch.bfloat16, "k_cache", 4); _need(v_cache, torch.bfloat16, "v_cache", 4)
+    _need(block_table, torch.int32, "block_table", 2)
+    if qkv.shape[1] < num_heads * head_dim or qkv.shape[1] % 8:
+        raise KernelError("flash attention: qkv rows are too narrow or not 16-byte aligned")
+    if k_cache.shape != v_cache.shape or k_cache.shape[1] != num_kv_heads or k_cache.shape[3] != head_dim:
+        raise KernelError(f"cache {tuple(k_cache.shape)} does not match kv heads {num_kv_heads} x {head_dim}")
+
+
+def flash_prefill(qkv, out, k_cache, v_cache, block_table, tiles, num_heads, num_kv_heads, head_dim, scale, window, err):
+    """Tensor-core attention for prompt portions.  `tiles` int32 [n, 4]: (row of the block table,
+    index of the tile's first token in the step, tokens (<= 64), position of the first token);
+    the tiles of a step cover every token once."""
+    _flash_checks(qkv, k_cache, v_cache, block_table, num_heads, num_kv_heads, head_dim)
+    _need(out, torch.bfloat16, "out", 2); _need(tiles, torch.int32, "tiles", 2)
+    if out.shape != (qkv.shape[0], num_heads * head_dim) or tiles.shape[1] != 4:
+        raise KernelError("flash_prefill: shapes disagree")
+    _check(_fn("flash_attn", "vl_flash_prefill", {"FA_HD": head_dim})(
+        _ptr(qkv), qkv.shape[1], _ptr(out), _ptr(k_cache), _ptr(v_cache), _ptr(block_table), block_table.shape[1],
+        _ptr(tiles), tiles.shape[0], num_heads, num_kv_heads, head_dim, k_cache.shape[2], k_cache.shape[0],
+        float(scale), int(window or 0), _ptr(err), _stream()), "vl_flash_prefill")
+    return out
+
+
+def flash_decode(qkv, out, k_cache, v_cache, block_table, req_index, positions, num_heads, num_kv_heads,
+                 head_dim, scale, window, max_context, part_acc, part_ml, err, chunk=DECODE_CHUNK):
+    """Tensor-core version of `decode_attention` (bfloat16): the split pass, then the merge."""
+    _flash_checks(qkv, k_cache, v_cache, block_table, num_heads, num_kv_heads, head_dim)
+    _need(out, torch.bfloat16, "out", 2)
+    _need(req_index, torch.int32, "req_index", 1); _need(positions, torch.int32, "positions", 1)
+    _need(part_acc, torch.float32, "part_acc"); _need(part_ml, torch.float32, "part_ml")
+    T = qkv.shape[0]
+    if out.shape != (T, num_heads * head_dim) or req_index.shape[0] != T or positions.shape[0] != T:
+        raise KernelError("flash_decode: token counts or widths disagree")
+    S, need_acc, need_ml = decode_attention_scratch(T, num_heads, head_dim, max_context, chunk)
+    if part_acc.numel() < need_acc or part_ml.numel() < need_ml:
+        raise KernelError(f"flash_decode: scratch too small ({part_acc.numel()} < {need_acc})")
+    _check(_fn("flash_attn", "vl_flash_decode", {"FA_HD": head_dim})(
+        _ptr(qkv), qkv.shape[1], _ptr(k_cache), _ptr(v_cache), _ptr(block_table), block_table.shape[1],
+        _ptr(req_index), _ptr(positions), T, num_heads, num_kv_heads, head_dim, k_cache.shape[2], k_cache.shape[0],
+        float(scale), int(window or 0), chunk, S, _ptr(part_acc), _ptr(part_ml), _ptr(err), _stream()),
+        "vl_flash_decode")
+    _check(_fn("attention", "vl_decode_attention_merge")(
+        _ptr(part_acc), _ptr(part_ml), _ptr(positions), _ptr(out), dtype_code(out.dtype), T, num_heads, head_dim,
+        chunk, S, int(window or 0), _stream()), "vl_decode_attention_merge")
     return out
 
 

@@ -195,8 +195,16 @@ class ModelRunner:
             nonlocal cursor
             off[name] = (cursor, n)
             cursor += _align4(max(n, 1))
+        # tiles of up to 64 consecutive tokens of one request, for the tensor-core prefill kernel
+        tile_list = []
+        if not bucket:
+            t0 = 0
+            for b, h in enumerate(host_entries):
+                for lo in range(0, h.count, 64):
+                    tile_list.append((b, t0 + lo, min(64, h.count - lo), h.start + lo))
+                t0 += h.count
         for name, n in (("tokens", T), ("positions", T), ("req_index", T), ("cu_seqlens", B + 1),
-                        ("state_slots", B), ("logit_rows", R)):
+                        ("state_slots", B), ("logit_rows", R), ("tiles", 4 * len(tile_list))):
             section(name, n)
         for g in range(G):
             section(f"slots{g}", T)
@@ -223,6 +231,8 @@ class ModelRunner:
             t += h.count
             cu[b + 1] = t
         view("state_slots")[:real_B] = [h.state_slot for h in host_entries]
+        if tile_list:
+            view("tiles")[:] = np.asarray(tile_list, dtype=np.int32).reshape(-1)
         for g in range(G):
             tb = view(f"table{g}").reshape(B, max_blocks[g])
             sl = view(f"slots{g}")
@@ -255,7 +265,8 @@ class ModelRunner:
                          logit_rows=dview("logit_rows"), groups=groups, entries=host_entries, err=self.err,
                          workspace=self.workspace, num_tokens=T, num_entries=B,
                          max_query_len=max(h.count for h in host_entries),
-                         tag=f"g{bucket}.{longest}." if bucket else "", graph_bucket=bucket)
+                         tag=f"g{bucket}.{longest}." if bucket else "", graph_bucket=bucket,
+                         query_tiles=dview("tiles").view(-1, 4) if tile_list else None)
 
     def _upload(self, meta: np.ndarray, bucket: int = 0) -> torch.Tensor:
         n = meta.shape[0]

@@ -4,8 +4,9 @@ Every kernel computes the same function of (query token, its request's pages);
 which one runs depends on the dtype and on the shape of the step only.  The
 float32 path always takes the one kernel whose order of additions depends on
 positions alone, so its results are bit-for-bit independent of the batch.  In
-bfloat16 a step of single tokens (decoding) takes the kernel that splits each
-token's key range over many blocks.
+bfloat16 the tensor-core kernels run: for a step of single tokens (decoding) the
+one that splits each token's key range over many blocks, else the one that walks
+tiles of 64 query tokens.
 """
 from __future__ import annotations
 
@@ -16,10 +17,14 @@ def run(qkv, out, cache, group, step, spec, scale):
     from ..csrc import ops
     args = (qkv, out, cache.k, cache.v, group.block_table, step.req_index, step.positions,
             spec.num_heads, spec.num_kv_heads, spec.head_dim, scale, spec.window)
-    if qkv.dtype == torch.bfloat16 and step.max_query_len == 1:
-        T = qkv.shape[0]
-        S, n_acc, n_ml = ops.decode_attention_scratch(T, spec.num_heads, spec.head_dim, group.max_context)
-        part_acc = step.workspace.get(step.tag + "attn.part_acc", (n_acc,), torch.float32)
-        part_ml = step.workspace.get(step.tag + "attn.part_ml", (n_ml,), torch.float32)
-        return ops.decode_attention(*args, group.max_context, part_acc, part_ml, step.err)
+    if ops.flash_supported(qkv.dtype, spec.head_dim):
+        if step.max_query_len == 1:
+            T = qkv.shape[0]
+            S, n_acc, n_ml = ops.decode_attention_scratch(T, spec.num_heads, spec.head_dim, group.max_context)
+            part_acc = step.workspace.get(step.tag + "attn.part_acc", (n_acc,), torch.float32)
+            part_ml = step.workspace.get(step.tag + "attn.part_ml", (n_ml,), torch.float32)
+            return ops.flash_decode(*args, group.max_context, part_acc, part_ml, step.err)
+        if step.query_tiles is not None:
+            return ops.flash_prefill(qkv, out, cache.k, cache.v, group.block_table, step.query_tiles,
+                                     spec.num_heads, spec.num_kv_heads, spec.head_dim, scale, spec.window, step.err)
     return ops.paged_attention(*args, step.err)

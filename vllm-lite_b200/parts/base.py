@@ -92,6 +92,7 @@ class StepBatch:
     max_query_len: int = 0
     tag: str = ""                   # namespace for workspace buffers
     graph_bucket: int = 0           # padded batch size when the step is replayed from a CUDA graph
+    query_tiles: Optional[torch.Tensor] = None   # int32 [n, 4]: (table row, first token, tokens <= 64, first position)
 
 
 @dataclass
