@@ -197,6 +197,9 @@ def main(argv=None):
     ap.add_argument("--context", type=int, default=4096)
     ap.add_argument("--layers", type=int, default=QWEN3_8B["num_hidden_layers"])
     ap.add_argument("--no-points", action="store_true", help="skip the batch 1 / 64 points and the prefill")
+    ap.add_argument("--no-e2e", action="store_true", help="skip the run through the Python entry point (for profiling)")
+    ap.add_argument("--kv-fill", default="prefill", choices=["prefill", "random"],
+                    help="what the cache holds before decoding: what real prompts leave, or random numbers (for profiling)")
     args = ap.parse_args(argv)
     if args.impl == "reference":
         return reference_arm()
@@ -225,9 +228,9 @@ def main(argv=None):
 
     clocks = ClockSampler().start()
     w0 = time.time()
-    ms, launches, mean_ctx = decode_run(runner, sampler, args.batch, args.context, warmup, args.steps, "prefill", vocab, "d")
+    ms, launches, mean_ctx = decode_run(runner, sampler, args.batch, args.context, warmup, args.steps, args.kv_fill, vocab, "d")
     w1 = time.time()
-    e2e_tps, h2d, d2h = e2e_run(engine, args.batch, args.context, warmup, args.steps, vocab)
+    e2e_tps, h2d, d2h = (0.0, 0, 0) if args.no_e2e else e2e_run(engine, args.batch, args.context, warmup, args.steps, vocab)
     clocks.stop()
     value = args.batch * 1000.0 / ms
     step_bytes = weight_bytes + args.batch * mean_ctx * kv_per_token
@@ -240,10 +243,11 @@ def main(argv=None):
                    "hidden": cfg["hidden_size"], "heads": cfg["num_attention_heads"], "kv_heads": cfg["num_key_value_heads"],
                    "head_dim": cfg["head_dim"], "intermediate": cfg["intermediate_size"], "vocab": vocab,
                    "global_batch": args.batch, "seq_len": args.context, "block_size": 16, "parallelism": "single GPU",
-                   "kv_fill": "real prefill", "l2": "inputs (weights 16 GB) larger than L2, no flush",
+                   "kv_fill": "real prefill" if args.kv_fill == "prefill" else "random numbers", "l2": "inputs (weights 16 GB) larger than L2, no flush",
                    "peaks": pk["source"]},
         "clocks": clocks.summary(w0, w1),
-        "e2e": {"value": round(e2e_tps, 1), "unit": "tokens/s", "h2d_bytes_per_step": int(h2d), "d2h_bytes_per_step": d2h},
+        "e2e": None if args.no_e2e else {"value": round(e2e_tps, 1), "unit": "tokens/s", "h2d_bytes_per_step": int(h2d),
+                                         "d2h_bytes_per_step": d2h},
         "gpu_launches": int(round(launches * args.steps)),
         "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": pk["hbm_gbs"], "unit": "GB/s",
                      "frac": round(achieved / pk["hbm_gbs"], 4)},

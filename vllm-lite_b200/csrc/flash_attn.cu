@@ -57,28 +57,31 @@ __device__ __forceinline__ unsigned pack_bf16(float lo, float hi) {
     return *reinterpret_cast<unsigned*>(&v);
 }
 
-// Copies the keys (or values) of positions [j0, j0 + rows) of one request and KV head into a
-// padded tile.  Positions outside [first, last] are filled with zeros and never looked up (their
-// pages may not exist, or may have been given back once a window passed them).
-__device__ __forceinline__ void load_kv_tile(bf16* tile, const bf16* cache, const int* table, int max_blocks,
-                                             int j0, int rows, int first, int last, int kvh, int nkv, int page_size,
-                                             int num_pages, unsigned* err) {
+// Row of the cache ([pages, nkv, page_size, HD] seen as rows of HD) that holds position j of the
+// request, or -1 when j lies outside [first, last] (such rows are filled with zeros and never looked
+// up: their pages may not exist, or may have been given back once a window passed them).
+__device__ __forceinline__ int cache_row(const int* table, int max_blocks, int j, int first, int last, int kvh,
+                                         int nkv, int page_size, int num_pages, unsigned* err) {
+    if (j < first || j > last) return -1;
+    const int blk = j / page_size;
+    const int page = blk < max_blocks ? table[blk] : -1;
+    if (page < 0 || page >= num_pages) {
+        atomicOr(err, VL_DEV_BAD_PAGE);
+        return -1;
+    }
+    return (page * nkv + kvh) * page_size + (j - blk * page_size);
+}
+
+// Copies `rows` rows of keys and of values into two padded tiles; rowidx[r] is the cache row of
+// tile row r (or -1: zeros).
+__device__ __forceinline__ void load_kv_tiles(bf16* ktile, bf16* vtile, const bf16* kcache, const bf16* vcache,
+                                              const int* rowidx, int rows) {
     for (int idx = threadIdx.x; idx < rows * CPR; idx += NTHREADS) {
         const int r = idx / CPR, c = idx - r * CPR;
-        const int j = j0 + r;
-        const bf16* src = cache;
-        bool valid = j >= first && j <= last;
-        if (valid) {
-            const int blk = j / page_size;
-            const int page = blk < max_blocks ? table[blk] : -1;
-            if (page < 0 || page >= num_pages) {
-                if (c == 0) atomicOr(err, VL_DEV_BAD_PAGE);
-                valid = false;
-            } else {
-                src = cache + (((size_t)page * nkv + kvh) * page_size + (j - blk * page_size)) * HD + c * 8;
-            }
-        }
-        cp_async16(tile + (size_t)r * LDS + c * 8, src, valid);
+        const int row = rowidx[r];
+        const size_t off = row < 0 ? 0 : (size_t)row * HD + c * 8;
+        cp_async16(ktile + (size_t)r * LDS + c * 8, kcache + off, row >= 0);
+        cp_async16(vtile + (size_t)r * LDS + c * 8, vcache + off, row >= 0);
     }
 }
 }  // namespace
@@ -93,6 +96,7 @@ flash_prefill_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restrict_
     bf16* Qs = reinterpret_cast<bf16*>(fa_smem);                 // [BM][LDS]
     bf16* Ks = Qs + BM * LDS;                                    // [2][BN][LDS]
     bf16* Vs = Ks + 2 * BN * LDS;                                // [2][BN][LDS]
+    __shared__ int s_rows[2][BN];                                // cache rows of the tile being loaded / the next one
     const int4 tile = tiles[blockIdx.x];
     const int req = tile.x, tok0 = tile.y, count = tile.z, pos0 = tile.w;
     const int h = blockIdx.y, kvh = h / (nq / nkv);
@@ -108,8 +112,12 @@ flash_prefill_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restrict_
         const bf16* src = valid ? q + (size_t)(tok0 + r) * q_stride + (size_t)h * HD + c * 8 : q;
         cp_async16(Qs + (size_t)r * LDS + c * 8, src, valid);
     }
-    load_kv_tile(Ks, kcache, table, max_blocks, kt_lo * BN, BN, lo, hi, kvh, nkv, page_size, num_pages, err);
-    load_kv_tile(Vs, vcache, table, max_blocks, kt_lo * BN, BN, lo, hi, kvh, nkv, page_size, num_pages, err);
+    if (tid < BN) {
+        s_rows[0][tid] = cache_row(table, max_blocks, kt_lo * BN + tid, lo, hi, kvh, nkv, page_size, num_pages, err);
+        s_rows[1][tid] = cache_row(table, max_blocks, (kt_lo + 1) * BN + tid, lo, hi, kvh, nkv, page_size, num_pages, err);
+    }
+    __syncthreads();
+    load_kv_tiles(Ks, Vs, kcache, vcache, s_rows[0], BN);
     cp_async_commit();
 
     float o[DTILES][4], m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};
@@ -123,16 +131,16 @@ flash_prefill_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restrict_
     for (int kt = kt_lo; kt <= kt_hi; ++kt) {
         const int buf = (kt - kt_lo) & 1;
         if (kt + 1 <= kt_hi) {
-            load_kv_tile(Ks + (buf ^ 1) * BN * LDS, kcache, table, max_blocks, (kt + 1) * BN, BN, lo, hi, kvh, nkv,
-                         page_size, num_pages, err);
-            load_kv_tile(Vs + (buf ^ 1) * BN * LDS, vcache, table, max_blocks, (kt + 1) * BN, BN, lo, hi, kvh, nkv,
-                         page_size, num_pages, err);
+            load_kv_tiles(Ks + (buf ^ 1) * BN * LDS, Vs + (buf ^ 1) * BN * LDS, kcache, vcache, s_rows[buf ^ 1], BN);
             cp_async_commit();
             cp_async_wait<1>();
         } else {
             cp_async_wait<0>();
         }
         __syncthreads();
+        // rows of tile kt + 2 (read after the barrier that ends this round; slot `buf` is no longer in use)
+        if (tid < BN && kt + 2 <= kt_hi)
+            s_rows[buf][tid] = cache_row(table, max_blocks, (kt + 2) * BN + tid, lo, hi, kvh, nkv, page_size, num_pages, err);
         if (kt == kt_lo) {
 #pragma unroll
             for (int ks = 0; ks < KSTEPS; ++ks)
@@ -255,6 +263,7 @@ extern "C" int vl_flash_prefill(const void* q, int q_stride, void* out, const vo
 namespace {
 constexpr int DEC_NST = (HD <= 128) ? 3 : 2;         // stages of 64 keys (K and V) in the ring
 constexpr int DEC_ROWS = 16;                         // query heads per block (rows of the tensor-core tile)
+constexpr int DEC_MAX_CHUNK = 1024;                  // most key positions per block
 }
 
 extern "C" __global__ void __launch_bounds__(NTHREADS)
@@ -268,6 +277,7 @@ flash_decode_kernel(const bf16* __restrict__ q, int q_stride,
     bf16* Qs = reinterpret_cast<bf16*>(fa_smem);                 // [16][LDS]
     bf16* ring = Qs + DEC_ROWS * LDS;                            // [NST][2][BN][LDS]
     __shared__ float s_m[4][DEC_ROWS], s_l[4][DEC_ROWS];
+    __shared__ int s_rows[DEC_MAX_CHUNK + BN];                   // cache rows of the chunk's positions, tile aligned
     const int split = blockIdx.x, tok = blockIdx.z;
     const int grp = nq / nkv;
     const int htiles = (grp + DEC_ROWS - 1) / DEC_ROWS;
@@ -290,10 +300,12 @@ flash_decode_kernel(const bf16* __restrict__ q, int q_stride,
         const bf16* src = valid ? q + (size_t)tok * q_stride + (size_t)(h0 + r) * HD + c * 8 : q;
         cp_async16(Qs + (size_t)r * LDS + c * 8, src, valid);
     }
+    for (int i = tid; i < (st1 - st0 + 1) * BN; i += NTHREADS)
+        s_rows[i] = cache_row(table, max_blocks, st0 * BN + i, c0, pos, kvh, nkv, page_size, num_pages, err);
+    __syncthreads();
     auto load_stage = [&](int st, int buf) {
         bf16* kt = ring + (size_t)buf * 2 * BN * LDS;
-        load_kv_tile(kt, kcache, table, max_blocks, st * BN, BN, c0, pos, kvh, nkv, page_size, num_pages, err);
-        load_kv_tile(kt + BN * LDS, vcache, table, max_blocks, st * BN, BN, c0, pos, kvh, nkv, page_size, num_pages, err);
+        load_kv_tiles(kt, kt + BN * LDS, kcache, vcache, s_rows + (st - st0) * BN, BN);
     };
 #pragma unroll
     for (int i = 0; i < DEC_NST - 1; ++i) {
@@ -419,7 +431,7 @@ extern "C" int vl_flash_decode(const void* q, int q_stride, const void* kcache, 
     if (T <= 0) return VL_OK;
     if (hd != HD) return VL_ERR_UNSUPPORTED;
     if (nq <= 0 || nkv <= 0 || nq % nkv || page_size <= 0 || max_blocks <= 0 || q_stride % 8) return VL_ERR_ARGUMENT;
-    if (chunk <= 0 || chunk % BN || S <= 0 || S > 65535 || T > 65535) return VL_ERR_ARGUMENT;
+    if (chunk <= 0 || chunk % BN || chunk > DEC_MAX_CHUNK || S <= 0 || S > 65535 || T > 65535) return VL_ERR_ARGUMENT;
     const int grp = nq / nkv;
     const int htiles = (grp + DEC_ROWS - 1) / DEC_ROWS;
     const size_t ring = (size_t)DEC_NST * 2 * BN * LDS * sizeof(bf16);
