@@ -3,23 +3,22 @@
 //
 // vl_gemm_bf16_small_m: for the few rows of a decode step (M <= 64).  The product is bound by
 // reading W once from HBM, so the kernel is built around that stream: a block owns 16 rows of W,
-// its 8 warps take the 32-wide slices of K in turn, every lane reads 16 contiguous bytes of two
-// rows of W and of one row of A per slice, and the tensor cores multiply them
-// (mma.sync m16n8k16, W as the 16-row operand, 8 rows of A as the other).  The instruction pairs
+// a producer warp brings them in by bulk copies (TMA) through a ring of shared-memory stages, and
+// four consumer warps multiply on the tensor cores (mma.sync m16n8k16, W as the 16-row operand,
+// 8 rows of A as the other); every lane reads 16 contiguous bytes of two rows of W and of one row
+// of A per 32-wide slice of K.  The instruction pairs
 // operand elements by their index along K and never mixes rows, so the 8 values a lane holds may
 // stand for any 8 of the 16 positions of a slice as long as both operands use the same
-// assignment; that is what lets each lane load whole 16-byte pieces.  The 8 warps' partial sums
+// assignment; that is what lets each lane load whole 16-byte pieces.  The 4 warps' partial sums
 // are added in warp order, so the result does not depend on the launch.
 // K must be a multiple of 8 (16-byte rows); any M <= 64 and any N.
 #include "common.cuh"
 
-#define GS_THREADS 256
-#define GS_WARPS (GS_THREADS / 32)
 #define GS_ROWS 16
 
 __device__ __forceinline__ uint4 ldg_stream16(const void* p) {
     uint4 v;
-    asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];"
+    asm("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];"
                  : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p));
     return v;
 }
@@ -30,47 +29,131 @@ __device__ __forceinline__ void mma_bf16_16816(float (&c)[4], unsigned a0, unsig
                  : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
 
+// ---- mbarrier / bulk-copy helpers ------------------------------------------------------------
+__device__ __forceinline__ unsigned smem_u32(const void* p) { return (unsigned)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ void mbar_init(unsigned long long* bar, unsigned count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
+}
+__device__ __forceinline__ void mbar_fence_init() { asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory"); }
+__device__ __forceinline__ void mbar_arrive_expect_tx(unsigned long long* bar, unsigned bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(unsigned long long* bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(unsigned long long* bar, unsigned parity) {
+    unsigned ok;
+    asm volatile(
+        "{\n .reg .pred p;\n mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n selp.u32 %0, 1, 0, p;\n}"
+        : "=r"(ok) : "r"(smem_u32(bar)), "r"(parity) : "memory");
+    return ok != 0;
+}
+// A wait gives up after this many polls (a fraction of a second) instead of hanging the device.
+#define MBAR_SPIN_LIMIT (1 << 22)
+__device__ __forceinline__ bool mbar_wait_bounded(unsigned long long* bar, unsigned parity) {
+    for (int i = 0; i < MBAR_SPIN_LIMIT; ++i)
+        if (mbar_try_wait(bar, parity)) return true;
+    return false;
+}
+// Both addresses 16-byte aligned, bytes a multiple of 16.
+__device__ __forceinline__ void bulk_copy_g2s(void* dst, const void* src, unsigned bytes, unsigned long long* bar) {
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                 ::"r"(smem_u32(dst)), "l"(src), "r"(bytes), "r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ void consumer_barrier() { asm volatile("bar.sync 1, 128;" ::: "memory"); }
+
+#define GS_KC 512                          // K elements of a stage
+#define GS_STAGES 4
+#define GS_ROWB (GS_KC * 2 + 16)           // bytes of a padded row of a stage: rows 16 bytes apart modulo 128
+#define GS_CONSUMERS 4                     // consumer warps; warp 4 is the producer
+
+// Block = 16 rows of W.  The producer warp streams them through a ring of GS_STAGES stages of
+// GS_KC columns with one bulk copy (TMA) per row and stage; four consumer warps each take a quarter
+// of every stage, read their tensor-core operands from shared memory (W) and from global memory (A,
+// small and cached), and hand the stage back.  Sums are added in warp order at the end.
 template <int MT, typename TO>
-__global__ void __launch_bounds__(GS_THREADS)
+__global__ void __launch_bounds__(160)
 gemm_bf16_small_m_kernel(const bf16* __restrict__ A, const bf16* __restrict__ W, TO* __restrict__ C,
-                         int M, int N, int K, int lda, int ldw, int ldc) {
-    __shared__ float red[GS_THREADS / 32][MT][GS_ROWS][8];
+                         int M, int N, int K, int lda, int ldw, int ldc, unsigned* err) {
+    extern __shared__ __align__(128) unsigned char gs_smem[];               // [GS_STAGES][16][GS_ROWB]
+    __shared__ float red[GS_CONSUMERS][MT][GS_ROWS][8];
+    __shared__ __align__(8) unsigned long long full_bar[GS_STAGES], empty_bar[GS_STAGES];
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    const int g = lane >> 2, t = lane & 3;
     const int n0 = blockIdx.x * GS_ROWS;
-    const int r_lo = n0 + g, r_hi = n0 + g + 8;
-    const bf16* w_lo = W + (size_t)min(r_lo, N - 1) * ldw;
-    const bf16* w_hi = W + (size_t)min(r_hi, N - 1) * ldw;
-    const bool ok_lo = r_lo < N, ok_hi = r_hi < N;
+    const int iters = (K + GS_KC - 1) / GS_KC;
+    if (tid == 0) {
+        for (int i = 0; i < GS_STAGES; ++i) { mbar_init(&full_bar[i], 1); mbar_init(&empty_bar[i], GS_CONSUMERS); }
+        mbar_fence_init();
+    }
+    __syncthreads();
+    if (warp == GS_CONSUMERS) {                                            // ---- producer ----
+        if (lane < GS_ROWS) {
+            const bf16* src_row = W + (size_t)min(n0 + lane, N - 1) * ldw;  // rows beyond N re-read the last one
+            for (int it = 0; it < iters; ++it) {
+                const int s = it % GS_STAGES;
+                if (it >= GS_STAGES) {                                   // lane 0 waits for the consumers, all 16 follow it
+                    int ok = 1;
+                    if (lane == 0) ok = mbar_wait_bounded(&empty_bar[s], (unsigned)((it / GS_STAGES - 1) & 1)) ? 1 : 0;
+                    ok = __shfl_sync(0x0000ffffu, ok, 0);
+                    if (!ok) {
+                        if (lane == 0 && err) atomicOr(err, VL_DEV_WAIT_EXPIRED);
+                        break;
+                    }
+                }
+                const int k0 = it * GS_KC;
+                const unsigned bytes = (unsigned)(min(GS_KC, K - k0) * 2);
+                if (lane == 0) mbar_arrive_expect_tx(&full_bar[s], bytes * GS_ROWS);
+                __syncwarp(0x0000ffffu);
+                bulk_copy_g2s(gs_smem + ((size_t)s * GS_ROWS + lane) * GS_ROWB, src_row + k0, bytes, &full_bar[s]);
+            }
+        }
+        return;
+    }
+    // ---- consumers ----
+    const int g = lane >> 2, t = lane & 3;
+    const bf16* a_row[MT];
+#pragma unroll
+    for (int j = 0; j < MT; ++j) a_row[j] = A + (size_t)min(8 * j + g, M - 1) * lda + 8 * t;
     float acc[MT][4];
 #pragma unroll
     for (int j = 0; j < MT; ++j)
 #pragma unroll
         for (int i = 0; i < 4; ++i) acc[j][i] = 0.f;
     const uint4 zero = make_uint4(0, 0, 0, 0);
-    const int steps = (K + 31) / 32;
-    constexpr int UNROLL = MT == 1 ? 8 : (MT == 2 ? 4 : 2);
-    for (int s0 = warp; s0 < steps; s0 += GS_WARPS * UNROLL) {
-        uint4 wl[UNROLL], wh[UNROLL], av[UNROLL][MT];
+    constexpr int STEPS = GS_KC / 32 / GS_CONSUMERS;                        // 32-wide slices per warp and stage
+    bool alive = true;
+    for (int it = 0; it < iters && alive; ++it) {
+        const int s = it % GS_STAGES;
+        const int kbase = it * GS_KC + warp * (GS_KC / GS_CONSUMERS);
+        uint4 av[STEPS][MT];
 #pragma unroll
-        for (int u = 0; u < UNROLL; ++u) {
-            const int k = (s0 + GS_WARPS * u) * 32 + 8 * t;
-            const bool in = (s0 + GS_WARPS * u) < steps && k < K;
-            wl[u] = (in && ok_lo) ? ldg_stream16(w_lo + k) : zero;
-            wh[u] = (in && ok_hi) ? ldg_stream16(w_hi + k) : zero;
+        for (int u = 0; u < STEPS; ++u) {                                  // A does not wait for the stage
+            const int k = kbase + 32 * u;
+#pragma unroll
+            for (int j = 0; j < MT; ++j)
+                av[u][j] = (k + 8 * t < K) ? __ldg(reinterpret_cast<const uint4*>(a_row[j] + k)) : zero;
+        }
+        if (!mbar_wait_bounded(&full_bar[s], (unsigned)((it / GS_STAGES) & 1))) {
+            if (lane == 0 && err) atomicOr(err, VL_DEV_WAIT_EXPIRED);
+            alive = false;
+            break;
+        }
+        const unsigned char* stage = gs_smem + (size_t)s * GS_ROWS * GS_ROWB + (size_t)warp * (GS_KC / GS_CONSUMERS) * 2;
+#pragma unroll
+        for (int u = 0; u < STEPS; ++u) {
+            // columns beyond K of the last stage were not copied; A is zero there, but stale bytes could
+            // be NaN patterns, so W is zeroed as well
+            const bool in = kbase + 32 * u + 8 * t < K;
+            const uint4 wl = in ? *reinterpret_cast<const uint4*>(stage + (size_t)g * GS_ROWB + (32 * u + 8 * t) * 2) : zero;
+            const uint4 wh = in ? *reinterpret_cast<const uint4*>(stage + (size_t)(g + 8) * GS_ROWB + (32 * u + 8 * t) * 2) : zero;
 #pragma unroll
             for (int j = 0; j < MT; ++j) {
-                const int m = 8 * j + g;
-                av[u][j] = (in && m < M) ? __ldg(reinterpret_cast<const uint4*>(A + (size_t)m * lda + k)) : zero;
+                mma_bf16_16816(acc[j], wl.x, wh.x, wl.y, wh.y, av[u][j].x, av[u][j].y);
+                mma_bf16_16816(acc[j], wl.z, wh.z, wl.w, wh.w, av[u][j].z, av[u][j].w);
             }
         }
-#pragma unroll
-        for (int u = 0; u < UNROLL; ++u)
-#pragma unroll
-            for (int j = 0; j < MT; ++j) {
-                mma_bf16_16816(acc[j], wl[u].x, wh[u].x, wl[u].y, wh[u].y, av[u][j].x, av[u][j].y);
-                mma_bf16_16816(acc[j], wl[u].z, wh[u].z, wl[u].w, wh[u].w, av[u][j].z, av[u][j].w);
-            }
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&empty_bar[s]);
     }
     // acc[j] = {(row g, m 2t), (row g, m 2t+1), (row g+8, m 2t), (row g+8, m 2t+1)} of m-tile j
 #pragma unroll
@@ -80,14 +163,14 @@ gemm_bf16_small_m_kernel(const bf16* __restrict__ A, const bf16* __restrict__ W,
         red[warp][j][g + 8][2 * t] = acc[j][2];
         red[warp][j][g + 8][2 * t + 1] = acc[j][3];
     }
-    __syncthreads();
-    for (int idx = tid; idx < MT * 8 * GS_ROWS; idx += GS_THREADS) {
-        const int n = idx % GS_ROWS, m = idx / GS_ROWS;          // n fastest: 16 neighbours of a row of C
+    consumer_barrier();
+    for (int idx = tid; idx < MT * 8 * GS_ROWS; idx += 32 * GS_CONSUMERS) {
+        const int n = idx % GS_ROWS, m = idx / GS_ROWS;                    // n fastest: 16 neighbours of a row of C
         const int j = m >> 3, mm = m & 7;
         if (m < M && n0 + n < N) {
             float v = red[0][j][n][mm];
 #pragma unroll
-            for (int w = 1; w < GS_THREADS / 32; ++w) v += red[w][j][n][mm];
+            for (int w = 1; w < GS_CONSUMERS; ++w) v += red[w][j][n][mm];
             C[(size_t)m * ldc + n0 + n] = from_f32<TO>(v);
         }
     }
@@ -95,23 +178,32 @@ gemm_bf16_small_m_kernel(const bf16* __restrict__ A, const bf16* __restrict__ W,
 
 template <typename TO>
 static int launch_small_m(const bf16* A, const bf16* W, TO* C, int M, int N, int K, int lda, int ldw, int ldc,
-                          cudaStream_t s) {
+                          unsigned* err, cudaStream_t s) {
     dim3 grid((N + GS_ROWS - 1) / GS_ROWS);
-    if (M <= 8) gemm_bf16_small_m_kernel<1, TO><<<grid, GS_THREADS, 0, s>>>(A, W, C, M, N, K, lda, ldw, ldc);
-    else if (M <= 16) gemm_bf16_small_m_kernel<2, TO><<<grid, GS_THREADS, 0, s>>>(A, W, C, M, N, K, lda, ldw, ldc);
-    else if (M <= 32) gemm_bf16_small_m_kernel<4, TO><<<grid, GS_THREADS, 0, s>>>(A, W, C, M, N, K, lda, ldw, ldc);
-    else gemm_bf16_small_m_kernel<8, TO><<<grid, GS_THREADS, 0, s>>>(A, W, C, M, N, K, lda, ldw, ldc);
+    const size_t smem = (size_t)GS_STAGES * GS_ROWS * GS_ROWB;
+#define GS_LAUNCH(MT)                                                                                      \
+    {                                                                                                      \
+        auto kern = gemm_bf16_small_m_kernel<MT, TO>;                                                      \
+        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
+        if (e != cudaSuccess) return (int)e;                                                               \
+        kern<<<grid, 160, smem, s>>>(A, W, C, M, N, K, lda, ldw, ldc, err);                                \
+    }
+    if (M <= 8) GS_LAUNCH(1)
+    else if (M <= 16) GS_LAUNCH(2)
+    else if (M <= 32) GS_LAUNCH(4)
+    else GS_LAUNCH(8)
+#undef GS_LAUNCH
     return vl_launch_status();
 }
 
 extern "C" int vl_gemm_bf16_small_m(const void* A, const void* W, void* C, int out_dtype, int M, int N, int K,
-                                    int lda, int ldw, int ldc, void* stream) {
+                                    int lda, int ldw, int ldc, unsigned* err, void* stream) {
     if (M <= 0 || N <= 0) return VL_OK;
     if (M > 64 || K <= 0 || K % 8 || lda % 8 || ldw % 8) return VL_ERR_UNSUPPORTED;
     if (lda < K || ldw < K || ldc < N) return VL_ERR_ARGUMENT;
     if (((uintptr_t)A | (uintptr_t)W) & 15) return VL_ERR_UNSUPPORTED;
     cudaStream_t s = (cudaStream_t)stream;
-    if (out_dtype == VL_BF16) return launch_small_m<bf16>((const bf16*)A, (const bf16*)W, (bf16*)C, M, N, K, lda, ldw, ldc, s);
-    if (out_dtype == VL_F32) return launch_small_m<float>((const bf16*)A, (const bf16*)W, (float*)C, M, N, K, lda, ldw, ldc, s);
+    if (out_dtype == VL_BF16) return launch_small_m<bf16>((const bf16*)A, (const bf16*)W, (bf16*)C, M, N, K, lda, ldw, ldc, err, s);
+    if (out_dtype == VL_F32) return launch_small_m<float>((const bf16*)A, (const bf16*)W, (float*)C, M, N, K, lda, ldw, ldc, err, s);
     return VL_ERR_UNSUPPORTED;
 }

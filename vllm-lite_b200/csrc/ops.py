@@ -54,7 +54,7 @@ _SIGNATURES = {
     ("activation", "vl_silu_mul"): [c_void_p, c_void_p, c_int, c_int, c_int, c_void_p],
     ("gemm_f32", "vl_gemm_f32_nt"): [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p],
     ("gemm_bf16", "vl_gemm_bf16_small_m"): [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
-                                            c_void_p],
+                                            c_void_p, c_void_p],
     ("sampling", "vl_apply_penalties"): [c_void_p, c_longlong, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p,
                                          c_void_p, c_void_p, c_void_p, c_void_p],
     ("sampling", "vl_sample"): [c_void_p, c_longlong, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p,
@@ -332,7 +332,7 @@ def gemm_bf16_small_m_ok(M, K) -> bool:
     return 0 < M <= SMALL_M and K % 8 == 0
 
 
-def gemm_bf16_small_m(a, w, out):
+def gemm_bf16_small_m(a, w, out, err=None):
     """out[M, N] = a[M, K] @ w[N, K]^T for M <= 64: bfloat16 operands, float32 accumulation,
     out bfloat16 or float32.  Bound by one read of w."""
     _need(a, torch.bfloat16, "a", 2); _need(w, torch.bfloat16, "w", 2); _need(out, None, "out", 2)
@@ -341,7 +341,7 @@ def gemm_bf16_small_m(a, w, out):
     if w.shape[1] != K or out.shape != (M, N):
         raise KernelError(f"gemm_bf16: shapes disagree a{tuple(a.shape)} w{tuple(w.shape)} out{tuple(out.shape)}")
     _check(_fn("gemm_bf16", "vl_gemm_bf16_small_m")(_ptr(a), _ptr(w), _ptr(out), dtype_code(out.dtype), M, N, K,
-                                                    K, K, N, _stream()), "vl_gemm_bf16_small_m")
+                                                    K, K, N, _ptr(err), _stream()), "vl_gemm_bf16_small_m")
     return out
 
 
