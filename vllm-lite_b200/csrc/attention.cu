@@ -583,3 +583,43 @@ extern "C" int vl_decode_attention(const void* q, int q_stride, void* out, int d
                                             part_acc, part_ml, err, s);
     return VL_ERR_UNSUPPORTED;
 }
+
+// ---------------------------------------------------------------------------------------------
+// vl_decode_attention_no_alloc: vl_decode_attention with its scratch inside the library.
+// See attention_no_alloc.h for who needs it and for the limits.
+// ---------------------------------------------------------------------------------------------
+#include "attention_no_alloc.h"
+
+// Partial results of the split pass: first the accumulators, then the (maximum, sum) pairs.
+// In host code this name is only a handle for cudaGetSymbolAddress, never a pointer to pass on.
+static __device__ __align__(256) float vl_no_alloc_scratch[VL_NO_ALLOC_SCRATCH_FLOATS];
+
+// Device address of the array, per device, looked up on the first call there.
+static float* vl_no_alloc_address[VL_NO_ALLOC_MAX_DEVICES];
+
+extern "C" int vl_decode_attention_no_alloc(const void* q, int q_stride, void* out, int dtype,
+                                            const void* kcache, const void* vcache,
+                                            const int* block_table, int max_blocks,
+                                            const int* req_index, const int* positions,
+                                            int T, int nq, int nkv, int hd, int page_size, int num_pages,
+                                            float scale, int window, int chunk, int S,
+                                            unsigned* err, void* stream) {
+    if (T <= 0) return VL_OK;
+    if (nq <= 0 || hd <= 0 || S <= 0) return VL_ERR_ARGUMENT;
+    const unsigned long long acc_floats = (unsigned long long)T * nq * S * hd;
+    const unsigned long long ml_floats = (unsigned long long)T * nq * S * 2;
+    if (acc_floats + ml_floats > VL_NO_ALLOC_SCRATCH_FLOATS) return VL_ERR_SCRATCH;
+    int device = -1;
+    cudaError_t e = cudaGetDevice(&device);
+    if (e != cudaSuccess) return (int)e;
+    if (device < 0 || device >= VL_NO_ALLOC_MAX_DEVICES) return VL_ERR_UNSUPPORTED;
+    float* scratch = vl_no_alloc_address[device];
+    if (scratch == nullptr) {                       // first call on this device (which is current)
+        e = cudaGetSymbolAddress((void**)&scratch, vl_no_alloc_scratch);
+        if (e != cudaSuccess) return (int)e;
+        vl_no_alloc_address[device] = scratch;
+    }
+    return vl_decode_attention(q, q_stride, out, dtype, kcache, vcache, block_table, max_blocks, req_index,
+                               positions, T, nq, nkv, hd, page_size, num_pages, scale, window, chunk, S,
+                               scratch, scratch + acc_floats, err, stream);
+}

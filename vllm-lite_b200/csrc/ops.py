@@ -16,7 +16,8 @@ from . import build
 
 F32, BF16 = 0, 1
 _DTYPE_CODE = {torch.float32: F32, torch.bfloat16: BF16}
-_ERRORS = {-2: "a size this kernel does not take", -3: "inconsistent arguments"}
+_ERRORS = {-2: "a size this kernel does not take", -3: "inconsistent arguments",
+           -4: "the problem does not fit the built-in scratch memory"}
 
 
 class KernelError(RuntimeError):
