@@ -95,8 +95,8 @@ def test_gemm_f32_is_true_float32_and_batch_invariant(M, N, K):
 
 
 @pytest.mark.parametrize("out_dtype", [torch.bfloat16, torch.float32])
-@pytest.mark.parametrize("M,N,K", [(1, 333, 96), (8, 6144, 4096), (9, 50, 200), (33, 1000, 264), (64, 160, 4096),
-                                   (5, 17, 8), (16, 4096, 12288)])
+@pytest.mark.parametrize("M,N,K", [(1, 333, 96), (8, 6144, 4096), (9, 50, 200), (13, 1000, 264), (16, 160, 4096),
+                                   (5, 17, 8), (16, 4096, 12288), (7, 100, 520), (3, 40, 2056)])
 def test_gemm_bf16_small_m(M, N, K, out_dtype):
     torch.manual_seed(M * N)
     a = torch.randn(M, K, device=DEV).to(torch.bfloat16)

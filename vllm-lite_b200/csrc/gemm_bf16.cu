@@ -121,22 +121,26 @@ gemm_bf16_small_m_kernel(const bf16* __restrict__ A, const bf16* __restrict__ W,
         for (int i = 0; i < 4; ++i) acc[j][i] = 0.f;
     const uint4 zero = make_uint4(0, 0, 0, 0);
     constexpr int STEPS = GS_KC / 32 / GS_CONSUMERS;                        // 32-wide slices per warp and stage
-    bool alive = true;
-    for (int it = 0; it < iters && alive; ++it) {
-        const int s = it % GS_STAGES;
+    // A is small and cached, but a miss in L1 costs about a microsecond under load: the rows of A for
+    // stage it + 1 are requested before stage it is multiplied, so that latency hides behind the wait
+    // for W and the tensor-core work.
+    uint4 av[2][STEPS][MT];
+    auto load_a = [&](int it, uint4 (&dst)[STEPS][MT]) {
         const int kbase = it * GS_KC + warp * (GS_KC / GS_CONSUMERS);
-        uint4 av[STEPS][MT];
 #pragma unroll
-        for (int u = 0; u < STEPS; ++u) {                                  // A does not wait for the stage
+        for (int u = 0; u < STEPS; ++u) {
             const int k = kbase + 32 * u;
 #pragma unroll
             for (int j = 0; j < MT; ++j)
-                av[u][j] = (k + 8 * t < K) ? __ldg(reinterpret_cast<const uint4*>(a_row[j] + k)) : zero;
+                dst[u][j] = (it < iters && k + 8 * t < K) ? __ldg(reinterpret_cast<const uint4*>(a_row[j] + k)) : zero;
         }
+    };
+    auto multiply = [&](int it, const uint4 (&a)[STEPS][MT]) -> bool {
+        const int s = it % GS_STAGES;
+        const int kbase = it * GS_KC + warp * (GS_KC / GS_CONSUMERS);
         if (!mbar_wait_bounded(&full_bar[s], (unsigned)((it / GS_STAGES) & 1))) {
             if (lane == 0 && err) atomicOr(err, VL_DEV_WAIT_EXPIRED);
-            alive = false;
-            break;
+            return false;
         }
         const unsigned char* stage = gs_smem + (size_t)s * GS_ROWS * GS_ROWB + (size_t)warp * (GS_KC / GS_CONSUMERS) * 2;
 #pragma unroll
@@ -148,12 +152,21 @@ gemm_bf16_small_m_kernel(const bf16* __restrict__ A, const bf16* __restrict__ W,
             const uint4 wh = in ? *reinterpret_cast<const uint4*>(stage + (size_t)(g + 8) * GS_ROWB + (32 * u + 8 * t) * 2) : zero;
 #pragma unroll
             for (int j = 0; j < MT; ++j) {
-                mma_bf16_16816(acc[j], wl.x, wh.x, wl.y, wh.y, av[u][j].x, av[u][j].y);
-                mma_bf16_16816(acc[j], wl.z, wh.z, wl.w, wh.w, av[u][j].z, av[u][j].w);
+                mma_bf16_16816(acc[j], wl.x, wh.x, wl.y, wh.y, a[u][j].x, a[u][j].y);
+                mma_bf16_16816(acc[j], wl.z, wh.z, wl.w, wh.w, a[u][j].z, a[u][j].w);
             }
         }
         __syncwarp();
         if (lane == 0) mbar_arrive(&empty_bar[s]);
+        return true;
+    };
+    load_a(0, av[0]);
+    for (int it = 0; it < iters; it += 2) {                                 // two stages per round: the buffers swap roles
+        load_a(it + 1, av[1]);
+        if (!multiply(it, av[0])) break;
+        if (it + 1 >= iters) break;
+        load_a(it + 2, av[0]);
+        if (!multiply(it + 1, av[1])) break;
     }
     // acc[j] = {(row g, m 2t), (row g, m 2t+1), (row g+8, m 2t), (row g+8, m 2t+1)} of m-tile j
 #pragma unroll

@@ -326,7 +326,7 @@ def gemm_f32(a, w, out):
     return out
 
 
-SMALL_M = 16              # most rows the weight-streaming product is used for (the kernel takes up to 64)
+SMALL_M = 16              # most rows the weight-streaming product takes
 
 
 def gemm_bf16_small_m_ok(M, K) -> bool:
@@ -334,7 +334,7 @@ def gemm_bf16_small_m_ok(M, K) -> bool:
 
 
 def gemm_bf16_small_m(a, w, out, err=None):
-    """out[M, N] = a[M, K] @ w[N, K]^T for M <= 64: bfloat16 operands, float32 accumulation,
+    """out[M, N] = a[M, K] @ w[N, K]^T for M <= 16: bfloat16 operands, float32 accumulation,
     out bfloat16 or float32.  Bound by one read of w."""
     _need(a, torch.bfloat16, "a", 2); _need(w, torch.bfloat16, "w", 2); _need(out, None, "out", 2)
     M, K = a.shape
