@@ -244,14 +244,20 @@ def run_attention(kernel, qkv, out, kc, vc, table, req, pos, nq, nkv, hd, scale,
     S, n_acc, n_ml = ops().decode_attention_scratch(qkv.shape[0], nq, hd, ctx)
     pa = torch.full((n_acc,), float("nan"), device=DEV)
     pm = torch.full((n_ml,), float("nan"), device=DEV)
-    fn = ops().flash_decode if kernel == "flash_decode" else ops().decode_attention
-    return fn(qkv, out, kc, vc, table, req, pos, nq, nkv, hd, scale, window, ctx, pa, pm, e)
+    if kernel.startswith("flash_decode"):       # "flash_decode", "flash_decode64", "flash_decode1024": the chunk size
+        chunk = int(kernel[len("flash_decode"):] or 256)
+        S, n_acc, n_ml = ops().decode_attention_scratch(qkv.shape[0], nq, hd, ctx, chunk)
+        pa = torch.full((n_acc,), float("nan"), device=DEV)
+        pm = torch.full((n_ml,), float("nan"), device=DEV)
+        return ops().flash_decode(qkv, out, kc, vc, table, req, pos, nq, nkv, hd, scale, window, ctx, pa, pm, e, chunk=chunk)
+    return ops().decode_attention(qkv, out, kc, vc, table, req, pos, nq, nkv, hd, scale, window, ctx, pa, pm, e)
 
 
 def attention_cases():
     """(kernel, dtype): the tensor-core kernels exist in bfloat16 only."""
     return [("paged", torch.float32), ("paged", torch.bfloat16), ("decode", torch.float32), ("decode", torch.bfloat16),
-            ("flash_decode", torch.bfloat16), ("flash_prefill", torch.bfloat16)]
+            ("flash_decode", torch.bfloat16), ("flash_decode64", torch.bfloat16), ("flash_decode1024", torch.bfloat16),
+            ("flash_prefill", torch.bfloat16)]
 
 
 @pytest.mark.parametrize("kernel,dtype", [c for c in attention_cases() if c[0] != "paged"])

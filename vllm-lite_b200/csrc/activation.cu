@@ -6,6 +6,8 @@
 
 template <typename T>
 __global__ void silu_mul_kernel(const T* __restrict__ gu, T* __restrict__ out, int I, size_t total) {
+    pdl_launch_dependents();
+    pdl_wait();
     size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (idx >= total) return;
     const size_t t = idx / I;
@@ -21,9 +23,9 @@ extern "C" int vl_silu_mul(const void* gu, void* out, int dtype, int T, int I, v
     const unsigned blocks = (unsigned)((total + 255) / 256);
     cudaStream_t s = (cudaStream_t)stream;
     if (dtype == VL_F32)
-        silu_mul_kernel<float><<<blocks, 256, 0, s>>>((const float*)gu, (float*)out, I, total);
+        return vl_launch(silu_mul_kernel<float>, dim3(blocks), dim3(256), 0, s, (const float*)gu, (float*)out, I, total);
     else if (dtype == VL_BF16)
-        silu_mul_kernel<bf16><<<blocks, 256, 0, s>>>((const bf16*)gu, (bf16*)out, I, total);
+        return vl_launch(silu_mul_kernel<bf16>, dim3(blocks), dim3(256), 0, s, (const bf16*)gu, (bf16*)out, I, total);
     else
         return VL_ERR_UNSUPPORTED;
     return vl_launch_status();

@@ -456,6 +456,8 @@ template <typename T>
 __global__ void decode_attention_merge_kernel(const float* __restrict__ part_acc, const float* __restrict__ part_ml,
                                               const int* __restrict__ positions, T* __restrict__ out,
                                               int nq, int hd, int chunk, int S, int window) {
+    pdl_launch_dependents();
+    pdl_wait();
     const int t = blockIdx.x, h = blockIdx.y;
     const int pos = positions[t];
     T* op = out + ((size_t)t * nq + h) * hd;
@@ -549,12 +551,12 @@ extern "C" int vl_decode_attention_merge(const float* part_acc, const float* par
     if (T <= 0) return VL_OK;
     cudaStream_t s = (cudaStream_t)stream;
     if (dtype == VL_F32)
-        decode_attention_merge_kernel<float><<<dim3(T, nq), 128, 0, s>>>(part_acc, part_ml, positions, (float*)out, nq, hd, chunk, S, window);
-    else if (dtype == VL_BF16)
-        decode_attention_merge_kernel<bf16><<<dim3(T, nq), 128, 0, s>>>(part_acc, part_ml, positions, (bf16*)out, nq, hd, chunk, S, window);
-    else
-        return VL_ERR_UNSUPPORTED;
-    return vl_launch_status();
+        return vl_launch(decode_attention_merge_kernel<float>, dim3(T, nq), dim3(128), 0, s, part_acc, part_ml, positions,
+                         (float*)out, nq, hd, chunk, S, window);
+    if (dtype == VL_BF16)
+        return vl_launch(decode_attention_merge_kernel<bf16>, dim3(T, nq), dim3(128), 0, s, part_acc, part_ml, positions,
+                         (bf16*)out, nq, hd, chunk, S, window);
+    return VL_ERR_UNSUPPORTED;
 }
 
 // Scratch: part_acc holds T*nq*S*hd floats and part_ml T*nq*S*2 floats, S = ceil(max_context / chunk),

@@ -60,3 +60,40 @@ __device__ __forceinline__ float block_sum(float v, float* scratch) {
 }
 
 static inline int vl_launch_status() { return (int)cudaGetLastError(); }
+
+// ---- programmatic dependent launch ---------------------------------------------------------------
+// Kernels of a step are launched with the attribute that lets the next kernel of the stream start
+// while this one is still running.  A kernel calls pdl_launch_dependents() at once (the next grid
+// may be brought onto the SMs as soon as every block of this one has started) and pdl_wait() before
+// it first touches memory that earlier kernels of the stream write, and before its own first write
+// to global memory: pdl_wait() returns when all earlier kernels have completed and their writes are
+// visible.  What lies before pdl_wait() may only read constants of the step (weights) and set up
+// shared memory.  Launched without the attribute, both calls do nothing.
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
+#include <cstdlib>
+static inline bool vl_pdl_enabled() {
+    static int on = -1;
+    if (on < 0) {
+        const char* v = getenv("VLLM_LITE_B200_PDL");        // "0" turns dependent launches off
+        on = (v && v[0] == '0') ? 0 : 1;
+    }
+    return on == 1;
+}
+
+template <typename... KArgs, typename... Args>
+static inline int vl_launch(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                            Args... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = vl_pdl_enabled() ? 1 : 0;
+    return (int)cudaLaunchKernelEx(&cfg, kernel, KArgs(args)...);
+}

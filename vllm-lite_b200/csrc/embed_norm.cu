@@ -12,6 +12,8 @@
 template <typename TW>
 __global__ void embed_kernel(const int* __restrict__ ids, const TW* __restrict__ table,
                              float* __restrict__ x, int H, int V, unsigned* err) {
+    pdl_launch_dependents();
+    pdl_wait();
     const int t = blockIdx.x;
     const int id = ids[t];
     float* row = x + (size_t)t * H;
@@ -83,6 +85,8 @@ __global__ void __launch_bounds__(256)
 add_rmsnorm_vec_kernel(float* __restrict__ x, const TA* __restrict__ delta, const int* __restrict__ rows,
                        const float* __restrict__ w, TA* __restrict__ out, int H, float eps) {
     __shared__ float scratch[32];
+    pdl_launch_dependents();
+    pdl_wait();
     const int r = blockIdx.x;
     const int src = rows ? rows[r] : r;
     float* xr = x + (size_t)src * H;
@@ -121,10 +125,10 @@ static bool launch_rmsnorm_vec(float* x, const TA* delta, const int* rows, const
                                float eps, cudaStream_t s) {
     if (H % 4) return false;
     const int pieces = (H / 4 + 255) / 256;
-    if (pieces <= 1) add_rmsnorm_vec_kernel<TA, 1><<<R, 256, 0, s>>>(x, delta, rows, w, out, H, eps);
-    else if (pieces <= 2) add_rmsnorm_vec_kernel<TA, 2><<<R, 256, 0, s>>>(x, delta, rows, w, out, H, eps);
-    else if (pieces <= 4) add_rmsnorm_vec_kernel<TA, 4><<<R, 256, 0, s>>>(x, delta, rows, w, out, H, eps);
-    else if (pieces <= 8) add_rmsnorm_vec_kernel<TA, 8><<<R, 256, 0, s>>>(x, delta, rows, w, out, H, eps);
+    if (pieces <= 1) vl_launch(add_rmsnorm_vec_kernel<TA, 1>, dim3(R), dim3(256), 0, s, x, delta, rows, w, out, H, eps);
+    else if (pieces <= 2) vl_launch(add_rmsnorm_vec_kernel<TA, 2>, dim3(R), dim3(256), 0, s, x, delta, rows, w, out, H, eps);
+    else if (pieces <= 4) vl_launch(add_rmsnorm_vec_kernel<TA, 4>, dim3(R), dim3(256), 0, s, x, delta, rows, w, out, H, eps);
+    else if (pieces <= 8) vl_launch(add_rmsnorm_vec_kernel<TA, 8>, dim3(R), dim3(256), 0, s, x, delta, rows, w, out, H, eps);
     else return false;
     return true;
 }
@@ -148,9 +152,9 @@ extern "C" int vl_embed(const int* ids, const void* table, int table_dtype, floa
     if (T <= 0) return VL_OK;
     cudaStream_t s = (cudaStream_t)stream;
     if (table_dtype == VL_F32)
-        embed_kernel<float><<<T, 256, 0, s>>>(ids, (const float*)table, x, H, V, err);
+        vl_launch(embed_kernel<float>, dim3(T), dim3(256), 0, s, ids, (const float*)table, x, H, V, err);
     else if (table_dtype == VL_BF16)
-        embed_kernel<bf16><<<T, 256, 0, s>>>(ids, (const bf16*)table, x, H, V, err);
+        vl_launch(embed_kernel<bf16>, dim3(T), dim3(256), 0, s, ids, (const bf16*)table, x, H, V, err);
     else
         return VL_ERR_UNSUPPORTED;
     return vl_launch_status();

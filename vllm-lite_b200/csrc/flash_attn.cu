@@ -278,6 +278,8 @@ flash_decode_kernel(const bf16* __restrict__ q, int q_stride,
     bf16* ring = Qs + DEC_ROWS * LDS;                            // [NST][2][BN][LDS]
     __shared__ float s_m[4][DEC_ROWS], s_l[4][DEC_ROWS];
     __shared__ int s_rows[DEC_MAX_CHUNK + BN];                   // cache rows of the chunk's positions, tile aligned
+    pdl_launch_dependents();
+    pdl_wait();
     const int split = blockIdx.x, tok = blockIdx.z;
     const int grp = nq / nkv;
     const int htiles = (grp + DEC_ROWS - 1) / DEC_ROWS;
@@ -439,8 +441,8 @@ extern "C" int vl_flash_decode(const void* q, int q_stride, const void* kcache, 
     const size_t smem = (size_t)DEC_ROWS * LDS * sizeof(bf16) + (ring > merge ? ring : merge);
     cudaError_t e = cudaFuncSetAttribute(flash_decode_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return (int)e;
-    flash_decode_kernel<<<dim3(S, nkv * htiles, T), NTHREADS, smem, (cudaStream_t)stream>>>(
-        (const bf16*)q, q_stride, (const bf16*)kcache, (const bf16*)vcache, block_table, max_blocks, req_index,
-        positions, nq, nkv, page_size, num_pages, scale * 1.4426950408889634f, window, chunk, S, part_acc, part_ml, err);
-    return vl_launch_status();
+    return vl_launch(flash_decode_kernel, dim3(S, nkv * htiles, T), dim3(NTHREADS), smem, (cudaStream_t)stream,
+                     (const bf16*)q, q_stride, (const bf16*)kcache, (const bf16*)vcache, block_table, max_blocks,
+                     req_index, positions, nq, nkv, page_size, num_pages, scale * 1.4426950408889634f, window, chunk, S,
+                     part_acc, part_ml, err);
 }

@@ -81,12 +81,14 @@ gemm_bf16_small_m_kernel(const bf16* __restrict__ A, const bf16* __restrict__ W,
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int n0 = blockIdx.x * GS_ROWS;
     const int iters = (K + GS_KC - 1) / GS_KC;
+    pdl_launch_dependents();
     if (tid == 0) {
         for (int i = 0; i < GS_STAGES; ++i) { mbar_init(&full_bar[i], 1); mbar_init(&empty_bar[i], GS_CONSUMERS); }
         mbar_fence_init();
     }
     __syncthreads();
     if (warp == GS_CONSUMERS) {                                            // ---- producer ----
+        // W is a constant of the step: its stream starts while earlier kernels are still running
         if (lane < GS_ROWS) {
             const bf16* src_row = W + (size_t)min(n0 + lane, N - 1) * ldw;  // rows beyond N re-read the last one
             for (int it = 0; it < iters; ++it) {
@@ -110,6 +112,7 @@ gemm_bf16_small_m_kernel(const bf16* __restrict__ A, const bf16* __restrict__ W,
         return;
     }
     // ---- consumers ----
+    pdl_wait();                                                            // A comes from the kernel before
     const int g = lane >> 2, t = lane & 3;
     const bf16* a_row[MT];
 #pragma unroll
@@ -199,7 +202,7 @@ static int launch_small_m(const bf16* A, const bf16* W, TO* C, int M, int N, int
         auto kern = gemm_bf16_small_m_kernel<MT, TO>;                                                      \
         cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
         if (e != cudaSuccess) return (int)e;                                                               \
-        kern<<<grid, 160, smem, s>>>(A, W, C, M, N, K, lda, ldw, ldc, err);                                \
+        { int rc = vl_launch(kern, grid, dim3(160), smem, s, A, W, C, M, N, K, lda, ldw, ldc, err); if (rc) return rc; } \
     }
     if (M <= 8) GS_LAUNCH(1)
     else if (M <= 16) GS_LAUNCH(2)

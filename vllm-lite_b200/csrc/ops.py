@@ -249,6 +249,15 @@ def decode_attention(qkv, out, k_cache, v_cache, block_table, req_index, positio
     return out
 
 
+def decode_chunk_for(num_tokens, num_kv_heads, max_context, target_blocks=592) -> int:
+    """Key positions per block of the split decode kernels: the largest of 64..1024 that still
+    gives about two waves of blocks on the 148 SMs (a block's start-up is paid once per chunk)."""
+    for chunk in (1024, 512, 256, 128, 64):
+        if num_tokens * num_kv_heads * -(-int(max_context) // chunk) >= target_blocks:
+            return chunk
+    return 64
+
+
 def flash_supported(dtype, head_dim) -> bool:
     """The tensor-core attention kernels take bfloat16 and head sizes in steps of 16 up to 256."""
     return dtype == torch.bfloat16 and head_dim % 16 == 0 and 16 <= head_dim <= 256

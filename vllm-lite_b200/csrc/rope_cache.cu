@@ -26,6 +26,8 @@ __global__ void qk_norm_rope_write_kernel(
     T* __restrict__ kcache, T* __restrict__ vcache,
     int nq, int nkv, int hd, int page_size, long long num_slots, int row_stride, unsigned* err) {
     __shared__ float buf[ROPE_WARPS][ROPE_MAX_HD];
+    pdl_launch_dependents();
+    pdl_wait();
     const int t = blockIdx.x;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int head = blockIdx.y * ROPE_WARPS + warp;
@@ -96,11 +98,11 @@ extern "C" int vl_qk_norm_rope_write(
     dim3 grid(T, (nheads + ROPE_WARPS - 1) / ROPE_WARPS);
     cudaStream_t s = (cudaStream_t)stream;
     if (dtype == VL_F32)
-        qk_norm_rope_write_kernel<float><<<grid, ROPE_WARPS * 32, 0, s>>>(
+        return vl_launch(qk_norm_rope_write_kernel<float>, grid, dim3(ROPE_WARPS * 32), 0, s,
             (float*)qkv, positions, slots, qw, kw, eps, inv_freq, rot, (float*)kcache, (float*)vcache,
             nq, nkv, hd, page_size, num_slots, row_stride, err);
     else if (dtype == VL_BF16)
-        qk_norm_rope_write_kernel<bf16><<<grid, ROPE_WARPS * 32, 0, s>>>(
+        return vl_launch(qk_norm_rope_write_kernel<bf16>, grid, dim3(ROPE_WARPS * 32), 0, s,
             (bf16*)qkv, positions, slots, qw, kw, eps, inv_freq, rot, (bf16*)kcache, (bf16*)vcache,
             nq, nkv, hd, page_size, num_slots, row_stride, err);
     else

@@ -82,6 +82,8 @@ sample_kernel(const float* __restrict__ logits, long long row_stride, int V,
     __shared__ float s_max;
     __shared__ int s_pick;
 
+    pdl_launch_dependents();
+    pdl_wait();
     const int r = blockIdx.x, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const float* l = logits + (size_t)r * row_stride;
     const float temp = temperature ? temperature[r] : 0.f;
@@ -308,7 +310,6 @@ extern "C" int vl_sample(const float* logits, long long row_stride, int R, int V
                          const float* uniform, int* out_token, float* out_logprob, void* stream) {
     if (R <= 0) return VL_OK;
     if (V <= 0) return VL_ERR_ARGUMENT;
-    sample_kernel<<<R, SMP_THREADS, 0, (cudaStream_t)stream>>>(
-        logits, row_stride, V, temperature, top_k, top_p, uniform, out_token, out_logprob);
-    return vl_launch_status();
+    return vl_launch(sample_kernel, dim3(R), dim3(SMP_THREADS), 0, (cudaStream_t)stream,
+                     logits, row_stride, V, temperature, top_k, top_p, uniform, out_token, out_logprob);
 }

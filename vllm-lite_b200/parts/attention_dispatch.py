@@ -20,10 +20,11 @@ def run(qkv, out, cache, group, step, spec, scale):
     if ops.flash_supported(qkv.dtype, spec.head_dim):
         if step.max_query_len == 1:
             T = qkv.shape[0]
-            S, n_acc, n_ml = ops.decode_attention_scratch(T, spec.num_heads, spec.head_dim, group.max_context)
+            chunk = ops.decode_chunk_for(T, spec.num_kv_heads, group.max_context)
+            S, n_acc, n_ml = ops.decode_attention_scratch(T, spec.num_heads, spec.head_dim, group.max_context, chunk)
             part_acc = step.workspace.get(step.tag + "attn.part_acc", (n_acc,), torch.float32)
             part_ml = step.workspace.get(step.tag + "attn.part_ml", (n_ml,), torch.float32)
-            return ops.flash_decode(*args, group.max_context, part_acc, part_ml, step.err)
+            return ops.flash_decode(*args, group.max_context, part_acc, part_ml, step.err, chunk=chunk)
         if step.query_tiles is not None:
             return ops.flash_prefill(qkv, out, cache.k, cache.v, group.block_table, step.query_tiles,
                                      spec.num_heads, spec.num_kv_heads, spec.head_dim, scale, spec.window, step.err)
