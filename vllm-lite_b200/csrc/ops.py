@@ -250,12 +250,12 @@ def decode_attention(qkv, out, k_cache, v_cache, block_table, req_index, positio
 
 
 def decode_chunk_for(num_tokens, num_kv_heads, max_context, target_blocks=592) -> int:
-    """Key positions per block of the split decode kernels: the largest of 64..1024 that still
+    """Key positions per block of the split decode kernels: the largest of 256..1024 that still
     gives about two waves of blocks on the 148 SMs (a block's start-up is paid once per chunk)."""
-    for chunk in (1024, 512, 256, 128, 64):
+    for chunk in (1024, 512):
         if num_tokens * num_kv_heads * -(-int(max_context) // chunk) >= target_blocks:
             return chunk
-    return 64
+    return 256
 
 
 def flash_supported(dtype, head_dim) -> bool:
