@@ -56,6 +56,8 @@ _SIGNATURES = {
     ("gemm_f32", "vl_gemm_f32_nt"): [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p],
     ("gemm_bf16", "vl_gemm_bf16_small_m"): [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
                                             c_void_p, c_void_p],
+    ("gemm_tc5", "vl_gemm_bf16_tc5"): [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
+                                       c_void_p, c_void_p],
     ("sampling", "vl_apply_penalties"): [c_void_p, c_longlong, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p,
                                          c_void_p, c_void_p, c_void_p, c_void_p],
     ("sampling", "vl_sample"): [c_void_p, c_longlong, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p,
@@ -352,6 +354,26 @@ def gemm_bf16_small_m(a, w, out, err=None):
         raise KernelError(f"gemm_bf16: shapes disagree a{tuple(a.shape)} w{tuple(w.shape)} out{tuple(out.shape)}")
     _check(_fn("gemm_bf16", "vl_gemm_bf16_small_m")(_ptr(a), _ptr(w), _ptr(out), dtype_code(out.dtype), M, N, K,
                                                     K, K, N, _ptr(err), _stream()), "vl_gemm_bf16_small_m")
+    return out
+
+
+TC5_MIN_M = 1024          # from this many rows on the tcgen05 kernel is used
+
+
+def gemm_bf16_tc5_ok(M, K) -> bool:
+    return M >= TC5_MIN_M and K % 8 == 0
+
+
+def gemm_bf16_tc5(a, w, out, err=None):
+    """out[M, N] = a[M, K] @ w[N, K]^T on the tcgen05 tensor cores (TMA tiles, accumulators in
+    TMEM): bfloat16 operands, float32 accumulation, out bfloat16 or float32.  For many rows."""
+    _need(a, torch.bfloat16, "a", 2); _need(w, torch.bfloat16, "w", 2); _need(out, None, "out", 2)
+    M, K = a.shape
+    N = w.shape[0]
+    if w.shape[1] != K or out.shape != (M, N):
+        raise KernelError(f"gemm_bf16: shapes disagree a{tuple(a.shape)} w{tuple(w.shape)} out{tuple(out.shape)}")
+    _check(_fn("gemm_tc5", "vl_gemm_bf16_tc5")(_ptr(a), _ptr(w), _ptr(out), dtype_code(out.dtype), M, N, K,
+                                               K, K, N, _ptr(err), _stream()), "vl_gemm_bf16_tc5")
     return out
 
 

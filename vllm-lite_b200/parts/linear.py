@@ -33,4 +33,4 @@ class Linear:
         if a.dtype != self.weight.dtype:
             raise TypeError(f"activation {a.dtype} does not match weight {self.weight.dtype}")
         out = ws.get(step.tag + tag, (M, self.out_features), out_dtype)
-        return matmul.gemm_bf16(a, self.weight, out)
+        return matmul.gemm_bf16(a, self.weight, out, step.err)

@@ -1,19 +1,22 @@
 """bfloat16 matrix product out[M, N] = a[M, K] @ w[N, K]^T with float32 accumulation.
 
-Few rows (a decode step) go to the engine's weight-streaming tensor-core kernel.
-Many rows go to the library product (cuBLAS through torch): the reference hands
-its matrix products to its tensor library's GEMM in the same way.
+Few rows (a decode step) go to the engine's weight-streaming kernel, many rows (a prompt
+portion of a thousand tokens or more) to its tcgen05 kernel.  What lies between goes to
+the library product (cuBLAS through torch), as the reference hands its matrix products to
+its tensor library's GEMM.
 """
 from __future__ import annotations
 
 import torch
 
 
-def gemm_bf16(a, w, out):
+def gemm_bf16(a, w, out, err=None):
     from ..csrc import ops
     M, K = a.shape
     if ops.gemm_bf16_small_m_ok(M, K):
-        return ops.gemm_bf16_small_m(a, w, out)
+        return ops.gemm_bf16_small_m(a, w, out, err)
+    if ops.gemm_bf16_tc5_ok(M, K):
+        return ops.gemm_bf16_tc5(a, w, out, err)
     if out.dtype == torch.bfloat16:
         return torch.mm(a, w.t(), out=out)
     return torch.mm(a, w.t(), out_dtype=torch.float32, out=out)      # float32 logits from bfloat16 operands
