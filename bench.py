@@ -197,6 +197,7 @@ def main(argv=None):
     ap.add_argument("--context", type=int, default=4096)
     ap.add_argument("--layers", type=int, default=QWEN3_8B["num_hidden_layers"])
     ap.add_argument("--no-points", action="store_true", help="skip the batch 1 / 64 points and the prefill")
+    ap.add_argument("--only-prefill", action="store_true", help="time the 2,048-token prefill alone (for profiling)")
     ap.add_argument("--no-e2e", action="store_true", help="skip the run through the Python entry point (for profiling)")
     ap.add_argument("--kv-fill", default="prefill", choices=["prefill", "random"],
                     help="what the cache holds before decoding: what real prompts leave, or random numbers (for profiling)")
@@ -226,6 +227,12 @@ def main(argv=None):
     weight_bytes, kv_per_token, prefill_flops = model_bytes_and_flops(cfg, args.layers)
     pk = peaks()
 
+    if args.only_prefill:
+        pms = prefill_run(runner, vocab, repeats=max(1, min(args.steps, 5)))
+        print(json.dumps({"prefill": {"value": round(PREFILL_TOKENS / pms * 1000.0, 1), "tokens": PREFILL_TOKENS,
+                                      "ms": round(pms, 3), "layers": args.layers,
+                                      "frac": round(prefill_flops / (pms * 1e-3) / (pk["bf16_tflops"] * 1e12), 4)}}))
+        return 0
     clocks = ClockSampler().start()
     w0 = time.time()
     ms, launches, mean_ctx = decode_run(runner, sampler, args.batch, args.context, warmup, args.steps, args.kv_fill, vocab, "d")

@@ -72,6 +72,13 @@ def test_silu_mul_and_cast(dtype):
     ops().silu_mul(gu, out)
     g, u = gu.float()[:, :I], gu.float()[:, I:]
     assert torch.allclose(out.float(), g / (1 + torch.exp(-g)) * u, **tol(dtype))
+    I8 = 40                                                 # blocks of 8 gate columns and their 8 up columns
+    gi = (torch.randn(T, 2 * I8, device=DEV) * 4).to(dtype)
+    outi = torch.empty(T, I8, device=DEV, dtype=dtype)
+    ops().silu_mul(gi, outi, group=8)
+    blocks = gi.float().view(T, I8 // 8, 2, 8)
+    gg, uu = blocks[:, :, 0].reshape(T, I8), blocks[:, :, 1].reshape(T, I8)
+    assert torch.allclose(outi.float(), gg / (1 + torch.exp(-gg)) * uu, **tol(dtype))
     src = torch.randn(1000, device=DEV)
     b = torch.empty(1000, device=DEV, dtype=torch.bfloat16)
     ops().cast(src, b)
@@ -132,6 +139,25 @@ def test_gemm_bf16_tcgen05(M, N, K, out_dtype):
         assert float((out.double() - ref).abs().max()) <= 1e-5 * scale * (K ** 0.5)
     else:
         assert float((out.double() - ref).abs().max()) <= 2 ** -8 * scale + 1e-6
+
+
+@pytest.mark.parametrize("kernel,M", [("small_m", 1), ("small_m", 8), ("small_m", 13), ("tc5", 128), ("tc5", 300), ("tc5", 2048)])
+@pytest.mark.parametrize("I,K", [(160, 96), (12288, 4096), (24, 64)])
+def test_gemm_with_fused_swiglu(kernel, M, I, K):
+    """W interleaves 8 gate rows with their 8 up rows; the kernel writes silu(gate) * up."""
+    torch.manual_seed(M + I)
+    a = torch.randn(M, K, device=DEV).to(torch.bfloat16)
+    gate = (torch.randn(I, K, device=DEV) * 0.05).to(torch.bfloat16)
+    up = (torch.randn(I, K, device=DEV) * 0.05).to(torch.bfloat16)
+    w = torch.stack([gate.view(I // 8, 8, K), up.view(I // 8, 8, K)], dim=1).reshape(2 * I, K).contiguous()
+    out = torch.full((M, I), float("nan"), device=DEV, dtype=torch.bfloat16)
+    e = err_word()
+    fn = ops().gemm_bf16_small_m if kernel == "small_m" else ops().gemm_bf16_tc5
+    fn(a, w, out, e, swiglu=True)
+    assert int(e.item()) == 0
+    g, u = a.double() @ gate.double().T, a.double() @ up.double().T
+    ref = g / (1 + torch.exp(-g)) * u
+    assert float((out.double() - ref).abs().max()) <= 2 ** -7 * float(ref.abs().max()) + 1e-6
 
 
 def plain_head_norm_rope(x, w, eps, pos, theta, rot):

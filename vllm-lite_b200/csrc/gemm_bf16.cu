@@ -74,7 +74,7 @@ __device__ __forceinline__ void consumer_barrier() { asm volatile("bar.sync 1, 1
 template <int MT, typename TO>
 __global__ void __launch_bounds__(160)
 gemm_bf16_small_m_kernel(const bf16* __restrict__ A, const bf16* __restrict__ W, TO* __restrict__ C,
-                         int M, int N, int K, int lda, int ldw, int ldc, unsigned* err) {
+                         int M, int N, int K, int lda, int ldw, int ldc, unsigned* err, int swiglu) {
     extern __shared__ __align__(128) unsigned char gs_smem[];               // [GS_STAGES][16][GS_ROWB]
     __shared__ float red[GS_CONSUMERS][MT][GS_ROWS][8];
     __shared__ __align__(8) unsigned long long full_bar[GS_STAGES], empty_bar[GS_STAGES];
@@ -180,6 +180,20 @@ gemm_bf16_small_m_kernel(const bf16* __restrict__ A, const bf16* __restrict__ W,
         red[warp][j][g + 8][2 * t + 1] = acc[j][3];
     }
     consumer_barrier();
+    if (swiglu) {
+        // the block's 16 rows of W are 8 gate rows and their 8 up rows: C[m, n0/2 + i] = silu(gate_i) * up_i
+        for (int idx = tid; idx < MT * 8 * 8; idx += 32 * GS_CONSUMERS) {
+            const int i = idx & 7, m = idx >> 3;
+            const int j = m >> 3, mm = m & 7;
+            if (m < M && n0 + 8 + i < N) {
+                float gt = red[0][j][i][mm], up = red[0][j][i + 8][mm];
+#pragma unroll
+                for (int w = 1; w < GS_CONSUMERS; ++w) { gt += red[w][j][i][mm]; up += red[w][j][i + 8][mm]; }
+                C[(size_t)m * ldc + n0 / 2 + i] = from_f32<TO>(gt / (1.0f + expf(-gt)) * up);
+            }
+        }
+        return;
+    }
     for (int idx = tid; idx < MT * 8 * GS_ROWS; idx += 32 * GS_CONSUMERS) {
         const int n = idx % GS_ROWS, m = idx / GS_ROWS;                    // n fastest: 16 neighbours of a row of C
         const int j = m >> 3, mm = m & 7;
@@ -194,7 +208,7 @@ gemm_bf16_small_m_kernel(const bf16* __restrict__ A, const bf16* __restrict__ W,
 
 template <typename TO>
 static int launch_small_m(const bf16* A, const bf16* W, TO* C, int M, int N, int K, int lda, int ldw, int ldc,
-                          unsigned* err, cudaStream_t s) {
+                          unsigned* err, int swiglu, cudaStream_t s) {
     dim3 grid((N + GS_ROWS - 1) / GS_ROWS);
     const size_t smem = (size_t)GS_STAGES * GS_ROWS * GS_ROWB;
 #define GS_LAUNCH(MT)                                                                                      \
@@ -202,7 +216,7 @@ static int launch_small_m(const bf16* A, const bf16* W, TO* C, int M, int N, int
         auto kern = gemm_bf16_small_m_kernel<MT, TO>;                                                      \
         cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
         if (e != cudaSuccess) return (int)e;                                                               \
-        { int rc = vl_launch(kern, grid, dim3(160), smem, s, A, W, C, M, N, K, lda, ldw, ldc, err); if (rc) return rc; } \
+        { int rc = vl_launch(kern, grid, dim3(160), smem, s, A, W, C, M, N, K, lda, ldw, ldc, err, swiglu); if (rc) return rc; } \
     }
     if (M <= 8) GS_LAUNCH(1)
     else if (M <= 16) GS_LAUNCH(2)
@@ -213,13 +227,14 @@ static int launch_small_m(const bf16* A, const bf16* W, TO* C, int M, int N, int
 }
 
 extern "C" int vl_gemm_bf16_small_m(const void* A, const void* W, void* C, int out_dtype, int M, int N, int K,
-                                    int lda, int ldw, int ldc, unsigned* err, void* stream) {
+                                    int lda, int ldw, int ldc, unsigned* err, int swiglu, void* stream) {
     if (M <= 0 || N <= 0) return VL_OK;
+    if (swiglu && (N % 16 || ldc < N / 2)) return VL_ERR_ARGUMENT;
     if (M > 64 || K <= 0 || K % 8 || lda % 8 || ldw % 8) return VL_ERR_UNSUPPORTED;
-    if (lda < K || ldw < K || ldc < N) return VL_ERR_ARGUMENT;
+    if (lda < K || ldw < K || (!swiglu && ldc < N)) return VL_ERR_ARGUMENT;
     if (((uintptr_t)A | (uintptr_t)W) & 15) return VL_ERR_UNSUPPORTED;
     cudaStream_t s = (cudaStream_t)stream;
-    if (out_dtype == VL_BF16) return launch_small_m<bf16>((const bf16*)A, (const bf16*)W, (bf16*)C, M, N, K, lda, ldw, ldc, err, s);
-    if (out_dtype == VL_F32) return launch_small_m<float>((const bf16*)A, (const bf16*)W, (float*)C, M, N, K, lda, ldw, ldc, err, s);
+    if (out_dtype == VL_BF16) return launch_small_m<bf16>((const bf16*)A, (const bf16*)W, (bf16*)C, M, N, K, lda, ldw, ldc, err, swiglu, s);
+    if (out_dtype == VL_F32) return launch_small_m<float>((const bf16*)A, (const bf16*)W, (float*)C, M, N, K, lda, ldw, ldc, err, swiglu, s);
     return VL_ERR_UNSUPPORTED;
 }

@@ -16,7 +16,9 @@
 //   warps 2..5           epilogue: tcgen05.ld of the accumulator (a warp reads the 32 TMEM lanes
 //                        of its quarter), conversion, stores of the rows that exist.
 // Rows beyond M or N and columns beyond K are zero-filled by the TMA unit, so any M and N are
-// taken; K must be a multiple of 8 (16-byte rows).  Every wait on an mbarrier is bounded: when one
+// taken; K must be a multiple of 8 (16-byte rows).  With swiglu != 0, W holds blocks of 8 gate rows
+// followed by their 8 up rows and the epilogue writes C[m, 8b + i] = silu(y[m, 16b + i]) * y[m, 16b + 8 + i]
+// into a [M, N/2] matrix.  Every wait on an mbarrier is bounded: when one
 // expires the block records VL_DEV_WAIT_EXPIRED, stops, and still frees its TMEM.
 #include "common.cuh"
 #include <cuda.h>
@@ -128,7 +130,7 @@ __device__ __forceinline__ void tile_corner(int tile, int tiles_m, int tiles_n, 
 template <int BN, int STAGES, typename TO>
 __global__ void __launch_bounds__(NUM_THREADS)
 gemm_tc5_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w,
-                TO* __restrict__ C, int M, int N, int K, int ldc, unsigned* err, int tiles_m, int tiles_n) {
+                TO* __restrict__ C, int M, int N, int K, int ldc, unsigned* err, int tiles_m, int tiles_n, int swiglu) {
     constexpr unsigned A_BYTES = BM * BK * 2, W_BYTES = BN * BK * 2, STAGE_BYTES = A_BYTES + W_BYTES;
     extern __shared__ unsigned char tc5_smem_raw[];
     // tiles of the 128-byte swizzle must start on 1024-byte boundaries
@@ -225,7 +227,39 @@ gemm_tc5_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
             for (int c0 = 0; c0 < BN; c0 += 32) {
                 unsigned v[32];
                 tc5_ld32(tmem_base + ((unsigned)(quarter * 32) << 16) + (unsigned)(acc * BN + c0), v);
-                if (row < M) {
+                if (row < M && swiglu) {
+                    // 32 columns = two blocks of 8 gate and 8 up columns -> 16 columns of C at (n0 + c0) / 2
+                    TO* dst = C + (size_t)row * ldc + (n0 + c0) / 2;
+#pragma unroll
+                    for (int blk = 0; blk < 2; ++blk) {
+                        if (n0 + c0 + 16 * blk + 16 <= N) {
+                            float o[8];
+#pragma unroll
+                            for (int i = 0; i < 8; ++i) {
+                                const float gt = __uint_as_float(v[16 * blk + i]), up = __uint_as_float(v[16 * blk + 8 + i]);
+                                o[i] = gt / (1.0f + __expf(-gt)) * up;
+                            }
+                            if constexpr (sizeof(TO) == 2) {
+                                uint4 q;
+                                unsigned* w = reinterpret_cast<unsigned*>(&q);
+#pragma unroll
+                                for (int i = 0; i < 4; ++i) {
+                                    __nv_bfloat162 p = __floats2bfloat162_rn(o[2 * i], o[2 * i + 1]);
+                                    w[i] = *reinterpret_cast<unsigned*>(&p);
+                                }
+                                if ((((uintptr_t)(dst + 8 * blk)) & 15) == 0) {
+                                    *reinterpret_cast<uint4*>(dst + 8 * blk) = q;
+                                } else {
+#pragma unroll
+                                    for (int i = 0; i < 8; ++i) dst[8 * blk + i] = from_f32<TO>(o[i]);
+                                }
+                            } else {
+#pragma unroll
+                                for (int i = 0; i < 8; ++i) dst[8 * blk + i] = from_f32<TO>(o[i]);
+                            }
+                        }
+                    }
+                } else if (row < M) {
                     TO* dst = C + (size_t)row * ldc + n0 + c0;
                     if (n0 + c0 + 32 <= N && (((uintptr_t)dst) & 15) == 0) {
                         if constexpr (sizeof(TO) == 2) {
@@ -293,7 +327,7 @@ static int make_map(CUtensorMap* map, const void* base, int rows, int K, int ld,
 
 template <int BN, int STAGES, typename TO>
 static int launch_tc5(const void* A, const void* W, TO* C, int M, int N, int K, int lda, int ldw, int ldc,
-                      unsigned* err, cudaStream_t s) {
+                      unsigned* err, int swiglu, cudaStream_t s) {
     CUtensorMap map_a, map_w;
     int rc = make_map(&map_a, A, M, K, lda, BM);
     if (rc) return rc;
@@ -312,7 +346,7 @@ static int launch_tc5(const void* A, const void* W, TO* C, int M, int N, int K, 
     }
     const int total = tiles_m * tiles_n;
     dim3 grid(total < num_sms ? total : num_sms);             // one block per SM; blocks walk the tiles
-    return vl_launch(kern, grid, dim3(NUM_THREADS), smem, s, map_a, map_w, C, M, N, K, ldc, err, tiles_m, tiles_n);
+    return vl_launch(kern, grid, dim3(NUM_THREADS), smem, s, map_a, map_w, C, M, N, K, ldc, err, tiles_m, tiles_n, swiglu);
 }
 
 // Width of the tiles: 256, or 128 when N is no wider.  (Narrower tiles spread few rows over more SMs
@@ -320,19 +354,20 @@ static int launch_tc5(const void* A, const void* W, TO* C, int M, int N, int K, 
 // kernel's business.)
 template <typename TO>
 static int dispatch_tc5(const void* A, const void* W, TO* C, int M, int N, int K, int lda, int ldw, int ldc,
-                        unsigned* err, cudaStream_t s) {
-    if (N > 128) return launch_tc5<256, 4, TO>(A, W, C, M, N, K, lda, ldw, ldc, err, s);
-    return launch_tc5<128, 6, TO>(A, W, C, M, N, K, lda, ldw, ldc, err, s);
+                        unsigned* err, int swiglu, cudaStream_t s) {
+    if (N > 128) return launch_tc5<256, 4, TO>(A, W, C, M, N, K, lda, ldw, ldc, err, swiglu, s);
+    return launch_tc5<128, 6, TO>(A, W, C, M, N, K, lda, ldw, ldc, err, swiglu, s);
 }
 
 extern "C" int vl_gemm_bf16_tc5(const void* A, const void* W, void* C, int out_dtype, int M, int N, int K,
-                                int lda, int ldw, int ldc, unsigned* err, void* stream) {
+                                int lda, int ldw, int ldc, unsigned* err, int swiglu, void* stream) {
     if (M <= 0 || N <= 0) return VL_OK;
     if (K <= 0 || K % 8 || lda % 8 || ldw % 8) return VL_ERR_UNSUPPORTED;
-    if (lda < K || ldw < K || ldc < N) return VL_ERR_ARGUMENT;
+    if (swiglu ? (N % 16 || ldc < N / 2) : ldc < N) return VL_ERR_ARGUMENT;
+    if (lda < K || ldw < K) return VL_ERR_ARGUMENT;
     if (((uintptr_t)A | (uintptr_t)W) & 15) return VL_ERR_UNSUPPORTED;
     cudaStream_t s = (cudaStream_t)stream;
-    if (out_dtype == VL_BF16) return dispatch_tc5<bf16>(A, W, (bf16*)C, M, N, K, lda, ldw, ldc, err, s);
-    if (out_dtype == VL_F32) return dispatch_tc5<float>(A, W, (float*)C, M, N, K, lda, ldw, ldc, err, s);
+    if (out_dtype == VL_BF16) return dispatch_tc5<bf16>(A, W, (bf16*)C, M, N, K, lda, ldw, ldc, err, swiglu, s);
+    if (out_dtype == VL_F32) return dispatch_tc5<float>(A, W, (float*)C, M, N, K, lda, ldw, ldc, err, swiglu, s);
     return VL_ERR_UNSUPPORTED;
 }

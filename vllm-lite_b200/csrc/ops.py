@@ -52,12 +52,12 @@ _SIGNATURES = {
     ("flash_attn", "vl_flash_decode"): [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p,
                                         c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_int, c_int,
                                         c_void_p, c_void_p, c_void_p, c_void_p],
-    ("activation", "vl_silu_mul"): [c_void_p, c_void_p, c_int, c_int, c_int, c_void_p],
+    ("activation", "vl_silu_mul"): [c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p],
     ("gemm_f32", "vl_gemm_f32_nt"): [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p],
     ("gemm_bf16", "vl_gemm_bf16_small_m"): [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
-                                            c_void_p, c_void_p],
+                                            c_void_p, c_int, c_void_p],
     ("gemm_tc5", "vl_gemm_bf16_tc5"): [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
-                                       c_void_p, c_void_p],
+                                       c_void_p, c_int, c_void_p],
     ("sampling", "vl_apply_penalties"): [c_void_p, c_longlong, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p,
                                          c_void_p, c_void_p, c_void_p, c_void_p],
     ("sampling", "vl_sample"): [c_void_p, c_longlong, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p,
@@ -315,13 +315,18 @@ def flash_decode(qkv, out, k_cache, v_cache, block_table, req_index, positions, 
 
 
 # ---------------------------------------------------------------- feed-forward
-def silu_mul(gate_up, out):
+SWIGLU_GROUP = 8          # gate/up interleave that the matrix-product kernels' fused activation expects
+
+
+def silu_mul(gate_up, out, group=0):
+    """out[t, i] = silu(gate_i) * up_i of gate_up [T, 2I].  group = 0: gate columns, then up columns;
+    group = g: blocks of g gate columns followed by their g up columns."""
     _need(gate_up, None, "gate_up", 2); _need(out, gate_up.dtype, "out", 2)
     T, I2 = gate_up.shape
     if I2 % 2 or out.shape != (T, I2 // 2):
         raise KernelError("silu_mul: out must be [T, I] for gate_up [T, 2I]")
-    _check(_fn("activation", "vl_silu_mul")(_ptr(gate_up), _ptr(out), dtype_code(out.dtype), T, I2 // 2, _stream()),
-           "vl_silu_mul")
+    _check(_fn("activation", "vl_silu_mul")(_ptr(gate_up), _ptr(out), dtype_code(out.dtype), T, I2 // 2, int(group),
+                                            _stream()), "vl_silu_mul")
     return out
 
 
@@ -344,16 +349,25 @@ def gemm_bf16_small_m_ok(M, K) -> bool:
     return 0 < M <= SMALL_M and K % 8 == 0
 
 
-def gemm_bf16_small_m(a, w, out, err=None):
-    """out[M, N] = a[M, K] @ w[N, K]^T for M <= 16: bfloat16 operands, float32 accumulation,
-    out bfloat16 or float32.  Bound by one read of w."""
+def _gemm_shapes(a, w, out, swiglu):
     _need(a, torch.bfloat16, "a", 2); _need(w, torch.bfloat16, "w", 2); _need(out, None, "out", 2)
     M, K = a.shape
     N = w.shape[0]
-    if w.shape[1] != K or out.shape != (M, N):
-        raise KernelError(f"gemm_bf16: shapes disagree a{tuple(a.shape)} w{tuple(w.shape)} out{tuple(out.shape)}")
+    width = N // 2 if swiglu else N
+    if w.shape[1] != K or out.shape != (M, width) or (swiglu and N % (2 * SWIGLU_GROUP)):
+        raise KernelError(f"gemm_bf16: shapes disagree a{tuple(a.shape)} w{tuple(w.shape)} out{tuple(out.shape)}"
+                          + (" (fused SwiGLU)" if swiglu else ""))
+    return M, N, K, width
+
+
+def gemm_bf16_small_m(a, w, out, err=None, swiglu=False):
+    """out[M, N] = a[M, K] @ w[N, K]^T for M <= 16: bfloat16 operands, float32 accumulation,
+    out bfloat16 or float32.  Bound by one read of w.  swiglu: w holds blocks of 8 gate rows and
+    their 8 up rows, out is [M, N/2] = silu(gate) * up."""
+    M, N, K, width = _gemm_shapes(a, w, out, swiglu)
     _check(_fn("gemm_bf16", "vl_gemm_bf16_small_m")(_ptr(a), _ptr(w), _ptr(out), dtype_code(out.dtype), M, N, K,
-                                                    K, K, N, _ptr(err), _stream()), "vl_gemm_bf16_small_m")
+                                                    K, K, width, _ptr(err), int(swiglu), _stream()),
+           "vl_gemm_bf16_small_m")
     return out
 
 
@@ -364,16 +378,13 @@ def gemm_bf16_tc5_ok(M, K) -> bool:
     return M >= TC5_MIN_M and K % 8 == 0
 
 
-def gemm_bf16_tc5(a, w, out, err=None):
+def gemm_bf16_tc5(a, w, out, err=None, swiglu=False):
     """out[M, N] = a[M, K] @ w[N, K]^T on the tcgen05 tensor cores (TMA tiles, accumulators in
-    TMEM): bfloat16 operands, float32 accumulation, out bfloat16 or float32.  For many rows."""
-    _need(a, torch.bfloat16, "a", 2); _need(w, torch.bfloat16, "w", 2); _need(out, None, "out", 2)
-    M, K = a.shape
-    N = w.shape[0]
-    if w.shape[1] != K or out.shape != (M, N):
-        raise KernelError(f"gemm_bf16: shapes disagree a{tuple(a.shape)} w{tuple(w.shape)} out{tuple(out.shape)}")
+    TMEM): bfloat16 operands, float32 accumulation, out bfloat16 or float32.  For many rows.
+    swiglu: as in `gemm_bf16_small_m`."""
+    M, N, K, width = _gemm_shapes(a, w, out, swiglu)
     _check(_fn("gemm_tc5", "vl_gemm_bf16_tc5")(_ptr(a), _ptr(w), _ptr(out), dtype_code(out.dtype), M, N, K,
-                                               K, K, N, _ptr(err), _stream()), "vl_gemm_bf16_tc5")
+                                               K, K, width, _ptr(err), int(swiglu), _stream()), "vl_gemm_bf16_tc5")
     return out
 
 

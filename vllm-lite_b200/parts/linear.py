@@ -17,6 +17,20 @@ class Linear:
         self.weight = weight
         self.out_features, self.in_features = weight.shape
 
+    def swiglu(self, a, step, tag, group):
+        """silu(gate) * up of y = a W^T, W holding gate and up rows (interleaved in blocks of `group`
+        rows, or gate rows then up rows when group is 0): [M, out_features / 2].  The activation runs
+        inside the product kernel when that kernel can, else in a kernel of its own."""
+        from ..csrc import ops
+        from . import matmul
+        M = a.shape[0]
+        ws = step.workspace
+        out = ws.get(step.tag + tag + ".act", (M, self.out_features // 2), a.dtype)
+        if (group == ops.SWIGLU_GROUP and self.weight.dtype == torch.bfloat16 and a.dtype == torch.bfloat16
+                and matmul.fuses_swiglu(M, self.in_features)):
+            return matmul.gemm_bf16(a, self.weight, out, step.err, swiglu=True)
+        return ops.silu_mul(self(a, step, tag), out, group)
+
     def __call__(self, a, step, tag, out_dtype=None):
         from ..csrc import ops
         from . import matmul

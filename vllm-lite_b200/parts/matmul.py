@@ -10,13 +10,23 @@ from __future__ import annotations
 import torch
 
 
-def gemm_bf16(a, w, out, err=None):
+def fuses_swiglu(M, K) -> bool:
+    """Whether the product for M rows runs in a kernel that can apply SwiGLU to its own tile."""
+    from ..csrc import ops
+    return ops.gemm_bf16_small_m_ok(M, K) or ops.gemm_bf16_tc5_ok(M, K)
+
+
+def gemm_bf16(a, w, out, err=None, swiglu=False):
+    """swiglu (only where `fuses_swiglu`): w interleaves 8 gate rows with their 8 up rows and out is
+    [M, N/2] = silu(gate) * up."""
     from ..csrc import ops
     M, K = a.shape
     if ops.gemm_bf16_small_m_ok(M, K):
-        return ops.gemm_bf16_small_m(a, w, out, err)
+        return ops.gemm_bf16_small_m(a, w, out, err, swiglu)
     if ops.gemm_bf16_tc5_ok(M, K):
-        return ops.gemm_bf16_tc5(a, w, out, err)
+        return ops.gemm_bf16_tc5(a, w, out, err, swiglu)
+    if swiglu:
+        raise ValueError("the library product has no fused activation; ask fuses_swiglu() first")
     if out.dtype == torch.bfloat16:
         return torch.mm(a, w.t(), out=out)
     return torch.mm(a, w.t(), out_dtype=torch.float32, out=out)      # float32 logits from bfloat16 operands

@@ -1,6 +1,9 @@
 """SwiGLU feed-forward: down(silu(gate(h)) * up(h)), no biases
 (crates/model/src/components/mlp/swiglu.rs:18-31 of the reference).  gate and up
-are bound by their own names and stacked at load time into one [gate | up] matrix."""
+are bound by their own names and stacked at load time into one matrix: blocks of 8
+gate rows followed by their 8 up rows (plain halves when the width is no multiple
+of 8), so that a product kernel holds matching gate and up values in one tile and
+can apply the activation itself.  Row order does not touch any row's arithmetic."""
 from __future__ import annotations
 
 import torch
@@ -23,12 +26,18 @@ class SwiGLU:
     def __init__(self, spec: SwiGLUSpec, weights: dict, ctx):
         self.spec = spec
         self.dtype = ctx.dtype
-        self.gate_up = Linear(torch.cat([weights["gate_proj.weight"], weights["up_proj.weight"]], dim=0).contiguous())
+        gate, up = weights["gate_proj.weight"], weights["up_proj.weight"]
+        inter, hidden = spec.intermediate_size, spec.hidden_size
+        self.group = 8 if inter % 8 == 0 else 0
+        if self.group:
+            g = self.group
+            stacked = torch.stack([gate.view(inter // g, g, hidden), up.view(inter // g, g, hidden)], dim=1)
+            stacked = stacked.reshape(2 * inter, hidden)
+        else:
+            stacked = torch.cat([gate, up], dim=0)
+        self.gate_up = Linear(stacked.contiguous())
         self.down = Linear(weights["down_proj.weight"])
 
     def __call__(self, h, step):
-        from ..csrc import ops
-        gu = self.gate_up(h, step, "mlp.gate_up")
-        act = step.workspace.get(step.tag + "mlp.act", (h.shape[0], self.spec.intermediate_size), self.dtype)
-        ops.silu_mul(gu, act)
+        act = self.gate_up.swiglu(h, step, "mlp.gate_up", self.group)
         return self.down(act, step, "mlp.down")
