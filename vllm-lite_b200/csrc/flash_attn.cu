@@ -52,6 +52,12 @@ __device__ __forceinline__ void mma16816(float (&c)[4], const unsigned (&a)[4], 
                  : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
                  : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
 }
+// 2^x for x <= 0 on the special-function unit: one MUFU.EX2, no range fix-ups (x = -inf gives 0).
+__device__ __forceinline__ float exp2_mufu(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
 __device__ __forceinline__ unsigned pack_bf16(float lo, float hi) {
     __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
     return *reinterpret_cast<unsigned*>(&v);
@@ -161,33 +167,36 @@ flash_prefill_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restrict_
                 mma16816(s[2 * np + 1], qf[ks], kb[2], kb[3]);
             }
         }
-        // mask and online softmax (scores are kept in units of log2: s * scale * log2(e))
+        // mask and online softmax.  The running maximum is kept in units of log2 (score * scale * log2 e);
+        // the scale is applied inside the exponent: p = 2^(s * scale_log2 - base).
         const int j_base = kt * BN + 2 * t;
         const bool need_mask = (kt * BN + BN - 1 > pos0 + row0) || (window > 0) || !row_a || !row_b;
         float mx[2] = {-INFINITY, -INFINITY};
+        if (need_mask) {
 #pragma unroll
-        for (int n = 0; n < BN / 8; ++n) {
+            for (int n = 0; n < BN / 8; ++n) {
 #pragma unroll
-            for (int e = 0; e < 4; ++e) {
-                float v = s[n][e] * scale_log2;
-                if (need_mask) {
+                for (int e = 0; e < 4; ++e) {
                     const int j = j_base + n * 8 + (e & 1);
                     const int p = (e < 2) ? pos_a : pos_b;
                     const bool rv = (e < 2) ? row_a : row_b;
-                    if (!rv || j > p || (window > 0 && j <= p - window)) v = -INFINITY;
+                    if (!rv || j > p || (window > 0 && j <= p - window)) s[n][e] = -INFINITY;
                 }
-                s[n][e] = v;
-                mx[e >> 1] = fmaxf(mx[e >> 1], v);
             }
+        }
+#pragma unroll
+        for (int n = 0; n < BN / 8; ++n) {
+            mx[0] = fmaxf(mx[0], fmaxf(s[n][0], s[n][1]));
+            mx[1] = fmaxf(mx[1], fmaxf(s[n][2], s[n][3]));
         }
         float corr[2], base[2];
 #pragma unroll
         for (int r = 0; r < 2; ++r) {
             mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 1));
             mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 2));
-            const float mn = fmaxf(m_run[r], mx[r]);
-            base[r] = (mn == -INFINITY) ? 0.f : mn;              // a row with no key yet: exp2(-inf - 0) = 0
-            corr[r] = exp2f(m_run[r] - base[r]);
+            const float mn = fmaxf(m_run[r], mx[r] * scale_log2);       // scale_log2 > 0 keeps the order
+            base[r] = (mn == -INFINITY) ? 0.f : mn;              // a row with no key yet: 2^(-inf - 0) = 0
+            corr[r] = exp2_mufu(m_run[r] - base[r]);
             m_run[r] = mn;
             l_run[r] *= corr[r];
         }
@@ -195,8 +204,8 @@ flash_prefill_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restrict_
         unsigned pf[BN / 16][4];
 #pragma unroll
         for (int n = 0; n < BN / 8; ++n) {
-            const float p0 = exp2f(s[n][0] - base[0]), p1 = exp2f(s[n][1] - base[0]);
-            const float p2 = exp2f(s[n][2] - base[1]), p3 = exp2f(s[n][3] - base[1]);
+            const float p0 = exp2_mufu(fmaf(s[n][0], scale_log2, -base[0])), p1 = exp2_mufu(fmaf(s[n][1], scale_log2, -base[0]));
+            const float p2 = exp2_mufu(fmaf(s[n][2], scale_log2, -base[1])), p3 = exp2_mufu(fmaf(s[n][3], scale_log2, -base[1]));
             ls[0] += p0 + p1;
             ls[1] += p2 + p3;
             pf[n >> 1][(n & 1) * 2] = pack_bf16(p0, p1);
@@ -204,9 +213,12 @@ flash_prefill_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restrict_
         }
         l_run[0] += ls[0];
         l_run[1] += ls[1];
+        // once the maxima have settled the correction is 1 for every row of the warp: skip the rescale
+        if (__any_sync(0xffffffffu, corr[0] != 1.f || corr[1] != 1.f)) {
 #pragma unroll
-        for (int d = 0; d < DTILES; ++d) {
-            o[d][0] *= corr[0]; o[d][1] *= corr[0]; o[d][2] *= corr[1]; o[d][3] *= corr[1];
+            for (int d = 0; d < DTILES; ++d) {
+                o[d][0] *= corr[0]; o[d][1] *= corr[0]; o[d][2] *= corr[1]; o[d][3] *= corr[1];
+            }
         }
 #pragma unroll
         for (int kb16 = 0; kb16 < BN / 16; ++kb16) {
@@ -358,16 +370,16 @@ flash_decode_kernel(const bf16* __restrict__ q, int q_stride,
             mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 2));
             const float mn = fmaxf(m_run[r], mx[r]);
             base[r] = (mn == -INFINITY) ? 0.f : mn;
-            corr[r] = exp2f(m_run[r] - base[r]);
+            corr[r] = exp2_mufu(m_run[r] - base[r]);
             m_run[r] = mn;
             l_run[r] *= corr[r];
         }
         unsigned pf[4];
         {
-            const float p00 = exp2f(s[0][0] - base[0]), p01 = exp2f(s[0][1] - base[0]);
-            const float p02 = exp2f(s[0][2] - base[1]), p03 = exp2f(s[0][3] - base[1]);
-            const float p10 = exp2f(s[1][0] - base[0]), p11 = exp2f(s[1][1] - base[0]);
-            const float p12 = exp2f(s[1][2] - base[1]), p13 = exp2f(s[1][3] - base[1]);
+            const float p00 = exp2_mufu(s[0][0] - base[0]), p01 = exp2_mufu(s[0][1] - base[0]);
+            const float p02 = exp2_mufu(s[0][2] - base[1]), p03 = exp2_mufu(s[0][3] - base[1]);
+            const float p10 = exp2_mufu(s[1][0] - base[0]), p11 = exp2_mufu(s[1][1] - base[0]);
+            const float p12 = exp2_mufu(s[1][2] - base[1]), p13 = exp2_mufu(s[1][3] - base[1]);
             l_run[0] += p00 + p01 + p10 + p11;
             l_run[1] += p02 + p03 + p12 + p13;
             pf[0] = pack_bf16(p00, p01); pf[1] = pack_bf16(p02, p03);
@@ -411,7 +423,7 @@ flash_decode_kernel(const bf16* __restrict__ q, int q_stride,
         float acc = 0.f, L = 0.f;
 #pragma unroll
         for (int w = 0; w < 4; ++w) {
-            const float wgt = (s_m[w][r] == -INFINITY) ? 0.f : exp2f(s_m[w][r] - M);
+            const float wgt = (s_m[w][r] == -INFINITY) ? 0.f : exp2_mufu(s_m[w][r] - M);
             acc += sO[((size_t)w * DEC_ROWS + r) * OLD + e] * wgt;
             L += s_l[w][r] * wgt;
         }
