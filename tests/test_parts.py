@@ -46,6 +46,66 @@ def test_norm_and_feed_forward_alone(dtype):
     assert torch.allclose(out.float().cpu(), ref, **tol)
 
 
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("window", [None, 9])
+def test_attention_and_block_alone(dtype, window):
+    """The attention mixer (with its norm and rotary parts) and a whole pre-norm block, built from
+    descriptions of their own at sizes of no model, stepped over pages as a prompt portion, a
+    continuation and single tokens, against the plain functions on the whole sequence."""
+    from vllm_lite_b200.cache import PagedKV
+    from vllm_lite_b200.parts import BLOCKS, MIXERS
+    from vllm_lite_b200.parts.base import BuildContext, CallCache, GroupView, Residual
+    from vllm_lite_b200.parts.spec import AttentionSpec, BlockSpec, NormSpec, RotarySpec, SwiGLUSpec
+    torch.manual_seed(5)
+    hidden, nq, nkv, hd, inter, page, theta, eps = 56, 6, 3, 48, 72, 4, 5000.0, 1e-4
+    att = AttentionSpec(hidden, nq, nkv, hd, qk_norm=NormSpec(hd, 2e-5), position=RotarySpec(hd, theta), window=window)
+    spec = BlockSpec(mixer=att, ffn=SwiGLUSpec(hidden, inter), norm1=NormSpec(hidden, eps), norm2=NormSpec(hidden, eps))
+    assert MIXERS.get("gqa_attention").cache_need(att) == PagedKV(nkv, hd, window)
+    decl = BLOCKS.get("pre_norm").declare(spec)
+    assert decl["self_attn.q_proj.weight"].shape == (nq * hd, hidden) and decl["self_attn.k_norm.weight"].shape == (hd,)
+    w = {k: ((1 + 0.1 * torch.randn(d.shape)) if d.init == "norm" else torch.randn(d.shape) * 0.08).to(dtype)
+         for k, d in decl.items()}
+    ctx = BuildContext(torch.device(DEV), dtype)
+    block = BLOCKS.get("pre_norm")(spec, {k: v.to(DEV) for k, v in w.items()}, ctx)
+    n = 23
+    x0 = torch.randn(n, hidden)
+    # plain: the block on the whole sequence
+    wf = {"L." + k: v.float() for k, v in w.items()}
+    cfg = dict(num_attention_heads=nq, num_key_value_heads=nkv, head_dim=hd, rms_norm_eps=eps, rope_theta=theta)
+    h = P.rms_norm(x0, wf["L.input_layernorm.weight"], eps)
+    q = P.rope(P.head_norm(P.linear(h, wf["L.self_attn.q_proj.weight"]).view(n, nq, hd), wf["L.self_attn.q_norm.weight"], 2e-5), range(n), theta)
+    k = P.rope(P.head_norm(P.linear(h, wf["L.self_attn.k_proj.weight"]).view(n, nkv, hd), wf["L.self_attn.k_norm.weight"], 2e-5), range(n), theta)
+    v = P.linear(h, wf["L.self_attn.v_proj.weight"]).view(n, nkv, hd)
+    a_ref = P.linear(P.causal_attention(q, k, v, window=window).reshape(n, nq * hd), wf["L.self_attn.o_proj.weight"])
+    x1 = x0 + a_ref
+    ref = x1 + P.swiglu(P.rms_norm(x1, wf["L.post_attention_layernorm.weight"], eps), wf, "L.")
+    # engine parts: portions of 9, 2, then single tokens, pages in shuffled order
+    pages = 8
+    kc = torch.zeros(pages, nkv, page, hd, device=DEV, dtype=dtype)
+    vc = torch.zeros_like(kc)
+    table = torch.tensor([[5, 2, 7, 0, 3, 6]], dtype=torch.int32, device=DEV)
+    cache = CallCache(group=0, k=kc, v=vc, writes=True)
+    outs, attn_outs, start = [], [], 0
+    for count in [9, 2] + [1] * 12:
+        pos = torch.arange(start, start + count, dtype=torch.int32, device=DEV)
+        slots = (table[0, (pos // page).long()] * page + pos % page).to(torch.int32)
+        step = make_step(None, count)
+        step.positions, step.req_index = pos, torch.zeros(count, dtype=torch.int32, device=DEV)
+        step.groups = [GroupView(page, table, slots, max_context=start + count)]
+        step.max_query_len = count
+        step.query_tiles = torch.tensor([[0, 0, count, start]], dtype=torch.int32, device=DEV)
+        res = Residual(x0[start:start + count].to(DEV).contiguous())
+        hh = block.norm1(res.x, None, step, tag="n1")
+        attn_outs.append(block.mixer(hh, step, cache).float().cpu())
+        res2 = Residual(x0[start:start + count].to(DEV).contiguous())
+        block(res2, step, cache)                                   # the whole block (writes the same cache rows again)
+        outs.append((res2.x + res2.pending.float()).cpu())
+        start += count
+    tol = dict(atol=2e-5, rtol=1e-4) if dtype == torch.float32 else dict(atol=4e-2, rtol=4e-2)
+    assert torch.allclose(torch.cat(attn_outs), a_ref, **tol)
+    assert torch.allclose(torch.cat(outs), ref, **tol)
+
+
 def plain_with_order(cfg, w, ids, order, share):
     """The plain model with a running order: layer indices, and for each call whether it
     reuses the keys/values of an earlier call (then only its queries are its own)."""
@@ -91,6 +151,79 @@ def test_order_may_repeat_a_layer_and_share_a_cache():
     runner.check_device_errors()
     assert float((got - ref).abs().max()) <= H.TOL["float32"] * float(ref.abs().max())
     assert not torch.allclose(ref, P.forward(cfg, w, toks), atol=1e-3)   # the order matters
+
+
+def plain_with_windows(cfg, w, ids, windows):
+    """The plain model with a window per layer (None: every earlier key)."""
+    cfg = P.normalise_config(cfg)
+    n = len(ids)
+    pos = list(range(n))
+    nq, nkv, d, eps = cfg["num_attention_heads"], cfg["num_key_value_heads"], cfg["head_dim"], cfg["rms_norm_eps"]
+    x = P.embedding(ids, w["model.embed_tokens.weight"])
+    for layer, window in enumerate(windows):
+        pre = f"model.layers.{layer}."
+        h = P.rms_norm(x, w[pre + "input_layernorm.weight"], eps)
+        q = P.rope(P.head_norm(P.linear(h, w[pre + "self_attn.q_proj.weight"]).view(n, nq, d), w[pre + "self_attn.q_norm.weight"], eps), pos, cfg["rope_theta"])
+        k = P.rope(P.head_norm(P.linear(h, w[pre + "self_attn.k_proj.weight"]).view(n, nkv, d), w[pre + "self_attn.k_norm.weight"], eps), pos, cfg["rope_theta"])
+        v = P.linear(h, w[pre + "self_attn.v_proj.weight"]).view(n, nkv, d)
+        x = x + P.linear(P.causal_attention(q, k, v, window=window).reshape(n, nq * d), w[pre + "self_attn.o_proj.weight"])
+        x = x + P.swiglu(P.rms_norm(x, w[pre + "post_attention_layernorm.weight"], eps), w, pre)
+    head = w["model.embed_tokens.weight"] if cfg.get("tie_word_embeddings") else w["lm_head.weight"]
+    return P.linear(P.rms_norm(x, w["model.norm.weight"], eps), head)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_layers_with_a_window_get_pages_of_their_own_and_give_them_back(dtype):
+    """A toy architecture over the tiny B weights: layers 0 and 2 read every key, layer 1 the last 20.
+    The windowed layer's group has a pool so small that it only works if pages behind the window
+    return; logits still match the plain implementation at every position."""
+    import dataclasses
+    from vllm_lite_b200.config import Qwen3Config, plan_from_config_json, register_architecture, unregister_architecture
+    from vllm_lite_b200.engine import ModelRunner, load_model_dir
+    from vllm_lite_b200.parts.spec import ModelPlan
+    window = 20
+
+    def plan(cfg):
+        base = plan_from_config_json({**H.TINY_B, "architectures": ["Qwen3ForCausalLM"]})[1]
+        layers = list(base.layers)
+        layers[1] = dataclasses.replace(layers[1], mixer=dataclasses.replace(layers[1].mixer, window=window))
+        return ModelPlan(**{**base.__dict__, "architecture": "ToyWindowLM", "layers": tuple(layers)})
+
+    register_architecture("ToyWindowLM", Qwen3Config, plan)
+    try:
+        import json, shutil
+        d = H.tmp_root() / "toy_window"
+        shutil.copytree(H.model_dir("B"), d, dirs_exist_ok=True)
+        (d / "config.json").write_text(json.dumps({**H.TINY_B, "architectures": ["ToyWindowLM"]}))
+        _, p, weights = load_model_dir(d, dtype, DEV)
+        page = 8
+        # 150 tokens need 19 pages in the full group; the windowed group gets 7: (20 + 17 + 8) / 8 rounded up
+        runner = ModelRunner(p, weights, dtype=torch.bfloat16 if dtype == "bfloat16" else torch.float32, device=DEV,
+                             page_size=page, num_pages=[19, 7], max_requests=2)
+        assert [g.window for g in runner.layout.paged_groups] == [None, window]
+        assert runner.layout.paged_members == [[0, 2], [1]]
+        toks = H.tokens_for("B", 150, 77)
+        schedule, pos = [], 0
+        for n in [17, 2, 9, 1, 1, 16, 3] + [1] * 40 + [11, 2] + [1] * 100:
+            n = min(n, 150 - pos)
+            if n <= 0:
+                break
+            schedule.append(([("r", toks[pos:pos + n], list(range(n)))], []))
+            pos += n
+        assert pos == 150
+        rows = H.run_schedule(runner, schedule)
+        cfg, w = H.plain_model("B")
+        ref = plain_with_windows(cfg, w, toks, [None, window, None])
+        assert not torch.allclose(ref, H.plain_logits("B", toks), atol=1e-3)          # the window matters
+        for (rid, i), row in rows.items():
+            err = float((row - ref[i]).abs().max()) / float(ref[i].abs().max())
+            assert err <= H.TOL[dtype], (i, err)
+        held = [sum(pg >= 0 for pg in t) for t in runner.cache.requests["r"].block_tables]
+        assert held[0] == 19 and held[1] <= 4
+        runner.release("r")
+        assert runner.cache.free_pages() == [19, 7]
+    finally:
+        unregister_architecture("ToyWindowLM")
 
 
 # ---- a toy mixer with state of its own, defined here ---------------------------------
