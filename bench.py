@@ -28,6 +28,8 @@ QWEN3_8B = dict(architectures=["Qwen3ForCausalLM"], model_type="qwen3", hidden_s
                 num_attention_heads=32, num_key_value_heads=8, head_dim=128, intermediate_size=12288,
                 vocab_size=151936, rope_theta=1000000.0, rms_norm_eps=1e-6, tie_word_embeddings=False,
                 max_position_embeddings=40960)
+# the other dense sizes of the architecture (layers, hidden, heads, intermediate); kv heads 8, head_dim 128
+SIZES = {"8b": (36, 4096, 32, 12288), "14b": (40, 5120, 40, 17408), "32b": (64, 5120, 64, 25600)}
 METRIC = "decode tok/s at batch 8 (Qwen3-8B, bf16)"
 PREFILL_TOKENS = 2048
 
@@ -195,7 +197,8 @@ def main(argv=None):
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--context", type=int, default=4096)
-    ap.add_argument("--layers", type=int, default=QWEN3_8B["num_hidden_layers"])
+    ap.add_argument("--size", default="8b", choices=sorted(SIZES), help="layer sizes of Qwen3-8B (default), 14B or 32B")
+    ap.add_argument("--layers", type=int, default=None, help="fewer layers than the size has (both numbers are reported)")
     ap.add_argument("--no-points", action="store_true", help="skip the batch 1 / 64 points and the prefill")
     ap.add_argument("--only-prefill", action="store_true", help="time the 2,048-token prefill alone (for profiling)")
     ap.add_argument("--no-e2e", action="store_true", help="skip the run through the Python entry point (for profiling)")
@@ -212,7 +215,11 @@ def main(argv=None):
     import torch
     from vllm_lite_b200.csrc import ops
     from vllm_lite_b200.engine import LLMEngine, random_model
-    cfg = dict(QWEN3_8B, num_hidden_layers=args.layers)
+    full_layers, hidden, heads, inter = SIZES[args.size]
+    if args.layers is None:
+        args.layers = full_layers
+    cfg = dict(QWEN3_8B, num_hidden_layers=args.layers, hidden_size=hidden, num_attention_heads=heads,
+               intermediate_size=inter)
     vocab = cfg["vocab_size"]
     _, plan, weights = random_model(cfg, seed=0, dtype="bfloat16", device="cuda:0")
     big = args.batch if args.no_points else max(args.batch, 64)
@@ -243,14 +250,14 @@ def main(argv=None):
     step_bytes = weight_bytes + args.batch * mean_ctx * kv_per_token
     achieved = step_bytes / (ms * 1e-3) / 1e9
     out = {
-        "metric": METRIC, "value": round(value, 1), "unit": "tokens/s", "n_gpus": 1, "steps": args.steps,
+        "metric": METRIC.replace("8B", args.size.upper()), "value": round(value, 1), "unit": "tokens/s", "n_gpus": 1, "steps": args.steps,
         "warmup": warmup, "ms_per_step": round(ms, 4), "higher_is_better": True, "scaling": "weak",
         "vs_baseline": None, "dtype": "bf16", "data": "synthetic (random weights N(0,0.02), uniform token ids)",
-        "config": {"model": "Qwen3-8B layer sizes", "layers": args.layers, "layers_full": QWEN3_8B["num_hidden_layers"],
+        "config": {"model": f"Qwen3-{args.size.upper()} layer sizes", "layers": args.layers, "layers_full": full_layers,
                    "hidden": cfg["hidden_size"], "heads": cfg["num_attention_heads"], "kv_heads": cfg["num_key_value_heads"],
                    "head_dim": cfg["head_dim"], "intermediate": cfg["intermediate_size"], "vocab": vocab,
                    "global_batch": args.batch, "seq_len": args.context, "block_size": 16, "parallelism": "single GPU",
-                   "kv_fill": "real prefill" if args.kv_fill == "prefill" else "random numbers", "l2": "inputs (weights 16 GB) larger than L2, no flush",
+                   "kv_fill": "real prefill" if args.kv_fill == "prefill" else "random numbers", "l2": f"inputs (weights {weight_bytes / 1e9:.0f} GB) larger than L2, no flush",
                    "peaks": pk["source"]},
         "clocks": clocks.summary(w0, w1),
         "e2e": None if args.no_e2e else {"value": round(e2e_tps, 1), "unit": "tokens/s", "h2d_bytes_per_step": int(h2d),

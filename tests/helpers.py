@@ -65,12 +65,12 @@ def plain_logits(which: str, tokens) -> torch.Tensor:
     return _plain_cache[key]
 
 
-def make_runner(which: str, dtype: str, num_pages: int, page_size=None, max_requests=8):
+def make_runner(which: str, dtype: str, num_pages: int, page_size=None, max_requests=8, native_host=True):
     from vllm_lite_b200.engine import ModelRunner, load_model_dir
     _, plan, weights = load_model_dir(model_dir(which), dtype, "cuda:0")
     return ModelRunner(plan, weights, dtype=torch.bfloat16 if dtype == "bfloat16" else torch.float32,
                        device="cuda:0", page_size=page_size or TINY[which]["page_size"], num_pages=num_pages,
-                       max_requests=max_requests)
+                       max_requests=max_requests, native_host=native_host)
 
 
 def run_schedule(runner, schedule):

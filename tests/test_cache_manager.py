@@ -1,10 +1,18 @@
 """The cache manager on the host: no page lost, held twice or freed twice, under
-random orders of requests; windows give pages back; slots for fixed state (no GPU)."""
+random orders of requests; windows give pages back; slots for fixed state (no GPU).
+Every test runs on the Python implementation and on the C++ core."""
 import random
 
 import pytest
 
 from vllm_lite_b200.cache import CacheLayout, CacheManager, FixedState, OutOfPages, PagedKV, Pool, PoolError
+from vllm_lite_b200.cache.native import NativeCacheManager
+
+
+@pytest.fixture(params=["python", "native"])
+def make(request):
+    """Both implementations of the bookkeeping: the Python reference and the C++ core."""
+    return CacheManager if request.param == "python" else NativeCacheManager
 
 
 def layout(*needs, cache_of=None):
@@ -44,8 +52,8 @@ def test_layers_with_equal_needs_share_a_group_others_get_their_own():
     assert shared.call_place[1] == ("paged", 0, 0, False)
 
 
-def test_pages_are_taken_when_written_and_returned_at_the_end():
-    m = CacheManager(layout(PagedKV(2, 16)), page_size=8, num_pages=6, max_requests=2)
+def test_pages_are_taken_when_written_and_returned_at_the_end(make):
+    m = make(layout(PagedKV(2, 16)), page_size=8, num_pages=6, max_requests=2)
     m.admit("a")
     assert m.append("a", 5) == 0 and m.requests["a"].block_tables == [[0]]
     assert m.append("a", 3) == 5 and m.requests["a"].block_tables == [[0]]      # still the first page
@@ -69,8 +77,8 @@ def test_pages_are_taken_when_written_and_returned_at_the_end():
         m.free("a")
 
 
-def test_window_gives_pages_back_once_it_has_passed_them():
-    m = CacheManager(layout(PagedKV(1, 16), PagedKV(1, 16, window=10)), page_size=4, num_pages=[16, 5], max_requests=1)
+def test_window_gives_pages_back_once_it_has_passed_them(make):
+    m = make(layout(PagedKV(1, 16), PagedKV(1, 16, window=10)), page_size=4, num_pages=[16, 5], max_requests=1)
     m.admit("r")
     m.append("r", 9)
     assert m.release_behind_window("r") == 0          # next query at 9 reads 0..9
@@ -90,8 +98,8 @@ def test_window_gives_pages_back_once_it_has_passed_them():
     assert m.free_pages() == [16, 5]
 
 
-def test_growth_is_all_groups_or_none():
-    m = CacheManager(layout(PagedKV(1, 16), PagedKV(2, 32)), page_size=4, num_pages=[8, 2], max_requests=1)
+def test_growth_is_all_groups_or_none(make):
+    m = make(layout(PagedKV(1, 16), PagedKV(2, 32)), page_size=4, num_pages=[8, 2], max_requests=1)
     m.admit("r")
     m.append("r", 8)
     with pytest.raises(OutOfPages):
@@ -99,8 +107,8 @@ def test_growth_is_all_groups_or_none():
     assert m.free_pages() == [6, 0] and m.requests["r"].num_tokens == 8
 
 
-def test_state_slots_are_fresh_once():
-    m = CacheManager(layout(FixedState((3,))), page_size=16, num_pages=0, max_requests=2)
+def test_state_slots_are_fresh_once(make):
+    m = make(layout(FixedState((3,))), page_size=16, num_pages=0, max_requests=2)
     a, b = m.admit("a"), m.admit("b")
     assert {a.state_slot, b.state_slot} == {0, 1} and sorted(m.take_fresh_slots()) == [0, 1]
     assert m.take_fresh_slots() == []
@@ -109,9 +117,9 @@ def test_state_slots_are_fresh_once():
 
 
 @pytest.mark.parametrize("seed", range(8))
-def test_random_orders_keep_the_books(seed):
+def test_random_orders_keep_the_books(make, seed):
     rng = random.Random(seed)
-    m = CacheManager(layout(PagedKV(2, 16), PagedKV(2, 16, window=24)), page_size=8, num_pages=[40, 14], max_requests=5)
+    m = make(layout(PagedKV(2, 16), PagedKV(2, 16, window=24)), page_size=8, num_pages=[40, 14], max_requests=5)
     live, n = {}, 0
     for _ in range(600):
         roll = rng.random()

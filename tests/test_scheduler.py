@@ -5,13 +5,23 @@ import random
 import pytest
 
 from vllm_lite_b200.cache import CacheLayout, CacheManager, PagedKV
+from vllm_lite_b200.cache.native import NativeCacheManager
+
+BACKEND = {"cls": CacheManager}
+
+
+@pytest.fixture(autouse=True, params=["python", "native"])
+def cache_backend(request):
+    """Every test runs with the Python cache manager and with the C++ core under the scheduler."""
+    BACKEND["cls"] = CacheManager if request.param == "python" else NativeCacheManager
+    yield
 from vllm_lite_b200.engine.scheduler import AdmissionError, Scheduler, SchedulerConfig
 from vllm_lite_b200.sampling import SamplingParams
 
 
 def make(num_pages=64, page_size=4, max_requests=8, **cfg):
     lay = CacheLayout.from_needs([PagedKV(2, 16)], [None])
-    cache = CacheManager(lay, page_size, num_pages, max_requests)
+    cache = BACKEND["cls"](lay, page_size, num_pages, max_requests)
     return cache, Scheduler(cache, SchedulerConfig(**cfg))
 
 

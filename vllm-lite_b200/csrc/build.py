@@ -125,6 +125,64 @@ def _compile(name: str, out: Path, stem: str, defines=None) -> Path:
     return out
 
 
+# ---- host-only C++ (no CUDA): csrc/host/<name>.cpp ------------------------------------------------
+HOST_SOURCES = ("cache_core",)
+HOST_FLAGS = ["-O2", "-std=c++17", "-shared", "-fPIC"]
+
+
+def find_cxx() -> str:
+    for cand in (os.environ.get("CXX"), shutil.which("g++"), shutil.which("c++"), shutil.which("clang++")):
+        if cand and os.path.isfile(cand) and os.access(cand, os.X_OK):
+            return cand
+    raise BuildError("no C++ compiler found (looked at $CXX, g++, c++, clang++)")
+
+
+def host_library_path(name: str) -> Path:
+    src = CSRC / "host" / f"{name}.cpp"
+    if not src.is_file():
+        raise BuildError(f"no C++ source {src}")
+    h = hashlib.sha256(src.read_bytes())
+    h.update(" ".join(HOST_FLAGS).encode())
+    fname = f"host_{name}.{h.hexdigest()[:12]}.so"
+    for d in _build_dirs():
+        if (d / fname).is_file():
+            return d / fname
+    last = None
+    for d in _build_dirs():
+        try:
+            d.mkdir(parents=True, exist_ok=True)
+            if not os.access(d, os.W_OK):
+                continue
+            out = d / fname
+            tmp = out.with_suffix(f".tmp{os.getpid()}.so")
+            _say(f"compiling host/{name}.cpp ...")
+            proc = subprocess.run([find_cxx()] + HOST_FLAGS + ["-o", str(tmp), str(src)], capture_output=True, text=True)
+            if proc.returncode != 0:
+                tmp.unlink(missing_ok=True)
+                raise BuildError(f"C++ compiler failed on host/{name}.cpp:\n{proc.stdout}{proc.stderr}")
+            os.replace(tmp, out)
+            for stale in d.glob(f"host_{name}.*.so"):
+                if stale != out and ".tmp" not in stale.name:
+                    try:
+                        stale.unlink()
+                    except OSError:
+                        pass
+            return out
+        except (OSError, BuildError) as e:
+            last = e
+    raise BuildError(f"could not build host/{name}.cpp: {last}")
+
+
+def load_host(name: str) -> ctypes.CDLL:
+    key = ("host", name)
+    with _lock:
+        lib = _loaded.get(key)
+        if lib is None:
+            lib = ctypes.CDLL(str(host_library_path(name)))
+            _loaded[key] = lib
+        return lib
+
+
 def load(name: str, defines=None) -> ctypes.CDLL:
     key = (name, _variant(defines))
     with _lock:
@@ -141,4 +199,6 @@ def build_all(names=SOURCES) -> dict:
     for n, variants in VARIANTS.items():
         for d in variants:
             out[f"{n}.{_variant(d)}"] = library_path(n, d)
+    for n in HOST_SOURCES:
+        out[f"host/{n}"] = host_library_path(n)
     return out

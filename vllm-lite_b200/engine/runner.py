@@ -17,6 +17,7 @@ from typing import List, Optional, Sequence
 import numpy as np
 import torch
 
+from ..cache import make_cache_manager
 from ..cache.manager import CacheLayout, CacheManager, OutOfPages
 from ..cache.storage import CacheStorage
 from ..parts.base import BuildContext, Entry, GroupView, StepBatch, Workspace
@@ -45,7 +46,7 @@ def _align4(n: int) -> int:
 class ModelRunner:
     def __init__(self, plan, weights: dict, *, dtype=torch.bfloat16, device="cuda:0", page_size: int = 16,
                  num_pages=1024, max_requests: int = 256, decode_graphs: bool = True,
-                 max_context: Optional[int] = None):
+                 max_context: Optional[int] = None, native_host: bool = True):
         self.device = torch.device(device)
         if self.device.type != "cuda":
             raise StepError("the engine runs on a CUDA device only; there is no CPU path")
@@ -57,7 +58,9 @@ class ModelRunner:
         torch.cuda.set_device(self.device)
         self.model = CausalLM(plan, weights, BuildContext(self.device, dtype))
         self.layout = CacheLayout.from_needs(cache_needs(plan), [c.cache_of for c in plan.order])
-        self.cache = CacheManager(self.layout, self.page_size, num_pages, max_requests)
+        # bookkeeping and batch packing in C++ (csrc/host/cache_core.cpp); the Python manager is the reference
+        self.native_host = bool(native_host)
+        self.cache = make_cache_manager(self.layout, self.page_size, num_pages, max_requests, native=self.native_host)
         self.storage = CacheStorage(self.layout, self.page_size, num_pages, max_requests, dtype, self.device)
         self.workspace = Workspace(self.device)
         self.err = torch.zeros(1, dtype=torch.int32, device=self.device)
@@ -176,6 +179,80 @@ class ModelRunner:
         return bucket
 
     def _layout_batch(self, entries, host_entries, bucket: int = 0) -> StepBatch:
+        if self.native_host:
+            return self._layout_native(entries, host_entries, bucket)
+        return self._layout_python(entries, host_entries, bucket)
+
+    def _pinned_slot(self, words: int):
+        """A pinned host buffer of at least `words` int32 whose last upload has completed."""
+        i = self._flip
+        self._flip ^= 1
+        if self._meta_evt[i] is not None:
+            self._meta_evt[i].synchronize()
+        if self._meta_pin[i] is None or self._meta_pin[i].numel() < words:
+            self._meta_pin[i] = torch.empty(max(words, 4096) * 2, dtype=torch.int32).pin_memory()
+        return i, self._meta_pin[i]
+
+    def _to_device(self, i: int, n: int, bucket: int) -> torch.Tensor:
+        pin = self._meta_pin[i]
+        if bucket:                                  # a graph reads its batch from a buffer of its own
+            dev = self._graph_meta.get(bucket)
+            if dev is None or dev.numel() < n:
+                dev = self._graph_meta[bucket] = torch.empty(n, dtype=torch.int32, device=self.device)
+        else:
+            if self._meta_dev is None or self._meta_dev.numel() < n:
+                self._meta_dev = torch.empty(max(n, 4096) * 2, dtype=torch.int32, device=self.device)
+            dev = self._meta_dev
+        dev[:n].copy_(pin[:n], non_blocking=True)
+        self.uploaded_bytes += 4 * n
+        if self._meta_evt[i] is None:
+            self._meta_evt[i] = torch.cuda.Event()
+        self._meta_evt[i].record()
+        return dev[:n]
+
+    def _layout_native(self, entries, host_entries, bucket: int) -> StepBatch:
+        """The C++ core packs the batch straight into pinned memory."""
+        B = len(entries)
+        counts = [h.count for h in host_entries]
+        starts = [h.start for h in host_entries]
+        if all(c == 1 for c in counts):
+            tokens = [e.tokens[0] for e in entries]
+        else:
+            tokens = np.concatenate([np.asarray(e.tokens, dtype=np.int64) for e in entries]).astype(np.int32)
+        want_offsets, wants = [0], []
+        for e in entries:
+            wants.extend(e.want)
+            want_offsets.append(len(wants))
+        ids = [e.request_id for e in entries]
+        fixed = -(-self.max_context // self.page_size) if bucket else 0
+        guess = 4096
+        while True:
+            i, pin = self._pinned_slot(guess)
+            used, off, sizes, max_blocks = self.cache.pack_step(ids, counts, starts, tokens, want_offsets, wants,
+                                                                bucket, not bucket, fixed, pin.numpy())
+            if used >= 0:
+                break
+            self._flip ^= 1                          # the slot was not used; take it again, larger
+            guess = -used
+        dev = self._to_device(i, used, bucket)
+        sec = lambda k: dev[int(off[k]):int(off[k]) + int(sizes[k])]
+        Bp = bucket or B
+        longest = max(h.start + h.count for h in host_entries)
+        if bucket:                       # a graph is recorded for a bound on the context, not for its value
+            bound = 1024
+            while bound < longest:
+                bound *= 2
+            longest = min(bound, self.max_context)
+        groups = [GroupView(page_size=self.page_size, block_table=sec(8 + 2 * g).view(Bp, int(max_blocks[g])),
+                            slots=sec(7 + 2 * g), max_context=longest) for g in range(len(self.cache.pools))]
+        tiles = sec(6)
+        return StepBatch(tokens=sec(0), positions=sec(1), req_index=sec(2), cu_seqlens=sec(3), state_slots=sec(4),
+                         logit_rows=sec(5), groups=groups, entries=host_entries, err=self.err, workspace=self.workspace,
+                         num_tokens=bucket or sum(counts), num_entries=Bp, max_query_len=max(counts),
+                         tag=f"g{bucket}.{longest}." if bucket else "", graph_bucket=bucket,
+                         query_tiles=tiles.view(-1, 4) if tiles.numel() else None)
+
+    def _layout_python(self, entries, host_entries, bucket: int = 0) -> StepBatch:
         real_B = len(entries)
         real_T = sum(h.count for h in host_entries)
         real_R = sum(len(e.want) for e in entries)
