@@ -187,3 +187,36 @@ def test_trace_run_program(dtype, tmp_path):
         for row, pos in zip(arr, positions):
             err = float(np.abs(row - ref[pos].numpy()).max()) / float(ref[pos].abs().max())
             assert err <= H.TOL[dtype], (step, pos, err)
+
+
+def test_real_layer_sizes_bfloat16_against_float32_engine():
+    """Two layers of Qwen3-8B width (hidden 4096, 32/8 heads of 128, intermediate 12288) with a small
+    vocabulary: a prompt long enough for the tcgen05 GEMM and the tensor-core attention, then decoded
+    tokens through the CUDA-graph path.  The float32 engine (bit-identical across cuts, checked against
+    the plain implementation at tiny sizes) is the reference for the bfloat16 engine here."""
+    from vllm_lite_b200.engine import ModelRunner, StepEntry, random_model
+    cfg = dict(architectures=["Qwen3ForCausalLM"], model_type="qwen3", hidden_size=4096, num_hidden_layers=2,
+               num_attention_heads=32, num_key_value_heads=8, head_dim=128, intermediate_size=12288, vocab_size=2048,
+               rope_theta=1000000.0, rms_norm_eps=1e-6, tie_word_embeddings=False, max_position_embeddings=4096)
+    toks = [int(t) for t in np.random.default_rng(5).integers(0, 2048, size=1130)]
+    rows = {}
+    for dtype in ("float32", "bfloat16"):
+        _, plan, weights = random_model(cfg, seed=3, dtype=dtype, device="cuda:0")
+        runner = ModelRunner(plan, weights, dtype=torch.float32 if dtype == "float32" else torch.bfloat16,
+                             device="cuda:0", page_size=16, num_pages=160, max_requests=2)
+        del weights
+        out = [runner.step([StepEntry("r", toks[:1100], [0, 63, 64, 1023, 1099])]).float().cpu()]
+        if dtype == "float32":                          # the same prompt cut in two gives the same bits
+            again = runner.step([StepEntry("s", toks[:700], [0, 63, 64])]).float().cpu()
+            again2 = runner.step([StepEntry("s", toks[700:1100], [323, 399])]).float().cpu()
+            assert torch.equal(torch.cat([again, again2]), out[0])
+            runner.release("s")
+        for p in range(1100, 1130):
+            out.append(runner.step([StepEntry("r", [toks[p]], [0])]).float().cpu())
+        runner.check_device_errors()
+        rows[dtype] = torch.cat(out)
+        del runner
+        torch.cuda.empty_cache()
+    ref, got = rows["float32"], rows["bfloat16"]
+    err = (got - ref).abs().amax(dim=1) / ref.abs().amax(dim=1)
+    assert float(err.max()) <= H.TOL["bfloat16"], err
