@@ -322,3 +322,149 @@ def test_toy_mixer_with_state_registers_builds_and_steps():
     finally:
         MIXERS.unregister("toy_decay")
         unregister_architecture("ToyDecayLM")
+
+
+# ---- a toy position encoding and a toy routed feed-forward, defined here -----------------------
+@dataclass(frozen=True)
+class LearnedPositionSpec:
+    head_dim: int
+    max_positions: int
+    kind: str = "toy_learned_position"
+
+
+class LearnedPosition:
+    """q_head += table[pos], k_head += table[pos]; not known to the fused kernel, so it acts by itself."""
+
+    @staticmethod
+    def declare(spec):
+        from vllm_lite_b200.parts.spec import TensorDecl
+        return {"table": TensorDecl((spec.max_positions, spec.head_dim))}
+
+    def __init__(self, spec, weights, ctx):
+        self.spec, self.table = spec, weights["table"]
+
+    def fused_rotary(self):
+        return None
+
+    def apply(self, qkv, positions, num_heads, num_kv_heads, head_dim, step):
+        T = qkv.shape[0]
+        qk = qkv[:, :(num_heads + num_kv_heads) * head_dim].view(T, num_heads + num_kv_heads, head_dim)
+        add = self.table[positions.long().clamp(min=0)].to(qkv.dtype)
+        qk += add[:, None, :]
+
+
+@dataclass(frozen=True)
+class RoutedSpec:
+    hidden_size: int
+    intermediate_size: int
+    num_experts: int
+    kind: str = "toy_routed"
+
+
+class RoutedFeedForward:
+    """Top-1 routing: e = argmax(softmax(h R^T)); y = p_e * W2[e] relu(W1[e] h).  Router in float32."""
+
+    @staticmethod
+    def declare(spec):
+        from vllm_lite_b200.parts.spec import TensorDecl
+        d = {"router.weight": TensorDecl((spec.num_experts, spec.hidden_size))}
+        for e in range(spec.num_experts):
+            d[f"experts.{e}.w1.weight"] = TensorDecl((spec.intermediate_size, spec.hidden_size))
+            d[f"experts.{e}.w2.weight"] = TensorDecl((spec.hidden_size, spec.intermediate_size))
+        return d
+
+    def __init__(self, spec, weights, ctx):
+        self.spec, self.w, self.dtype = spec, {k: v.float() for k, v in weights.items()}, ctx.dtype
+
+    def __call__(self, h, step):
+        return routed_reference(h.float(), self.w, self.spec.num_experts, "").to(self.dtype)
+
+
+def routed_reference(h, w, num_experts, prefix):
+    probs = torch.softmax(h @ w[prefix + "router.weight"].T, dim=-1)
+    p, e = probs.max(dim=-1)
+    out = torch.zeros_like(h)
+    for k in range(num_experts):
+        rows = (e == k).nonzero().flatten()
+        if rows.numel():
+            hid = torch.relu(h[rows] @ w[prefix + f"experts.{k}.w1.weight"].T)
+            out[rows] = p[rows, None] * (hid @ w[prefix + f"experts.{k}.w2.weight"].T)
+    return out
+
+
+def plain_toy_mix(cfg, w, ids, rotary_dim, num_experts):
+    """Layer 0: attention with learned positions (no rotation) and the routed feed-forward;
+    layer 1: attention rotating only the first `rotary_dim` features of each head, SwiGLU."""
+    cfg = P.normalise_config(cfg)
+    n = len(ids)
+    pos = list(range(n))
+    nq, nkv, d, eps = cfg["num_attention_heads"], cfg["num_key_value_heads"], cfg["head_dim"], cfg["rms_norm_eps"]
+    x = P.embedding(ids, w["model.embed_tokens.weight"])
+    for layer in range(2):
+        pre = f"model.layers.{layer}."
+        h = P.rms_norm(x, w[pre + "input_layernorm.weight"], eps)
+        q = P.linear(h, w[pre + "self_attn.q_proj.weight"]).view(n, nq, d)
+        k = P.linear(h, w[pre + "self_attn.k_proj.weight"]).view(n, nkv, d)
+        v = P.linear(h, w[pre + "self_attn.v_proj.weight"]).view(n, nkv, d)
+        if layer == 0:
+            table = w[pre + "self_attn.rotary.table"][:n]
+            q, k = q + table[:, None, :], k + table[:, None, :]
+        q, k = P.head_norm(q, w[pre + "self_attn.q_norm.weight"], eps), P.head_norm(k, w[pre + "self_attn.k_norm.weight"], eps)
+        if layer == 1:
+            q = torch.cat([P.rope(q[..., :rotary_dim], pos, cfg["rope_theta"]), q[..., rotary_dim:]], dim=-1)
+            k = torch.cat([P.rope(k[..., :rotary_dim], pos, cfg["rope_theta"]), k[..., rotary_dim:]], dim=-1)
+        x = x + P.linear(P.causal_attention(q, k, v).reshape(n, nq * d), w[pre + "self_attn.o_proj.weight"])
+        h = P.rms_norm(x, w[pre + "post_attention_layernorm.weight"], eps)
+        x = x + (routed_reference(h, w, num_experts, pre + "mlp.") if layer == 0 else P.swiglu(h, w, pre))
+    return P.linear(P.rms_norm(x, w["model.norm.weight"], eps), w["model.embed_tokens.weight"])
+
+
+def test_toy_position_encoding_and_routed_feed_forward_register_and_step():
+    import dataclasses, json
+    from vllm_lite_b200.config import Qwen3Config, plan_from_config_json, register_architecture, unregister_architecture
+    from vllm_lite_b200.engine import ModelRunner, load_model_dir
+    from vllm_lite_b200.parts import FEED_FORWARDS, POSITIONS, declare_model
+    from vllm_lite_b200.parts.spec import ModelPlan, RotarySpec
+    from vllm_lite_b200.weights import random_tensors, write_safetensors
+    experts, rotary_dim = 3, 8
+
+    def plan(cfg):
+        base = plan_from_config_json({**H.TINY_A, "architectures": ["Qwen3ForCausalLM"]})[1]
+        l0, l1 = base.layers
+        l0 = dataclasses.replace(l0, mixer=dataclasses.replace(l0.mixer, position=LearnedPositionSpec(cfg.head_dim, 64)),
+                                 ffn=RoutedSpec(cfg.hidden_size, 40, experts))
+        l1 = dataclasses.replace(l1, mixer=dataclasses.replace(
+            l1.mixer, position=RotarySpec(cfg.head_dim, cfg.rope_theta, rotary_dim=rotary_dim)))
+        return ModelPlan(**{**base.__dict__, "architecture": "ToyMixLM", "layers": (l0, l1)})
+
+    POSITIONS.register("toy_learned_position", LearnedPosition)
+    FEED_FORWARDS.register("toy_routed", RoutedFeedForward)
+    register_architecture("ToyMixLM", Qwen3Config, plan)
+    try:
+        cfg_json = {**H.TINY_A, "architectures": ["ToyMixLM"]}
+        d = H.tmp_root() / "toy_mix"
+        d.mkdir(exist_ok=True)
+        (d / "config.json").write_text(json.dumps(cfg_json))
+        _, p = plan_from_config_json(cfg_json)
+        decl = declare_model(p)
+        assert "model.layers.0.self_attn.rotary.table" in decl and "model.layers.0.mlp.experts.2.w2.weight" in decl
+        assert "model.layers.0.mlp.gate_proj.weight" not in decl and "model.layers.1.mlp.gate_proj.weight" in decl
+        write_safetensors(d / "model.safetensors", random_tensors(decl, 9, std=0.08))
+        _, p, weights = load_model_dir(d, "float32", DEV)
+        runner = ModelRunner(p, weights, dtype=torch.float32, device=DEV, page_size=16, num_pages=8, max_requests=3)
+        assert not runner.decode_graphs                      # the toy feed-forward did not declare itself graph safe
+        a, b = H.tokens_for("A", 41, 3), H.tokens_for("A", 14, 4)
+        cfg, w = P.read_model_dir(d)
+        ref = {"a": plain_toy_mix(cfg, w, a, rotary_dim, experts), "b": plain_toy_mix(cfg, w, b, rotary_dim, experts)}
+        rows = H.run_schedule(runner, [
+            ([("a", a[:19], list(range(19)))], []),
+            ([("a", a[19:21], [0, 1]), ("b", b, list(range(14)))], ["b"]),
+            ([("a", a[21:22], [0])], []),
+            ([("a", a[22:], list(range(19)))], ["a"]),
+        ])
+        for (rid, pos), row in rows.items():
+            assert float((row - ref[rid][pos]).abs().max()) <= 5e-5 * float(ref[rid].abs().max()), (rid, pos)
+    finally:
+        POSITIONS.unregister("toy_learned_position")
+        FEED_FORWARDS.unregister("toy_routed")
+        unregister_architecture("ToyMixLM")

@@ -70,7 +70,9 @@ class GqaAttention:
         qkv = self.qkv_proj(h, step, "attn.qkv")
         fused = self.position.fused_rotary() if self.position is not None else None
         if self.position is not None and fused is None:
-            raise NotImplementedError("a position encoding without fused_rotary() must be applied by its own kernel")
+            # an encoding that the fused kernel does not know acts on the q and k parts of qkv itself
+            # (after the projections, before the head norm's kernel writes the cache)
+            self.position.apply(qkv, step.positions, s.num_heads, s.num_kv_heads, s.head_dim, step)
         inv_freq, rot = fused if fused is not None else (None, 0)
         ops.qk_norm_rope_write(
             qkv, step.positions, group.slots if cache.writes else None,

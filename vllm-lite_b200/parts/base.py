@@ -7,8 +7,9 @@ Interfaces (duck-typed; a part is any class registered under its kind):
   norm           __call__(x, delta, step, rows=None) -> h
                      x float32 [T, H] residual stream; delta (activation dtype) or None is
                      added into x first (not stored when `rows` picks rows); h is new
-  position       fused_rotary() -> (inv_freq, rotary_dim) or None
-                 apply(qkv, positions, num_heads, num_kv_heads, head_dim, step)  when not fused
+  position       fused_rotary() -> (inv_freq, rotary_dim), or None for an encoding of its own, which then
+                 offers apply(qkv, positions, num_heads, num_kv_heads, head_dim, step): it changes the
+                 q and k parts of qkv [T, (nq + 2 nkv) hd] in place, before the head norm
   mixer          cache_need(spec) -> PagedKV | FixedState | None                  static
                  __call__(h, step, cache) -> [T, hidden] in the activation dtype
   feed-forward   __call__(h, step) -> [T, hidden]
