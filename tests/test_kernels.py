@@ -238,7 +238,8 @@ def build_paged(seqs_kv, nkv, hd, page, dtype, shuffle_seed=0):
     return kc.to(DEV), vc.to(DEV), table.to(DEV)
 
 
-@pytest.mark.parametrize("kernel,dtype", [("paged", torch.float32), ("paged", torch.bfloat16), ("flash", torch.bfloat16)])
+@pytest.mark.parametrize("kernel,dtype", [("paged", torch.float32), ("paged", torch.bfloat16), ("flash", torch.bfloat16),
+                                          ("flash_split", torch.bfloat16)])
 @pytest.mark.parametrize("nq,nkv,hd,page,window", [(6, 2, 48, 4, 0), (5, 5, 16, 16, 0), (8, 1, 128, 16, 0),
                                                    (3, 1, 80, 8, 37), (4, 2, 256, 32, 0)])
 def test_paged_attention_ragged(kernel, dtype, nq, nkv, hd, page, window):
@@ -260,14 +261,24 @@ def test_paged_attention_ragged(kernel, dtype, nq, nkv, hd, page, window):
     out = torch.empty(T, nq * hd, device=DEV, dtype=dtype)
     e = err_word()
     scale = hd ** -0.5
-    if kernel == "flash":                       # tiles of up to 64 tokens per request, as the engine cuts them
-        tiles, t0 = [], 0
+    if kernel in ("flash", "flash_split"):      # tiles of up to 64 tokens per request, as the engine cuts them
+        tiles, single, t0 = [], [], 0
         for b, (n, c) in enumerate(zip(lens, new)):
-            for lo_ in range(0, c, 64):
-                tiles.append([b, t0 + lo_, min(64, c - lo_), n - c + lo_])
+            if c == 1 and kernel == "flash_split":        # single tokens go to the decode kernel, by index
+                single.append(t0)
+            else:
+                for lo_ in range(0, c, 64):
+                    tiles.append([b, t0 + lo_, min(64, c - lo_), n - c + lo_])
             t0 += c
         ops().flash_prefill(qkv, out, kc, vc, table, torch.tensor(tiles, dtype=torch.int32, device=DEV),
                             nq, nkv, hd, scale, window, e)
+        if single:
+            ctx = max(lens[req[t]] for t in single)
+            S, n_acc, n_ml = ops().decode_attention_scratch(len(single), nq, hd, ctx, 64)
+            ops().flash_decode(qkv, out, kc, vc, table, torch.tensor(req, dtype=torch.int32, device=DEV),
+                               torch.tensor(pos, dtype=torch.int32, device=DEV), nq, nkv, hd, scale, window, ctx,
+                               torch.full((n_acc,), float("nan"), device=DEV), torch.full((n_ml,), float("nan"), device=DEV),
+                               e, chunk=64, token_index=torch.tensor(single, dtype=torch.int32, device=DEV))
     else:
         ops().paged_attention(qkv, out, kc, vc, table, torch.tensor(req, dtype=torch.int32, device=DEV),
                               torch.tensor(pos, dtype=torch.int32, device=DEV), nq, nkv, hd, scale, window, e)

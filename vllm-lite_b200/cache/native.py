@@ -218,8 +218,8 @@ class NativeCacheManager:
         want_offsets = np.ascontiguousarray(want_offsets, dtype=np.int32)
         wants = np.ascontiguousarray(wants if len(wants) else [0], dtype=np.int32)
         max_blocks = np.full(max(G, 1), int(fixed_blocks), dtype=np.int32)
-        offsets = np.zeros(7 + 2 * G, dtype=np.int32)
-        sizes = np.zeros(7 + 2 * G, dtype=np.int32)
+        offsets = np.zeros(8 + 2 * G, dtype=np.int32)
+        sizes = np.zeros(8 + 2 * G, dtype=np.int32)
         ptr = lambda a: a.ctypes.data
         used = _core().vc_pack_step(self._h, B, ptr(keys), ptr(counts), ptr(starts), ptr(tokens), ptr(want_offsets),
                                     ptr(wants), int(pad_to), int(bool(with_tiles)), ptr(max_blocks), ptr(out),

@@ -455,12 +455,14 @@ decode_attention_split_kernel(const T* __restrict__ q, int q_stride,
 template <typename T>
 __global__ void decode_attention_merge_kernel(const float* __restrict__ part_acc, const float* __restrict__ part_ml,
                                               const int* __restrict__ positions, T* __restrict__ out,
-                                              int nq, int hd, int chunk, int S, int window) {
+                                              int nq, int hd, int chunk, int S, int window,
+                                              const int* __restrict__ token_index) {
     pdl_launch_dependents();
     pdl_wait();
-    const int t = blockIdx.x, h = blockIdx.y;
-    const int pos = positions[t];
-    T* op = out + ((size_t)t * nq + h) * hd;
+    const int t = blockIdx.x, h = blockIdx.y;                    // t numbers the tokens of the launch
+    const int tok = token_index ? token_index[t] : t;            // ... tok those of the step
+    const int pos = positions[tok];
+    T* op = out + ((size_t)tok * nq + h) * hd;
     if (pos < 0) {
         for (int e = threadIdx.x; e < hd; e += blockDim.x) op[e] = from_f32<T>(0.f);
         return;
@@ -541,21 +543,22 @@ static int decode_attention_typed(const T* q, int q_stride, T* out, const T* kc,
     }
 #undef DEC_PASS
     if (rc != 0) return rc;
-    decode_attention_merge_kernel<T><<<dim3(T_, nq), 128, 0, s>>>(pacc, pml, pos, out, nq, hd, chunk, S, window);
+    decode_attention_merge_kernel<T><<<dim3(T_, nq), 128, 0, s>>>(pacc, pml, pos, out, nq, hd, chunk, S, window, nullptr);
     return vl_launch_status();
 }
 
 // Merges per-chunk partial results (of vl_decode_attention's first pass or of vl_flash_decode).
 extern "C" int vl_decode_attention_merge(const float* part_acc, const float* part_ml, const int* positions, void* out,
-                                         int dtype, int T, int nq, int hd, int chunk, int S, int window, void* stream) {
+                                         int dtype, int T, int nq, int hd, int chunk, int S, int window,
+                                         const int* token_index, void* stream) {
     if (T <= 0) return VL_OK;
     cudaStream_t s = (cudaStream_t)stream;
     if (dtype == VL_F32)
         return vl_launch(decode_attention_merge_kernel<float>, dim3(T, nq), dim3(128), 0, s, part_acc, part_ml, positions,
-                         (float*)out, nq, hd, chunk, S, window);
+                         (float*)out, nq, hd, chunk, S, window, token_index);
     if (dtype == VL_BF16)
         return vl_launch(decode_attention_merge_kernel<bf16>, dim3(T, nq), dim3(128), 0, s, part_acc, part_ml, positions,
-                         (bf16*)out, nq, hd, chunk, S, window);
+                         (bf16*)out, nq, hd, chunk, S, window, token_index);
     return VL_ERR_UNSUPPORTED;
 }
 

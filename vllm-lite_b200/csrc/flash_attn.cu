@@ -284,7 +284,8 @@ flash_decode_kernel(const bf16* __restrict__ q, int q_stride,
                     const int* __restrict__ block_table, int max_blocks,
                     const int* __restrict__ req_index, const int* __restrict__ positions,
                     int nq, int nkv, int page_size, int num_pages, float scale_log2, int window,
-                    int chunk, int S, float* __restrict__ part_acc, float* __restrict__ part_ml, unsigned* err) {
+                    int chunk, int S, float* __restrict__ part_acc, float* __restrict__ part_ml, unsigned* err,
+                    const int* __restrict__ token_index) {
     extern __shared__ __align__(128) unsigned char fa_smem[];
     bf16* Qs = reinterpret_cast<bf16*>(fa_smem);                 // [16][LDS]
     bf16* ring = Qs + DEC_ROWS * LDS;                            // [NST][2][BN][LDS]
@@ -292,7 +293,9 @@ flash_decode_kernel(const bf16* __restrict__ q, int q_stride,
     __shared__ int s_rows[DEC_MAX_CHUNK + BN];                   // cache rows of the chunk's positions, tile aligned
     pdl_launch_dependents();
     pdl_wait();
-    const int split = blockIdx.x, tok = blockIdx.z;
+    // token_index (optional) picks the tokens of the step that this launch serves; partial results
+    // are stored by the number of the token within the launch
+    const int split = blockIdx.x, tok = token_index ? token_index[blockIdx.z] : (int)blockIdx.z;
     const int grp = nq / nkv;
     const int htiles = (grp + DEC_ROWS - 1) / DEC_ROWS;
     const int kvh = blockIdx.y / htiles, htile = blockIdx.y - kvh * htiles;
@@ -427,7 +430,7 @@ flash_decode_kernel(const bf16* __restrict__ q, int q_stride,
             acc += sO[((size_t)w * DEC_ROWS + r) * OLD + e] * wgt;
             L += s_l[w][r] * wgt;
         }
-        const size_t row = ((size_t)tok * nq + (h0 + r)) * S + split;
+        const size_t row = ((size_t)blockIdx.z * nq + (h0 + r)) * S + split;
         part_acc[row * HD + e] = acc;
         if (e == 0) {
             part_ml[row * 2] = M * 0.6931471805599453f;          // the merge kernel works in natural-log units
@@ -437,11 +440,13 @@ flash_decode_kernel(const bf16* __restrict__ q, int q_stride,
 }
 
 // Scratch as for vl_decode_attention: part_acc [T, nq, S, hd], part_ml [T, nq, S, 2] float32,
-// S = ceil(max_context / chunk); follow with vl_decode_attention_merge.
+// S = ceil(max_context / chunk); follow with vl_decode_attention_merge.  T counts the tokens served: all
+// tokens of the step, or those that token_index (T entries) names.
 extern "C" int vl_flash_decode(const void* q, int q_stride, const void* kcache, const void* vcache,
                                const int* block_table, int max_blocks, const int* req_index, const int* positions,
                                int T, int nq, int nkv, int hd, int page_size, int num_pages, float scale, int window,
-                               int chunk, int S, float* part_acc, float* part_ml, unsigned* err, void* stream) {
+                               int chunk, int S, float* part_acc, float* part_ml, unsigned* err,
+                               const int* token_index, void* stream) {
     if (T <= 0) return VL_OK;
     if (hd != HD) return VL_ERR_UNSUPPORTED;
     if (nq <= 0 || nkv <= 0 || nq % nkv || page_size <= 0 || max_blocks <= 0 || q_stride % 8) return VL_ERR_ARGUMENT;
@@ -456,5 +461,5 @@ extern "C" int vl_flash_decode(const void* q, int q_stride, const void* kcache, 
     return vl_launch(flash_decode_kernel, dim3(S, nkv * htiles, T), dim3(NTHREADS), smem, (cudaStream_t)stream,
                      (const bf16*)q, q_stride, (const bf16*)kcache, (const bf16*)vcache, block_table, max_blocks,
                      req_index, positions, nq, nkv, page_size, num_pages, scale * 1.4426950408889634f, window, chunk, S,
-                     part_acc, part_ml, err);
+                     part_acc, part_ml, err, token_index);
 }

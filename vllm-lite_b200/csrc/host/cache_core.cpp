@@ -279,10 +279,13 @@ int vc_check(void* h) {
 // ---- packing a step ---------------------------------------------------------------------------
 // The batch of a step as one int32 buffer of 16-byte aligned sections:
 //   tokens[T] positions[T] req_index[T] cu_seqlens[B+1] state_slots[B] logit_rows[R] tiles[4*NT]
-//   and per group g: slots[T] table[B * max_blocks[g]]
+//   single_tokens[ND], and per group g: slots[T] table[B * max_blocks[g]]
+// tiles: up to 64 consecutive tokens of a request that brings more than one token (for the
+// prefill attention kernel); single_tokens: indices of the tokens of requests that bring exactly
+// one (for the decode attention kernel) when the step holds both kinds.
 // B, T, R are the padded sizes (pad_to > 0: a decode step padded to pad_to requests; padded tokens
 // sit at position -1 with slot -1 and read nothing).  max_blocks[g] in: 0 = widest table of the
-// step (at least 1), else the fixed width.  offsets receives 7 + 2 * groups section offsets; the
+// step (at least 1), else the fixed width.  offsets receives 8 + 2 * groups section offsets; the
 // return value is the number of int32 words used (or needed, when capacity is too small: then
 // nothing is written), or a negative code.
 //   keys[B], counts[B], starts[B]  one entry per request (starts = position of its first new token)
@@ -308,9 +311,14 @@ long long vc_pack_step(void* h, int B_real, const long long* keys, const int* co
     const long long T = pad_to > 0 ? pad_to : T_real;
     const int R = pad_to > 0 ? pad_to : R_real;
     if (pad_to > 0 && (B_real > pad_to || T_real != B_real || R_real != B_real)) return VC_ARGUMENT;
-    int num_tiles = 0;
-    if (with_tiles && pad_to <= 0)
-        for (int b = 0; b < B_real; ++b) num_tiles += (counts[b] + 63) / 64;
+    int num_tiles = 0, num_single = 0;
+    if (with_tiles && pad_to <= 0) {
+        for (int b = 0; b < B_real; ++b) {
+            if (counts[b] > 1) num_tiles += (counts[b] + 63) / 64;
+            else ++num_single;
+        }
+        if (num_tiles == 0) num_single = 0;          // a step of single tokens only needs no list
+    }
     for (int g = 0; g < G; ++g) {
         if (max_blocks[g] <= 0) {
             int widest = 1;
@@ -327,6 +335,7 @@ long long vc_pack_step(void* h, int B_real, const long long* keys, const int* co
         cursor += align4((int)(n > 0 ? n : 1));
     };
     section(T); section(T); section(T); section(B + 1); section(B); section(R); section(4LL * num_tiles);
+    section(num_single);
     for (int g = 0; g < G; ++g) { section(T); section((long long)B * max_blocks[g]); }
     if (cursor > capacity) return cursor;
     for (long long i = 0; i < cursor; ++i) out[i] = -1;
@@ -337,6 +346,7 @@ long long vc_pack_step(void* h, int B_real, const long long* keys, const int* co
     int* sslot = out + offsets[4];
     int* rows = out + offsets[5];
     int* tiles = out + offsets[6];
+    int* single = out + offsets[7];
     if (pad_to > 0) {
         for (long long i = 0; i < T; ++i) { tok[i] = 0; req[i] = 0; rows[i] = (int)i; }
         for (int b = 0; b <= B; ++b) cu[b] = (int)T_real;
@@ -344,7 +354,7 @@ long long vc_pack_step(void* h, int B_real, const long long* keys, const int* co
     }
     cu[0] = 0;
     long long t = 0;
-    int r = 0, ti = 0;
+    int r = 0, ti = 0, si1 = 0;
     for (int b = 0; b < B_real; ++b) {
         const int n = counts[b];
         for (int i = 0; i < n; ++i) {
@@ -356,19 +366,20 @@ long long vc_pack_step(void* h, int B_real, const long long* keys, const int* co
             if (wants[w] < 0 || wants[w] >= n) return VC_ARGUMENT;
             rows[r++] = (int)(t + wants[w]);
         }
-        if (with_tiles && pad_to <= 0)
+        if (num_tiles > 0 && n > 1)
             for (int lo = 0; lo < n; lo += 64) {
                 tiles[4 * ti] = b; tiles[4 * ti + 1] = (int)(t + lo);
                 tiles[4 * ti + 2] = n - lo < 64 ? n - lo : 64; tiles[4 * ti + 3] = (int)(starts[b] + lo);
                 ++ti;
             }
+        if (num_single > 0 && n == 1) single[si1++] = (int)t;
         sslot[b] = reqs[b]->state_slot;
         t += n;
         cu[b + 1] = (int)t;
     }
     for (int g = 0; g < G; ++g) {
-        int* sl = out + offsets[7 + 2 * g];
-        int* tb = out + offsets[8 + 2 * g];
+        int* sl = out + offsets[8 + 2 * g];
+        int* tb = out + offsets[9 + 2 * g];
         const int mb = max_blocks[g];
         long long tt = 0;
         for (int b = 0; b < B_real; ++b) {

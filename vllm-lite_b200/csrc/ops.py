@@ -46,12 +46,12 @@ _SIGNATURES = {
                                            c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int,
                                            c_float, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p],
     ("attention", "vl_decode_attention_merge"): [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int,
-                                                 c_int, c_int, c_void_p],
+                                                 c_int, c_int, c_void_p, c_void_p],
     ("flash_attn", "vl_flash_prefill"): [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int,
                                          c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_void_p, c_void_p],
     ("flash_attn", "vl_flash_decode"): [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p,
                                         c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_int, c_int,
-                                        c_void_p, c_void_p, c_void_p, c_void_p],
+                                        c_void_p, c_void_p, c_void_p, c_void_p, c_void_p],
     ("activation", "vl_silu_mul"): [c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p],
     ("gemm_f32", "vl_gemm_f32_nt"): [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p],
     ("gemm_bf16", "vl_gemm_bf16_small_m"): [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
@@ -291,8 +291,10 @@ def flash_prefill(qkv, out, k_cache, v_cache, block_table, tiles, num_heads, num
 
 
 def flash_decode(qkv, out, k_cache, v_cache, block_table, req_index, positions, num_heads, num_kv_heads,
-                 head_dim, scale, window, max_context, part_acc, part_ml, err, chunk=DECODE_CHUNK):
-    """Tensor-core version of `decode_attention` (bfloat16): the split pass, then the merge."""
+                 head_dim, scale, window, max_context, part_acc, part_ml, err, chunk=DECODE_CHUNK, token_index=None):
+    """Tensor-core version of `decode_attention` (bfloat16): the split pass, then the merge.
+    `token_index` (int32) restricts the launch to some tokens of the step (the others' rows of `out`
+    are left alone); the scratch is then sized for that many tokens."""
     _flash_checks(qkv, k_cache, v_cache, block_table, num_heads, num_kv_heads, head_dim)
     _need(out, torch.bfloat16, "out", 2)
     _need(req_index, torch.int32, "req_index", 1); _need(positions, torch.int32, "positions", 1)
@@ -300,17 +302,20 @@ def flash_decode(qkv, out, k_cache, v_cache, block_table, req_index, positions, 
     T = qkv.shape[0]
     if out.shape != (T, num_heads * head_dim) or req_index.shape[0] != T or positions.shape[0] != T:
         raise KernelError("flash_decode: token counts or widths disagree")
+    if token_index is not None:
+        _need(token_index, torch.int32, "token_index", 1)
+        T = token_index.shape[0]
     S, need_acc, need_ml = decode_attention_scratch(T, num_heads, head_dim, max_context, chunk)
     if part_acc.numel() < need_acc or part_ml.numel() < need_ml:
         raise KernelError(f"flash_decode: scratch too small ({part_acc.numel()} < {need_acc})")
     _check(_fn("flash_attn", "vl_flash_decode", {"FA_HD": head_dim})(
         _ptr(qkv), qkv.shape[1], _ptr(k_cache), _ptr(v_cache), _ptr(block_table), block_table.shape[1],
         _ptr(req_index), _ptr(positions), T, num_heads, num_kv_heads, head_dim, k_cache.shape[2], k_cache.shape[0],
-        float(scale), int(window or 0), chunk, S, _ptr(part_acc), _ptr(part_ml), _ptr(err), _stream()),
-        "vl_flash_decode")
+        float(scale), int(window or 0), chunk, S, _ptr(part_acc), _ptr(part_ml), _ptr(err), _ptr(token_index),
+        _stream()), "vl_flash_decode")
     _check(_fn("attention", "vl_decode_attention_merge")(
         _ptr(part_acc), _ptr(part_ml), _ptr(positions), _ptr(out), dtype_code(out.dtype), T, num_heads, head_dim,
-        chunk, S, int(window or 0), _stream()), "vl_decode_attention_merge")
+        chunk, S, int(window or 0), _ptr(token_index), _stream()), "vl_decode_attention_merge")
     return out
 
 

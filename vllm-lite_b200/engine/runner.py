@@ -243,14 +243,16 @@ class ModelRunner:
             while bound < longest:
                 bound *= 2
             longest = min(bound, self.max_context)
-        groups = [GroupView(page_size=self.page_size, block_table=sec(8 + 2 * g).view(Bp, int(max_blocks[g])),
-                            slots=sec(7 + 2 * g), max_context=longest) for g in range(len(self.cache.pools))]
-        tiles = sec(6)
+        groups = [GroupView(page_size=self.page_size, block_table=sec(9 + 2 * g).view(Bp, int(max_blocks[g])),
+                            slots=sec(8 + 2 * g), max_context=longest) for g in range(len(self.cache.pools))]
+        tiles, single = sec(6), sec(7)
+        single_context = max([h.start + 1 for h in host_entries if h.count == 1], default=0)
         return StepBatch(tokens=sec(0), positions=sec(1), req_index=sec(2), cu_seqlens=sec(3), state_slots=sec(4),
                          logit_rows=sec(5), groups=groups, entries=host_entries, err=self.err, workspace=self.workspace,
                          num_tokens=bucket or sum(counts), num_entries=Bp, max_query_len=max(counts),
                          tag=f"g{bucket}.{longest}." if bucket else "", graph_bucket=bucket,
-                         query_tiles=tiles.view(-1, 4) if tiles.numel() else None)
+                         query_tiles=tiles.view(-1, 4) if tiles.numel() else None,
+                         single_tokens=single if single.numel() else None, single_context=single_context)
 
     def _layout_python(self, entries, host_entries, bucket: int = 0) -> StepBatch:
         real_B = len(entries)
@@ -273,15 +275,22 @@ class ModelRunner:
             off[name] = (cursor, n)
             cursor += _align4(max(n, 1))
         # tiles of up to 64 consecutive tokens of one request, for the tensor-core prefill kernel
-        tile_list = []
+        # ... and, when the step also holds requests that bring one token, the indices of those tokens
+        tile_list, single_list = [], []
         if not bucket:
             t0 = 0
             for b, h in enumerate(host_entries):
-                for lo in range(0, h.count, 64):
-                    tile_list.append((b, t0 + lo, min(64, h.count - lo), h.start + lo))
+                if h.count > 1:
+                    for lo in range(0, h.count, 64):
+                        tile_list.append((b, t0 + lo, min(64, h.count - lo), h.start + lo))
+                else:
+                    single_list.append(t0)
                 t0 += h.count
+            if not tile_list:
+                single_list = []
         for name, n in (("tokens", T), ("positions", T), ("req_index", T), ("cu_seqlens", B + 1),
-                        ("state_slots", B), ("logit_rows", R), ("tiles", 4 * len(tile_list))):
+                        ("state_slots", B), ("logit_rows", R), ("tiles", 4 * len(tile_list)),
+                        ("single", len(single_list))):
             section(name, n)
         for g in range(G):
             section(f"slots{g}", T)
@@ -310,6 +319,8 @@ class ModelRunner:
         view("state_slots")[:real_B] = [h.state_slot for h in host_entries]
         if tile_list:
             view("tiles")[:] = np.asarray(tile_list, dtype=np.int32).reshape(-1)
+        if single_list:
+            view("single")[:] = single_list
         for g in range(G):
             tb = view(f"table{g}").reshape(B, max_blocks[g])
             sl = view(f"slots{g}")
@@ -343,7 +354,9 @@ class ModelRunner:
                          workspace=self.workspace, num_tokens=T, num_entries=B,
                          max_query_len=max(h.count for h in host_entries),
                          tag=f"g{bucket}.{longest}." if bucket else "", graph_bucket=bucket,
-                         query_tiles=dview("tiles").view(-1, 4) if tile_list else None)
+                         query_tiles=dview("tiles").view(-1, 4) if tile_list else None,
+                         single_tokens=dview("single") if single_list else None,
+                         single_context=max([h.start + 1 for h in host_entries if h.count == 1], default=0))
 
     def _upload(self, meta: np.ndarray, bucket: int = 0) -> torch.Tensor:
         n = meta.shape[0]

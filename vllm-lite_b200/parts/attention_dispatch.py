@@ -4,13 +4,22 @@ Every kernel computes the same function of (query token, its request's pages);
 which one runs depends on the dtype and on the shape of the step only.  The
 float32 path always takes the one kernel whose order of additions depends on
 positions alone, so its results are bit-for-bit independent of the batch.  In
-bfloat16 the tensor-core kernels run: for a step of single tokens (decoding) the
-one that splits each token's key range over many blocks, else the one that walks
-tiles of 64 query tokens.
+bfloat16 the tensor-core kernels run: requests that bring one token (decoding)
+go to the kernel that splits each token's key range over many blocks, requests
+that bring a portion of a prompt to the one that walks tiles of 64 query tokens;
+a step that holds both kinds launches both, each on its own tokens.
 """
 from __future__ import annotations
 
 import torch
+
+
+def _decode(ops, args, step, spec, group, num_tokens, max_context, token_index=None):
+    chunk = ops.decode_chunk_for(num_tokens, spec.num_kv_heads, max_context)
+    S, n_acc, n_ml = ops.decode_attention_scratch(num_tokens, spec.num_heads, spec.head_dim, max_context, chunk)
+    part_acc = step.workspace.get(step.tag + "attn.part_acc", (n_acc,), torch.float32)
+    part_ml = step.workspace.get(step.tag + "attn.part_ml", (n_ml,), torch.float32)
+    return ops.flash_decode(*args, max_context, part_acc, part_ml, step.err, chunk=chunk, token_index=token_index)
 
 
 def run(qkv, out, cache, group, step, spec, scale):
@@ -19,13 +28,12 @@ def run(qkv, out, cache, group, step, spec, scale):
             spec.num_heads, spec.num_kv_heads, spec.head_dim, scale, spec.window)
     if ops.flash_supported(qkv.dtype, spec.head_dim):
         if step.max_query_len == 1:
-            T = qkv.shape[0]
-            chunk = ops.decode_chunk_for(T, spec.num_kv_heads, group.max_context)
-            S, n_acc, n_ml = ops.decode_attention_scratch(T, spec.num_heads, spec.head_dim, group.max_context, chunk)
-            part_acc = step.workspace.get(step.tag + "attn.part_acc", (n_acc,), torch.float32)
-            part_ml = step.workspace.get(step.tag + "attn.part_ml", (n_ml,), torch.float32)
-            return ops.flash_decode(*args, group.max_context, part_acc, part_ml, step.err, chunk=chunk)
+            return _decode(ops, args, step, spec, group, qkv.shape[0], group.max_context)
         if step.query_tiles is not None:
-            return ops.flash_prefill(qkv, out, cache.k, cache.v, group.block_table, step.query_tiles,
-                                     spec.num_heads, spec.num_kv_heads, spec.head_dim, scale, spec.window, step.err)
+            ops.flash_prefill(qkv, out, cache.k, cache.v, group.block_table, step.query_tiles,
+                              spec.num_heads, spec.num_kv_heads, spec.head_dim, scale, spec.window, step.err)
+            if step.single_tokens is not None:
+                _decode(ops, args, step, spec, group, step.single_tokens.shape[0], step.single_context,
+                        token_index=step.single_tokens)
+            return out
     return ops.paged_attention(*args, step.err)

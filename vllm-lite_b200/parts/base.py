@@ -94,6 +94,8 @@ class StepBatch:
     tag: str = ""                   # namespace for workspace buffers
     graph_bucket: int = 0           # padded batch size when the step is replayed from a CUDA graph
     query_tiles: Optional[torch.Tensor] = None   # int32 [n, 4]: (table row, first token, tokens <= 64, first position)
+    single_tokens: Optional[torch.Tensor] = None  # int32: tokens of one-token requests, when the step also holds portions
+    single_context: int = 0                      # bound on position + 1 of those tokens
 
 
 @dataclass
