@@ -290,6 +290,48 @@ def test_paged_attention_ragged(kernel, dtype, nq, nkv, hd, page, window):
         assert torch.allclose(out[t].float().cpu().view(nq, hd), ref, **tol(dtype)), (t, req[t], pos[t])
 
 
+@pytest.mark.parametrize("nq,nkv,hd,page,window", [(2, 1, 64, 16, 0), (6, 2, 64, 8, 37), (5, 5, 64, 64, 0),
+                                                   (4, 2, 128, 16, 0), (8, 1, 128, 32, 150), (3, 3, 128, 128, 0),
+                                                   (32, 8, 128, 16, 0)])
+def test_flash_tc5_prefill(nq, nkv, hd, page, window):
+    """The tcgen05 kernel on a ragged batch: a whole prompt of several tiles, a continuation that
+    starts inside a page, a short portion, a single token; pages shuffled; a NaN in every cache row
+    that no query may read would show in the output."""
+    dtype = torch.bfloat16
+    torch.manual_seed(nq * 100 + hd + page)
+    lens = [300, 471, 130, 77]                    # keys present per request
+    new = [300, 200, 3, 1]                        # query tokens of this step per request (the last `new` positions)
+    seqs = [(torch.randn(n, nkv, hd), torch.randn(n, nkv, hd)) for n in lens]
+    kc, vc, table = build_paged(seqs, nkv, hd, page, dtype)
+    kc = torch.nan_to_num(kc, nan=0.0); vc = torch.nan_to_num(vc, nan=0.0)    # unwritten slots of held pages: finite
+    req, pos, tiles, t0 = [], [], [], 0
+    for b, (n, c) in enumerate(zip(lens, new)):
+        for p_ in range(n - c, n):
+            req.append(b); pos.append(p_)
+        for lo_ in range(0, c, 128):
+            tiles.append([b, t0 + lo_, min(128, c - lo_), n - c + lo_])
+        t0 += c
+    T = len(req)
+    q = torch.randn(T, nq, hd)
+    qkv = torch.zeros(T, (nq + 2 * nkv) * hd)
+    qkv[:, :nq * hd] = q.view(T, -1)
+    qkv = qkv.to(DEV).to(dtype)
+    out = torch.full((T, nq * hd), 9.0, device=DEV, dtype=dtype)
+    e = err_word()
+    scale = hd ** -0.5
+    ops().flash_prefill_tc5(qkv, out, kc, vc, table, torch.tensor(tiles, dtype=torch.int32, device=DEV),
+                            nq, nkv, hd, scale, window, e)
+    assert int(e.item()) == 0
+    qd = qkv[:, :nq * hd].float().cpu().view(T, nq, hd)
+    worst = 0.0
+    for t in range(T):
+        k, v = seqs[req[t]]
+        ref = paged_reference(qd[t], k.to(dtype).float(), v.to(dtype).float(), pos[t], scale, window)
+        got = out[t].float().cpu().view(nq, hd)
+        worst = max(worst, float((got - ref).abs().max()))
+        assert torch.allclose(got, ref, **tol(dtype)), (t, req[t], pos[t], worst)
+
+
 def run_attention(kernel, qkv, out, kc, vc, table, req, pos, nq, nkv, hd, scale, window, e):
     if kernel == "paged":
         return ops().paged_attention(qkv, out, kc, vc, table, req, pos, nq, nkv, hd, scale, window, e)

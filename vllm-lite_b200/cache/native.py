@@ -205,7 +205,7 @@ class NativeCacheManager:
             raise PoolError("the host's and the core's lists of requests differ")
 
     # ---- packing a step (used by the step function) ---------------------------
-    def pack_step(self, request_ids, counts, starts, tokens, want_offsets, wants, pad_to, with_tiles, fixed_blocks,
+    def pack_step(self, request_ids, counts, starts, tokens, want_offsets, wants, pad_to, tile_rows, fixed_blocks,
                   out: np.ndarray):
         """Writes the packed batch into `out` (int32).  Returns (words used, offsets, sizes, max_blocks)
         or raises; when `out` is too small returns the words needed as a negative number."""
@@ -222,7 +222,7 @@ class NativeCacheManager:
         sizes = np.zeros(8 + 2 * G, dtype=np.int32)
         ptr = lambda a: a.ctypes.data
         used = _core().vc_pack_step(self._h, B, ptr(keys), ptr(counts), ptr(starts), ptr(tokens), ptr(want_offsets),
-                                    ptr(wants), int(pad_to), int(bool(with_tiles)), ptr(max_blocks), ptr(out),
+                                    ptr(wants), int(pad_to), int(tile_rows), ptr(max_blocks), ptr(out),
                                     out.shape[0], ptr(offsets), ptr(sizes))
         if used < 0:
             self._call("vc_check") if used == -7 else None

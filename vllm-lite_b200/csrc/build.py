@@ -26,7 +26,8 @@ NVCC_FLAGS = ARCH_FLAGS + ["-O3", "-lineinfo", "-std=c++17", "--shared", "-Xcomp
 SOURCES = ("embed_norm", "rope_cache", "attention", "activation", "gemm_f32", "gemm_bf16", "gemm_tc5", "sampling")
 # sources compiled once per value of a constant; the values here are what build_all() prepares,
 # any other allowed value is compiled when a model first needs it
-VARIANTS = {"flash_attn": [{"FA_HD": 128}, {"FA_HD": 64}, {"FA_HD": 32}, {"FA_HD": 16}]}
+VARIANTS = {"flash_attn": [{"FA_HD": 128}, {"FA_HD": 64}, {"FA_HD": 32}, {"FA_HD": 16}],
+            "flash_tc5": [{"FA_HD": 128}, {"FA_HD": 64}]}
 EXTRA_LIBS = {}
 
 _loaded = {}

@@ -9,7 +9,8 @@
 //
 // vl_flash_prefill: a block owns up to 64 consecutive tokens of one request and one query head
 //   (4 warps x 16 rows) and walks that request's keys in tiles of 64, K and V tiles double
-//   buffered in shared memory by cp.async.  The host passes the list of token tiles.
+//   buffered in shared memory by cp.async.  The host passes the list of token tiles; a tile of
+//   more than 64 tokens is shared out among several blocks.
 // vl_flash_decode: a block owns one token, one KV head with all its query heads as rows, and one
 //   chunk of `chunk` key positions; its 4 warps take 16 keys each of every 64-key tile and their
 //   partial results are merged in warp order.  The per-chunk partials go to the same scratch
@@ -92,19 +93,22 @@ __device__ __forceinline__ void load_kv_tiles(bf16* ktile, bf16* vtile, const bf
 }
 }  // namespace
 
-// tiles[i] = {row of the block table, index of the tile's first token in the step, tokens, position of the first}
+// tiles[i] = {row of the block table, index of the tile's first token in the step, tokens, position of the first};
+// block x serves the tokens 64 * (x % parts) ... of tile x / parts
 extern "C" __global__ void __launch_bounds__(NTHREADS)
 flash_prefill_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restrict__ out,
                      const bf16* __restrict__ kcache, const bf16* __restrict__ vcache,
-                     const int* __restrict__ block_table, int max_blocks, const int4* __restrict__ tiles,
+                     const int* __restrict__ block_table, int max_blocks, const int4* __restrict__ tiles, int parts,
                      int nq, int nkv, int page_size, int num_pages, float scale_log2, int window, unsigned* err) {
     extern __shared__ __align__(128) unsigned char fa_smem[];
     bf16* Qs = reinterpret_cast<bf16*>(fa_smem);                 // [BM][LDS]
     bf16* Ks = Qs + BM * LDS;                                    // [2][BN][LDS]
     bf16* Vs = Ks + 2 * BN * LDS;                                // [2][BN][LDS]
     __shared__ int s_rows[2][BN];                                // cache rows of the tile being loaded / the next one
-    const int4 tile = tiles[blockIdx.x];
-    const int req = tile.x, tok0 = tile.y, count = tile.z, pos0 = tile.w;
+    const int4 tile = tiles[blockIdx.x / parts];
+    const int part0 = (int)(blockIdx.x % parts) * BM;
+    if (part0 >= tile.z) return;
+    const int req = tile.x, tok0 = tile.y + part0, count = min(BM, tile.z - part0), pos0 = tile.w + part0;
     const int h = blockIdx.y, kvh = h / (nq / nkv);
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, t = lane & 3;
     const int* table = block_table + (size_t)req * max_blocks;
@@ -253,19 +257,21 @@ flash_prefill_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restrict_
 extern "C" int vl_flash_head_dim() { return HD; }
 
 extern "C" int vl_flash_prefill(const void* q, int q_stride, void* out, const void* kcache, const void* vcache,
-                                const int* block_table, int max_blocks, const int* tiles, int num_tiles,
+                                const int* block_table, int max_blocks, const int* tiles, int num_tiles, int tile_rows,
                                 int nq, int nkv, int hd, int page_size, int num_pages, float scale, int window,
                                 unsigned* err, void* stream) {
     if (num_tiles <= 0) return VL_OK;
     if (hd != HD) return VL_ERR_UNSUPPORTED;
     if (nq <= 0 || nkv <= 0 || nq % nkv || page_size <= 0 || max_blocks <= 0 || q_stride % 8) return VL_ERR_ARGUMENT;
+    if (tile_rows <= 0 || tile_rows > 65536) return VL_ERR_ARGUMENT;
+    const int parts = (tile_rows + BM - 1) / BM;                 // blocks per tile of the list
     if (nq > 65535) return VL_ERR_UNSUPPORTED;
     const size_t smem = (size_t)(BM + 4 * BN) * LDS * sizeof(bf16);
     cudaError_t e = cudaFuncSetAttribute(flash_prefill_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return (int)e;
-    flash_prefill_kernel<<<dim3(num_tiles, nq), NTHREADS, smem, (cudaStream_t)stream>>>(
+    flash_prefill_kernel<<<dim3(num_tiles * parts, nq), NTHREADS, smem, (cudaStream_t)stream>>>(
         (const bf16*)q, q_stride, (bf16*)out, (const bf16*)kcache, (const bf16*)vcache, block_table, max_blocks,
-        (const int4*)tiles, nq, nkv, page_size, num_pages, scale * 1.4426950408889634f, window, err);
+        (const int4*)tiles, parts, nq, nkv, page_size, num_pages, scale * 1.4426950408889634f, window, err);
     return vl_launch_status();
 }
 

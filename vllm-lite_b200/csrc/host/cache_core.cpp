@@ -280,7 +280,7 @@ int vc_check(void* h) {
 // The batch of a step as one int32 buffer of 16-byte aligned sections:
 //   tokens[T] positions[T] req_index[T] cu_seqlens[B+1] state_slots[B] logit_rows[R] tiles[4*NT]
 //   single_tokens[ND], and per group g: slots[T] table[B * max_blocks[g]]
-// tiles: up to 64 consecutive tokens of a request that brings more than one token (for the
+// tiles: up to tile_rows (0: no list) consecutive tokens of a request that brings more than one token (for the
 // prefill attention kernel); single_tokens: indices of the tokens of requests that bring exactly
 // one (for the decode attention kernel) when the step holds both kinds.
 // B, T, R are the padded sizes (pad_to > 0: a decode step padded to pad_to requests; padded tokens
@@ -292,7 +292,7 @@ int vc_check(void* h) {
 //   tokens                         all new tokens, entry after entry
 //   want_offsets[B+1], wants       places (within an entry's tokens) whose logits are wanted
 long long vc_pack_step(void* h, int B_real, const long long* keys, const int* counts, const long long* starts,
-                       const int* tokens, const int* want_offsets, const int* wants, int pad_to, int with_tiles,
+                       const int* tokens, const int* want_offsets, const int* wants, int pad_to, int tile_rows,
                        int* max_blocks, int* out, long long capacity, int* offsets, int* sizes) {
     Core* c = static_cast<Core*>(h);
     const int G = (int)c->pools.size();
@@ -312,9 +312,9 @@ long long vc_pack_step(void* h, int B_real, const long long* keys, const int* co
     const int R = pad_to > 0 ? pad_to : R_real;
     if (pad_to > 0 && (B_real > pad_to || T_real != B_real || R_real != B_real)) return VC_ARGUMENT;
     int num_tiles = 0, num_single = 0;
-    if (with_tiles && pad_to <= 0) {
+    if (tile_rows > 0 && pad_to <= 0) {
         for (int b = 0; b < B_real; ++b) {
-            if (counts[b] > 1) num_tiles += (counts[b] + 63) / 64;
+            if (counts[b] > 1) num_tiles += (counts[b] + tile_rows - 1) / tile_rows;
             else ++num_single;
         }
         if (num_tiles == 0) num_single = 0;          // a step of single tokens only needs no list
@@ -367,9 +367,9 @@ long long vc_pack_step(void* h, int B_real, const long long* keys, const int* co
             rows[r++] = (int)(t + wants[w]);
         }
         if (num_tiles > 0 && n > 1)
-            for (int lo = 0; lo < n; lo += 64) {
+            for (int lo = 0; lo < n; lo += tile_rows) {
                 tiles[4 * ti] = b; tiles[4 * ti + 1] = (int)(t + lo);
-                tiles[4 * ti + 2] = n - lo < 64 ? n - lo : 64; tiles[4 * ti + 3] = (int)(starts[b] + lo);
+                tiles[4 * ti + 2] = n - lo < tile_rows ? n - lo : tile_rows; tiles[4 * ti + 3] = (int)(starts[b] + lo);
                 ++ti;
             }
         if (num_single > 0 && n == 1) single[si1++] = (int)t;

@@ -48,7 +48,9 @@ _SIGNATURES = {
     ("attention", "vl_decode_attention_merge"): [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int,
                                                  c_int, c_int, c_void_p, c_void_p],
     ("flash_attn", "vl_flash_prefill"): [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int,
-                                         c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_void_p, c_void_p],
+                                         c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_void_p, c_void_p],
+    ("flash_tc5", "vl_flash_prefill_tc5"): [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int,
+                                            c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_void_p, c_void_p],
     ("flash_attn", "vl_flash_decode"): [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p,
                                         c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_int, c_int,
                                         c_void_p, c_void_p, c_void_p, c_void_p, c_void_p],
@@ -275,18 +277,45 @@ def _flash_checks(qkv, k_cache, v_cache, block_table, num_heads, num_kv_heads, h
         raise KernelError(f"cache {tuple(k_cache.shape)} does not match kv heads {num_kv_heads} x {head_dim}")
 
 
-def flash_prefill(qkv, out, k_cache, v_cache, block_table, tiles, num_heads, num_kv_heads, head_dim, scale, window, err):
-    """Tensor-core attention for prompt portions.  `tiles` int32 [n, 4]: (row of the block table,
-    index of the tile's first token in the step, tokens (<= 64), position of the first token);
-    the tiles of a step cover every token once."""
+def flash_prefill(qkv, out, k_cache, v_cache, block_table, tiles, num_heads, num_kv_heads, head_dim, scale, window, err,
+                  tile_rows=64):
+    """Tensor-core (mma.sync) attention for prompt portions.  `tiles` int32 [n, 4]: (row of the block
+    table, index of the tile's first token in the step, tokens (<= tile_rows), position of the first
+    token); the tiles of a step cover every token that the kernel is to serve once."""
     _flash_checks(qkv, k_cache, v_cache, block_table, num_heads, num_kv_heads, head_dim)
     _need(out, torch.bfloat16, "out", 2); _need(tiles, torch.int32, "tiles", 2)
     if out.shape != (qkv.shape[0], num_heads * head_dim) or tiles.shape[1] != 4:
         raise KernelError("flash_prefill: shapes disagree")
     _check(_fn("flash_attn", "vl_flash_prefill", {"FA_HD": head_dim})(
         _ptr(qkv), qkv.shape[1], _ptr(out), _ptr(k_cache), _ptr(v_cache), _ptr(block_table), block_table.shape[1],
+        _ptr(tiles), tiles.shape[0], int(tile_rows), num_heads, num_kv_heads, head_dim, k_cache.shape[2],
+        k_cache.shape[0], float(scale), int(window or 0), _ptr(err), _stream()), "vl_flash_prefill")
+    return out
+
+
+FLASH_TC5_TILE = 128
+
+
+def flash_tc5_supported(dtype, head_dim, page_size) -> bool:
+    """The tcgen05 attention kernel takes bfloat16, head sizes 64 and 128, and pages of a multiple of
+    8 positions that divide 64 or are a multiple of it."""
+    return (dtype == torch.bfloat16 and head_dim in (64, 128) and page_size % 8 == 0
+            and (64 % page_size == 0 if page_size < 64 else page_size % 64 == 0))
+
+
+def flash_prefill_tc5(qkv, out, k_cache, v_cache, block_table, tiles, num_heads, num_kv_heads, head_dim, scale, window, err):
+    """Attention for prompt portions on the tcgen05 tensor cores; `tiles` as for `flash_prefill`,
+    up to 128 tokens each."""
+    _flash_checks(qkv, k_cache, v_cache, block_table, num_heads, num_kv_heads, head_dim)
+    _need(out, torch.bfloat16, "out", 2); _need(tiles, torch.int32, "tiles", 2)
+    if out.shape != (qkv.shape[0], num_heads * head_dim) or tiles.shape[1] != 4:
+        raise KernelError("flash_prefill_tc5: shapes disagree")
+    if not flash_tc5_supported(qkv.dtype, head_dim, k_cache.shape[2]):
+        raise KernelError(f"flash_prefill_tc5: head size {head_dim} / page size {k_cache.shape[2]} not taken")
+    _check(_fn("flash_tc5", "vl_flash_prefill_tc5", {"FA_HD": head_dim})(
+        _ptr(qkv), qkv.shape[1], _ptr(out), _ptr(k_cache), _ptr(v_cache), _ptr(block_table), block_table.shape[1],
         _ptr(tiles), tiles.shape[0], num_heads, num_kv_heads, head_dim, k_cache.shape[2], k_cache.shape[0],
-        float(scale), int(window or 0), _ptr(err), _stream()), "vl_flash_prefill")
+        float(scale), int(window or 0), _ptr(err), _stream()), "vl_flash_prefill_tc5")
     return out
 
 

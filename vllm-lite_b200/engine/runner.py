@@ -20,7 +20,7 @@ import torch
 from ..cache import make_cache_manager
 from ..cache.manager import CacheLayout, CacheManager, OutOfPages
 from ..cache.storage import CacheStorage
-from ..parts.base import BuildContext, Entry, GroupView, StepBatch, Workspace
+from ..parts.base import QUERY_TILE, BuildContext, Entry, GroupView, StepBatch, Workspace
 from ..parts.model import CausalLM, cache_needs
 
 
@@ -229,7 +229,7 @@ class ModelRunner:
         while True:
             i, pin = self._pinned_slot(guess)
             used, off, sizes, max_blocks = self.cache.pack_step(ids, counts, starts, tokens, want_offsets, wants,
-                                                                bucket, not bucket, fixed, pin.numpy())
+                                                                bucket, 0 if bucket else QUERY_TILE, fixed, pin.numpy())
             if used >= 0:
                 break
             self._flip ^= 1                          # the slot was not used; take it again, larger
@@ -274,15 +274,15 @@ class ModelRunner:
             nonlocal cursor
             off[name] = (cursor, n)
             cursor += _align4(max(n, 1))
-        # tiles of up to 64 consecutive tokens of one request, for the tensor-core prefill kernel
+        # tiles of up to QUERY_TILE consecutive tokens of one request, for the tensor-core prefill kernels
         # ... and, when the step also holds requests that bring one token, the indices of those tokens
         tile_list, single_list = [], []
         if not bucket:
             t0 = 0
             for b, h in enumerate(host_entries):
                 if h.count > 1:
-                    for lo in range(0, h.count, 64):
-                        tile_list.append((b, t0 + lo, min(64, h.count - lo), h.start + lo))
+                    for lo in range(0, h.count, QUERY_TILE):
+                        tile_list.append((b, t0 + lo, min(QUERY_TILE, h.count - lo), h.start + lo))
                 else:
                     single_list.append(t0)
                 t0 += h.count

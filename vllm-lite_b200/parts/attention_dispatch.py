@@ -6,12 +6,16 @@ float32 path always takes the one kernel whose order of additions depends on
 positions alone, so its results are bit-for-bit independent of the batch.  In
 bfloat16 the tensor-core kernels run: requests that bring one token (decoding)
 go to the kernel that splits each token's key range over many blocks, requests
-that bring a portion of a prompt to the one that walks tiles of 64 query tokens;
-a step that holds both kinds launches both, each on its own tokens.
+that bring a portion of a prompt to one that walks tiles of query tokens (the
+tcgen05 kernel when a portion is long enough to fill its 128-row tiles and it
+takes the head and page size, else the mma.sync kernel); a step that holds both
+kinds launches both, each on its own tokens.
 """
 from __future__ import annotations
 
 import torch
+
+from .base import QUERY_TILE
 
 
 def _decode(ops, args, step, spec, group, num_tokens, max_context, token_index=None):
@@ -30,8 +34,12 @@ def run(qkv, out, cache, group, step, spec, scale):
         if step.max_query_len == 1:
             return _decode(ops, args, step, spec, group, qkv.shape[0], group.max_context)
         if step.query_tiles is not None:
-            ops.flash_prefill(qkv, out, cache.k, cache.v, group.block_table, step.query_tiles,
-                              spec.num_heads, spec.num_kv_heads, spec.head_dim, scale, spec.window, step.err)
+            tile_args = (qkv, out, cache.k, cache.v, group.block_table, step.query_tiles,
+                         spec.num_heads, spec.num_kv_heads, spec.head_dim, scale, spec.window, step.err)
+            if step.max_query_len > 64 and ops.flash_tc5_supported(qkv.dtype, spec.head_dim, group.page_size):
+                ops.flash_prefill_tc5(*tile_args)
+            else:
+                ops.flash_prefill(*tile_args, tile_rows=QUERY_TILE)
             if step.single_tokens is not None:
                 _decode(ops, args, step, spec, group, step.single_tokens.shape[0], step.single_context,
                         token_index=step.single_tokens)

@@ -76,6 +76,11 @@ class Entry:
     state_slot: int = -1
 
 
+# most consecutive tokens of one request in an entry of StepBatch.query_tiles (what the tiled
+# attention kernels take as one tile of query rows)
+QUERY_TILE = 128
+
+
 @dataclass
 class StepBatch:
     tokens: torch.Tensor            # int32 [T]
@@ -93,7 +98,7 @@ class StepBatch:
     max_query_len: int = 0
     tag: str = ""                   # namespace for workspace buffers
     graph_bucket: int = 0           # padded batch size when the step is replayed from a CUDA graph
-    query_tiles: Optional[torch.Tensor] = None   # int32 [n, 4]: (table row, first token, tokens <= 64, first position)
+    query_tiles: Optional[torch.Tensor] = None   # int32 [n, 4]: (table row, first token, tokens <= QUERY_TILE, first position)
     single_tokens: Optional[torch.Tensor] = None  # int32: tokens of one-token requests, when the step also holds portions
     single_context: int = 0                      # bound on position + 1 of those tokens
 
