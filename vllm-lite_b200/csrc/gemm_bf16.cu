@@ -62,19 +62,20 @@ __device__ __forceinline__ void bulk_copy_g2s(void* dst, const void* src, unsign
 }
 __device__ __forceinline__ void consumer_barrier() { asm volatile("bar.sync 1, 128;" ::: "memory"); }
 
-#define GS_KC 512                          // K elements of a stage
-#define GS_STAGES 4
-#define GS_ROWB (GS_KC * 2 + 16)           // bytes of a padded row of a stage: rows 16 bytes apart modulo 128
 #define GS_CONSUMERS 4                     // consumer warps; warp 4 is the producer
 
 // Block = 16 rows of W.  The producer warp streams them through a ring of GS_STAGES stages of
-// GS_KC columns with one bulk copy (TMA) per row and stage; four consumer warps each take a quarter
-// of every stage, read their tensor-core operands from shared memory (W) and from global memory (A,
-// small and cached), and hand the stage back.  Sums are added in warp order at the end.
-template <int MT, typename TO>
+// GS_KC columns (a multiple of 128) with one bulk copy (TMA) per row and stage; four consumer warps
+// each take a quarter of every stage, read their tensor-core operands from shared memory (W) and
+// from global memory (A, small and cached), and hand the stage back.  Sums are added in warp order
+// at the end.  Stage size and count decide how many blocks share an SM and how many bytes each
+// keeps in flight; the launcher picks them by the shape.
+template <int MT, typename TO, int GS_KC, int GS_STAGES>
 __global__ void __launch_bounds__(160)
 gemm_bf16_small_m_kernel(const bf16* __restrict__ A, const bf16* __restrict__ W, TO* __restrict__ C,
                          int M, int N, int K, int lda, int ldw, int ldc, unsigned* err, int swiglu) {
+    static_assert(GS_KC % (32 * GS_CONSUMERS) == 0, "a stage is shared out in 32-wide slices among the consumer warps");
+    constexpr int GS_ROWB = GS_KC * 2 + 16;    // bytes of a padded row of a stage: rows 16 bytes apart modulo 128
     extern __shared__ __align__(128) unsigned char gs_smem[];               // [GS_STAGES][16][GS_ROWB]
     __shared__ float red[GS_CONSUMERS][MT][GS_ROWS][8];
     __shared__ __align__(8) unsigned long long full_bar[GS_STAGES], empty_bar[GS_STAGES];
@@ -210,20 +211,31 @@ template <typename TO>
 static int launch_small_m(const bf16* A, const bf16* W, TO* C, int M, int N, int K, int lda, int ldw, int ldc,
                           unsigned* err, int swiglu, cudaStream_t s) {
     dim3 grid((N + GS_ROWS - 1) / GS_ROWS);
-    const size_t smem = (size_t)GS_STAGES * GS_ROWS * GS_ROWB;
-#define GS_LAUNCH(MT)                                                                                      \
+    static int num_sms = 0;
+    if (!num_sms) {
+        int dev = 0;
+        cudaGetDevice(&dev);
+        if (cudaDeviceGetAttribute(&num_sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || num_sms <= 0) num_sms = 148;
+    }
+#define GS_LAUNCH(MT, KC, STAGES)                                                                          \
     {                                                                                                      \
-        auto kern = gemm_bf16_small_m_kernel<MT, TO>;                                                      \
+        const size_t smem = (size_t)STAGES * GS_ROWS * (KC * 2 + 16);                                      \
+        auto kern = gemm_bf16_small_m_kernel<MT, TO, KC, STAGES>;                                          \
         cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
         if (e != cudaSuccess) return (int)e;                                                               \
-        { int rc = vl_launch(kern, grid, dim3(160), smem, s, A, W, C, M, N, K, lda, ldw, ldc, err, swiglu); if (rc) return rc; } \
+        return vl_launch(kern, grid, dim3(160), smem, s, A, W, C, M, N, K, lda, ldw, ldc, err, swiglu);    \
     }
-    if (M <= 8) GS_LAUNCH(1)
-    else if (M <= 16) GS_LAUNCH(2)
-    else if (M <= 32) GS_LAUNCH(4)
-    else GS_LAUNCH(8)
+    // Measured on the shapes of decode steps: up to 8 rows run best with three larger stages (three
+    // blocks per SM; two, with still larger stages, when the blocks are so few that all are resident
+    // and K is long); more rows need the registers and keep four stages of 512 columns.
+    if (M <= 8) {
+        if ((int)grid.x <= 2 * num_sms && K >= 8192) GS_LAUNCH(1, 1024, 3)
+        GS_LAUNCH(1, 768, 3)
+    }
+    if (M <= 16) GS_LAUNCH(2, 512, 4)
+    if (M <= 32) GS_LAUNCH(4, 512, 4)
+    GS_LAUNCH(8, 512, 4)
 #undef GS_LAUNCH
-    return vl_launch_status();
 }
 
 extern "C" int vl_gemm_bf16_small_m(const void* A, const void* W, void* C, int out_dtype, int M, int N, int K,
