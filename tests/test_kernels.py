@@ -300,15 +300,14 @@ def test_paged_attention_ragged(kernel, dtype, nq, nkv, hd, page, window):
                                                    (32, 8, 128, 16, 0)])
 def test_flash_tc5_prefill(nq, nkv, hd, page, window):
     """The tcgen05 kernel on a ragged batch: a whole prompt of several tiles, a continuation that
-    starts inside a page, a short portion, a single token; pages shuffled; a NaN in every cache row
-    that no query may read would show in the output."""
+    starts inside a page, a short portion, a single token; pages shuffled; every cache slot that no
+    query may read holds NaN, which would show in the output."""
     dtype = torch.bfloat16
     torch.manual_seed(nq * 100 + hd + page)
     lens = [300, 471, 130, 77]                    # keys present per request
     new = [300, 200, 3, 1]                        # query tokens of this step per request (the last `new` positions)
     seqs = [(torch.randn(n, nkv, hd), torch.randn(n, nkv, hd)) for n in lens]
     kc, vc, table = build_paged(seqs, nkv, hd, page, dtype)
-    kc = torch.nan_to_num(kc, nan=0.0); vc = torch.nan_to_num(vc, nan=0.0)    # unwritten slots of held pages: finite
     req, pos, tiles, t0 = [], [], [], 0
     for b, (n, c) in enumerate(zip(lens, new)):
         for p_ in range(n - c, n):
@@ -348,12 +347,17 @@ def run_attention(kernel, qkv, out, kc, vc, table, req, pos, nq, nkv, hd, scale,
     S, n_acc, n_ml = ops().decode_attention_scratch(qkv.shape[0], nq, hd, ctx)
     pa = torch.full((n_acc,), float("nan"), device=DEV)
     pm = torch.full((n_ml,), float("nan"), device=DEV)
-    if kernel.startswith("flash_decode"):       # "flash_decode", "flash_decode64", "flash_decode1024": the chunk size
+    if kernel.startswith("flash_decode"):       # "flash_decode", "flash_decode64", "flash_decode1024": the chunk size;
+        stream = kernel.endswith("tma")         # "...tma": the persistent TMA kernel, else a block per chunk
+        kernel = kernel[:-3] if stream else kernel
+        if stream and not ops().flash_tc5_supported(qkv.dtype, hd, kc.shape[2]):
+            pytest.skip("the TMA kernel does not take this head or page size")
         chunk = int(kernel[len("flash_decode"):] or 256)
         S, n_acc, n_ml = ops().decode_attention_scratch(qkv.shape[0], nq, hd, ctx, chunk)
         pa = torch.full((n_acc,), float("nan"), device=DEV)
         pm = torch.full((n_ml,), float("nan"), device=DEV)
-        return ops().flash_decode(qkv, out, kc, vc, table, req, pos, nq, nkv, hd, scale, window, ctx, pa, pm, e, chunk=chunk)
+        return ops().flash_decode(qkv, out, kc, vc, table, req, pos, nq, nkv, hd, scale, window, ctx, pa, pm, e, chunk=chunk,
+                                  stream_kernel=stream)
     return ops().decode_attention(qkv, out, kc, vc, table, req, pos, nq, nkv, hd, scale, window, ctx, pa, pm, e)
 
 
@@ -361,13 +365,15 @@ def attention_cases():
     """(kernel, dtype): the tensor-core kernels exist in bfloat16 only."""
     return [("paged", torch.float32), ("paged", torch.bfloat16), ("decode", torch.float32), ("decode", torch.bfloat16),
             ("flash_decode", torch.bfloat16), ("flash_decode64", torch.bfloat16), ("flash_decode1024", torch.bfloat16),
+            ("flash_decodetma", torch.bfloat16), ("flash_decode64tma", torch.bfloat16), ("flash_decode1024tma", torch.bfloat16),
             ("flash_prefill", torch.bfloat16)]
 
 
 @pytest.mark.parametrize("kernel,dtype", [c for c in attention_cases() if c[0] != "paged"])
 @pytest.mark.parametrize("nq,nkv,hd,page,window", [(6, 2, 48, 4, 0), (5, 5, 16, 16, 0), (32, 8, 128, 16, 0),
                                                    (3, 1, 80, 8, 300), (16, 2, 256, 32, 0), (7, 1, 64, 16, 0),
-                                                   (40, 2, 32, 16, 0)])
+                                                   (40, 2, 32, 16, 0), (20, 1, 128, 64, 500), (4, 2, 64, 8, 0),
+                                                   (6, 3, 128, 128, 0)])
 def test_decode_attention_split(kernel, dtype, nq, nkv, hd, page, window):
     """Single tokens of requests of very different lengths (one token, a chunk's edge, several
     chunks), pages shuffled; a padded token at position -1 yields zeros."""

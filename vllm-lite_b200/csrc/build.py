@@ -27,7 +27,8 @@ SOURCES = ("embed_norm", "rope_cache", "attention", "activation", "gemm_f32", "g
 # sources compiled once per value of a constant; the values here are what build_all() prepares,
 # any other allowed value is compiled when a model first needs it
 VARIANTS = {"flash_attn": [{"FA_HD": 128}, {"FA_HD": 64}, {"FA_HD": 32}, {"FA_HD": 16}],
-            "flash_tc5": [{"FA_HD": 128}, {"FA_HD": 64}]}
+            "flash_tc5": [{"FA_HD": 128}, {"FA_HD": 64}],
+            "flash_decode_tma": [{"FA_HD": 128}, {"FA_HD": 64}]}
 EXTRA_LIBS = {}
 
 _loaded = {}

@@ -18,7 +18,8 @@
 //        columns (cp.async.bulk.tensor.2d, 128-byte swizzle), into two stages each; a lane owns a
 //        box and looks its page up one tile ahead; a page that no query of the tile may read, or
 //        that the block table does not hold, is fetched from beyond the end of the tensor, which
-//        the TMA unit fills with zeros;
+//        the TMA unit fills with zeros; the rows of V behind the tile's last key (another request's
+//        leftovers, possibly NaN) are zeroed in shared memory once the last key tile has landed;
 //   warp 5, one thread   issues the products: S_j = Q K_j^T (M 128, N 64, K = head size; both
 //        operands K-major) into one of two score buffers, so that the scores of the next tile are
 //        computed while the rows of this one are exponentiated, and O += P_j V_j (M 128, N = head
@@ -117,9 +118,9 @@ flash_tc5_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constan
     unsigned char* Ps = Vs + 2 * KV_STAGE;
     unsigned long long* bars = reinterpret_cast<unsigned long long*>(smem + TILE_BYTES);
     unsigned long long *k_full = bars, *k_empty = bars + 2, *v_full = bars + 4, *v_empty = bars + 6, *s_full = bars + 8;
-    unsigned long long &p_full = bars[10], &pv_done = bars[11];
-    unsigned& tmem_base_slot = *reinterpret_cast<unsigned*>(bars + 12);
-    int& failed = *reinterpret_cast<int*>(bars + 13);
+    unsigned long long &p_full = bars[10], &pv_done = bars[11], &v_fixed = bars[12];
+    unsigned& tmem_base_slot = *reinterpret_cast<unsigned*>(bars + 13);
+    int& failed = *reinterpret_cast<int*>(bars + 14);
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     if (smem_u32(smem) & 1023u) {                    // (uniform) never expected; the tiles would be misread
         if (tid == 0 && err) atomicOr(err, VL_DEV_WAIT_EXPIRED);
@@ -134,6 +135,7 @@ flash_tc5_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constan
         }
         mbar_init(&p_full, BM);
         mbar_init(&pv_done, 1);
+        mbar_init(&v_fixed, 1);
         mbar_fence_init();
         failed = 0;
     }
@@ -205,7 +207,24 @@ flash_tc5_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constan
             row_v = row_k;
             row_k = row_next;
         }
-        if (!ok && lane == 0) atomicExch(&failed, 1);
+        // Slots behind the request's last key hold whatever the page's earlier owner left there.  Their
+        // probabilities are zero, but 0 * NaN is NaN: zero those rows of V of the last key tile.
+        const int last = n_tiles - 1, first_bad = hi + 1 - (jt0 + last) * BN;
+        if (ok && first_bad < BN) {
+            ok = __all_sync(0xffffffffu, mbar_wait_bounded(&v_full[last & 1], (unsigned)((last / 2) & 1)));
+            if (ok) {
+                unsigned char* vs = Vs + (unsigned)(last & 1) * KV_STAGE;
+                for (int r = first_bad; r < BN; ++r)
+                    if (lane < CB * 8)
+                        *reinterpret_cast<uint4*>(vs + (unsigned)(lane >> 3) * (BN * ROW_BYTES) + (unsigned)r * ROW_BYTES + ((lane & 7) << 4)) = make_uint4(0u, 0u, 0u, 0u);
+                fence_proxy_async_smem();
+                __syncwarp();
+            }
+        }
+        if (lane == 0) {
+            if (ok) mbar_arrive(&v_fixed);
+            else atomicExch(&failed, 1);
+        }
     } else if (warp == 5) {
         if (lane == 0) {                                         // ---- MMA issuer ----
             constexpr unsigned idesc_qk = make_idesc(BM, BN);
@@ -238,7 +257,8 @@ flash_tc5_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constan
                 if (it + 1 < n_tiles) issue_qk(it + 1);          // the next scores run during this tile's softmax
                 if (!ok) break;
                 if (!mbar_wait_bounded(&p_full, (unsigned)(it & 1)) ||
-                    !mbar_wait_bounded(&v_full[s], (unsigned)((it / 2) & 1))) { ok = false; break; }
+                    !mbar_wait_bounded(&v_full[s], (unsigned)((it / 2) & 1)) ||
+                    (it == n_tiles - 1 && !mbar_wait_bounded(&v_fixed, 0u))) { ok = false; break; }
                 tc5_fence_after();
                 const unsigned vb = v_lo + (unsigned)s * (KV_STAGE >> 4);
 #pragma unroll

@@ -54,6 +54,9 @@ _SIGNATURES = {
     ("flash_attn", "vl_flash_decode"): [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p,
                                         c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_int, c_int,
                                         c_void_p, c_void_p, c_void_p, c_void_p, c_void_p],
+    ("flash_decode_tma", "vl_flash_decode_tma"): [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p,
+                                                  c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_int, c_int,
+                                                  c_void_p, c_void_p, c_void_p, c_void_p, c_void_p],
     ("activation", "vl_silu_mul"): [c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p],
     ("gemm_f32", "vl_gemm_f32_nt"): [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p],
     ("gemm_bf16", "vl_gemm_bf16_small_m"): [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
@@ -253,9 +256,10 @@ def decode_attention(qkv, out, k_cache, v_cache, block_table, req_index, positio
     return out
 
 
-def decode_chunk_for(num_tokens, num_kv_heads, max_context, target_blocks=592) -> int:
+def decode_chunk_for(num_tokens, num_kv_heads, max_context, target_blocks=256) -> int:
     """Key positions per block of the split decode kernels: the largest of 256..1024 that still
-    gives about two waves of blocks on the 148 SMs (a block's start-up is paid once per chunk)."""
+    gives most of the 148 SMs two blocks (a block's start-up is paid once per chunk; measured at
+    batch 8, context 4,096: 4.80 / 4.55 / 4.38 ms a step with chunks of 256 / 512 / 1,024)."""
     for chunk in (1024, 512):
         if num_tokens * num_kv_heads * -(-int(max_context) // chunk) >= target_blocks:
             return chunk
@@ -320,8 +324,12 @@ def flash_prefill_tc5(qkv, out, k_cache, v_cache, block_table, tiles, num_heads,
 
 
 def flash_decode(qkv, out, k_cache, v_cache, block_table, req_index, positions, num_heads, num_kv_heads,
-                 head_dim, scale, window, max_context, part_acc, part_ml, err, chunk=DECODE_CHUNK, token_index=None):
+                 head_dim, scale, window, max_context, part_acc, part_ml, err, chunk=DECODE_CHUNK, token_index=None,
+                 stream_kernel=None):
     """Tensor-core version of `decode_attention` (bfloat16): the split pass, then the merge.
+    The split pass is the persistent TMA kernel where it takes the head size and pages hold at
+    least 64 positions (`stream_kernel`: None = that rule, True / False to force), else a block
+    per chunk.
     `token_index` (int32) restricts the launch to some tokens of the step (the others' rows of `out`
     are left alone); the scratch is then sized for that many tokens."""
     _flash_checks(qkv, k_cache, v_cache, block_table, num_heads, num_kv_heads, head_dim)
@@ -337,7 +345,11 @@ def flash_decode(qkv, out, k_cache, v_cache, block_table, req_index, positions, 
     S, need_acc, need_ml = decode_attention_scratch(T, num_heads, head_dim, max_context, chunk)
     if part_acc.numel() < need_acc or part_ml.numel() < need_ml:
         raise KernelError(f"flash_decode: scratch too small ({part_acc.numel()} < {need_acc})")
-    _check(_fn("flash_attn", "vl_flash_decode", {"FA_HD": head_dim})(
+    if stream_kernel is None:           # measured: it wins from 64-position pages on (TMA boxes of 8 KB, not 2 KB)
+        stream_kernel = flash_tc5_supported(qkv.dtype, head_dim, k_cache.shape[2]) and k_cache.shape[2] >= 64
+    split = (_fn("flash_decode_tma", "vl_flash_decode_tma", {"FA_HD": head_dim}) if stream_kernel
+             else _fn("flash_attn", "vl_flash_decode", {"FA_HD": head_dim}))
+    _check(split(
         _ptr(qkv), qkv.shape[1], _ptr(k_cache), _ptr(v_cache), _ptr(block_table), block_table.shape[1],
         _ptr(req_index), _ptr(positions), T, num_heads, num_kv_heads, head_dim, k_cache.shape[2], k_cache.shape[0],
         float(scale), int(window or 0), chunk, S, _ptr(part_acc), _ptr(part_ml), _ptr(err), _ptr(token_index),
