@@ -73,14 +73,17 @@ __device__ __forceinline__ void consumer_barrier() { asm volatile("bar.sync 1, 1
 template <int MT, typename TO, int GS_KC, int GS_STAGES>
 __global__ void __launch_bounds__(160)
 gemm_bf16_small_m_kernel(const bf16* __restrict__ A, const bf16* __restrict__ W, TO* __restrict__ C,
-                         int M, int N, int K, int lda, int ldw, int ldc, unsigned* err, int swiglu) {
+                         int M, int N, int K, int lda, int ldw, int ldc, unsigned* err, int swiglu, int gran) {
     static_assert(GS_KC % (32 * GS_CONSUMERS) == 0, "a stage is shared out in 32-wide slices among the consumer warps");
     constexpr int GS_ROWB = GS_KC * 2 + 16;    // bytes of a padded row of a stage: rows 16 bytes apart modulo 128
     extern __shared__ __align__(128) unsigned char gs_smem[];               // [GS_STAGES][16][GS_ROWB]
     __shared__ float red[GS_CONSUMERS][MT][GS_ROWS][8];
     __shared__ __align__(8) unsigned long long full_bar[GS_STAGES], empty_bar[GS_STAGES];
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    const int n0 = blockIdx.x * GS_ROWS;
+    // rows of W of this block: an even share of N, in units of `gran` rows, walked in tiles of 16
+    const int units = (N + gran - 1) / gran;
+    const int r0 = (int)((long long)blockIdx.x * units / gridDim.x) * gran;
+    const int r1 = min(N, (int)((long long)(blockIdx.x + 1) * units / gridDim.x) * gran);
     const int iters = (K + GS_KC - 1) / GS_KC;
     pdl_launch_dependents();
     if (tid == 0) {
@@ -91,23 +94,31 @@ gemm_bf16_small_m_kernel(const bf16* __restrict__ A, const bf16* __restrict__ W,
     if (warp == GS_CONSUMERS) {                                            // ---- producer ----
         // W is a constant of the step: its stream starts while earlier kernels are still running
         if (lane < GS_ROWS) {
-            const bf16* src_row = W + (size_t)min(n0 + lane, N - 1) * ldw;  // rows beyond N re-read the last one
-            for (int it = 0; it < iters; ++it) {
-                const int s = it % GS_STAGES;
-                if (it >= GS_STAGES) {                                   // lane 0 waits for the consumers, all 16 follow it
-                    int ok = 1;
-                    if (lane == 0) ok = mbar_wait_bounded(&empty_bar[s], (unsigned)((it / GS_STAGES - 1) & 1)) ? 1 : 0;
-                    ok = __shfl_sync(0x0000ffffu, ok, 0);
-                    if (!ok) {
-                        if (lane == 0 && err) atomicOr(err, VL_DEV_WAIT_EXPIRED);
-                        break;
+            int git = 0;                                                 // stages issued so far, over all tiles
+            for (int n0 = r0; n0 < r1; n0 += GS_ROWS) {
+                const int valid = min(GS_ROWS, r1 - n0);                   // rows of this tile; the others are not copied
+                const bf16* src_row = W + (size_t)min(n0 + lane, N - 1) * ldw;
+                bool stop = false;
+                for (int it = 0; it < iters; ++it, ++git) {
+                    const int s = git % GS_STAGES;
+                    if (git >= GS_STAGES) {                              // lane 0 waits for the consumers, all 16 follow it
+                        int ok = 1;
+                        if (lane == 0) ok = mbar_wait_bounded(&empty_bar[s], (unsigned)((git / GS_STAGES - 1) & 1)) ? 1 : 0;
+                        ok = __shfl_sync(0x0000ffffu, ok, 0);
+                        if (!ok) {
+                            if (lane == 0 && err) atomicOr(err, VL_DEV_WAIT_EXPIRED);
+                            stop = true;
+                            break;
+                        }
                     }
+                    const int k0 = it * GS_KC;
+                    const unsigned bytes = (unsigned)(min(GS_KC, K - k0) * 2);
+                    if (lane == 0) mbar_arrive_expect_tx(&full_bar[s], bytes * (unsigned)valid);
+                    __syncwarp(0x0000ffffu);
+                    if (lane < valid)
+                        bulk_copy_g2s(gs_smem + ((size_t)s * GS_ROWS + lane) * GS_ROWB, src_row + k0, bytes, &full_bar[s]);
                 }
-                const int k0 = it * GS_KC;
-                const unsigned bytes = (unsigned)(min(GS_KC, K - k0) * 2);
-                if (lane == 0) mbar_arrive_expect_tx(&full_bar[s], bytes * GS_ROWS);
-                __syncwarp(0x0000ffffu);
-                bulk_copy_g2s(gs_smem + ((size_t)s * GS_ROWS + lane) * GS_ROWB, src_row + k0, bytes, &full_bar[s]);
+                if (stop) break;
             }
         }
         return;
@@ -139,10 +150,11 @@ gemm_bf16_small_m_kernel(const bf16* __restrict__ A, const bf16* __restrict__ W,
                 dst[u][j] = (it < iters && k + 8 * t < K) ? __ldg(reinterpret_cast<const uint4*>(a_row[j] + k)) : zero;
         }
     };
+    int git = 0;                                                           // stages consumed so far, over all tiles
     auto multiply = [&](int it, const uint4 (&a)[STEPS][MT]) -> bool {
-        const int s = it % GS_STAGES;
+        const int s = git % GS_STAGES;
         const int kbase = it * GS_KC + warp * (GS_KC / GS_CONSUMERS);
-        if (!mbar_wait_bounded(&full_bar[s], (unsigned)((it / GS_STAGES) & 1))) {
+        if (!mbar_wait_bounded(&full_bar[s], (unsigned)((git / GS_STAGES) & 1))) {
             if (lane == 0 && err) atomicOr(err, VL_DEV_WAIT_EXPIRED);
             return false;
         }
@@ -162,15 +174,22 @@ gemm_bf16_small_m_kernel(const bf16* __restrict__ A, const bf16* __restrict__ W,
         }
         __syncwarp();
         if (lane == 0) mbar_arrive(&empty_bar[s]);
+        ++git;
         return true;
     };
+    for (int n0 = r0; n0 < r1; n0 += GS_ROWS) {
+#pragma unroll
+    for (int j = 0; j < MT; ++j)
+#pragma unroll
+        for (int i = 0; i < 4; ++i) acc[j][i] = 0.f;
+    bool ok = true;
     load_a(0, av[0]);
     for (int it = 0; it < iters; it += 2) {                                 // two stages per round: the buffers swap roles
         load_a(it + 1, av[1]);
-        if (!multiply(it, av[0])) break;
+        if (!multiply(it, av[0])) { ok = false; break; }
         if (it + 1 >= iters) break;
         load_a(it + 2, av[0]);
-        if (!multiply(it + 1, av[1])) break;
+        if (!multiply(it + 1, av[1])) { ok = false; break; }
     }
     // acc[j] = {(row g, m 2t), (row g, m 2t+1), (row g+8, m 2t), (row g+8, m 2t+1)} of m-tile j
 #pragma unroll
@@ -182,54 +201,64 @@ gemm_bf16_small_m_kernel(const bf16* __restrict__ A, const bf16* __restrict__ W,
     }
     consumer_barrier();
     if (swiglu) {
-        // the block's 16 rows of W are 8 gate rows and their 8 up rows: C[m, n0/2 + i] = silu(gate_i) * up_i
+        // the tile's 16 rows of W are 8 gate rows and their 8 up rows: C[m, n0/2 + i] = silu(gate_i) * up_i
         for (int idx = tid; idx < MT * 8 * 8; idx += 32 * GS_CONSUMERS) {
             const int i = idx & 7, m = idx >> 3;
             const int j = m >> 3, mm = m & 7;
-            if (m < M && n0 + 8 + i < N) {
+            if (m < M && n0 + 8 + i < r1) {
                 float gt = red[0][j][i][mm], up = red[0][j][i + 8][mm];
 #pragma unroll
                 for (int w = 1; w < GS_CONSUMERS; ++w) { gt += red[w][j][i][mm]; up += red[w][j][i + 8][mm]; }
                 C[(size_t)m * ldc + n0 / 2 + i] = from_f32<TO>(gt / (1.0f + expf(-gt)) * up);
             }
         }
-        return;
-    }
-    for (int idx = tid; idx < MT * 8 * GS_ROWS; idx += 32 * GS_CONSUMERS) {
-        const int n = idx % GS_ROWS, m = idx / GS_ROWS;                    // n fastest: 16 neighbours of a row of C
-        const int j = m >> 3, mm = m & 7;
-        if (m < M && n0 + n < N) {
-            float v = red[0][j][n][mm];
+    } else {
+        for (int idx = tid; idx < MT * 8 * GS_ROWS; idx += 32 * GS_CONSUMERS) {
+            const int n = idx % GS_ROWS, m = idx / GS_ROWS;                // n fastest: 16 neighbours of a row of C
+            const int j = m >> 3, mm = m & 7;
+            if (ok && m < M && n0 + n < r1) {
+                float v = red[0][j][n][mm];
 #pragma unroll
-            for (int w = 1; w < GS_CONSUMERS; ++w) v += red[w][j][n][mm];
-            C[(size_t)m * ldc + n0 + n] = from_f32<TO>(v);
+                for (int w = 1; w < GS_CONSUMERS; ++w) v += red[w][j][n][mm];
+                C[(size_t)m * ldc + n0 + n] = from_f32<TO>(v);
+            }
         }
+    }
+    consumer_barrier();                                                    // `red` is free for the next tile
+    if (!ok) break;                                                        // a wait ran out: the error word says so
     }
 }
 
 template <typename TO>
 static int launch_small_m(const bf16* A, const bf16* W, TO* C, int M, int N, int K, int lda, int ldw, int ldc,
                           unsigned* err, int swiglu, cudaStream_t s) {
-    dim3 grid((N + GS_ROWS - 1) / GS_ROWS);
     static int num_sms = 0;
     if (!num_sms) {
         int dev = 0;
         cudaGetDevice(&dev);
         if (cudaDeviceGetAttribute(&num_sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || num_sms <= 0) num_sms = 148;
     }
+    // A block per tile of 16 rows, or, when that gives more blocks than fit on the device at once, as
+    // many blocks as fit, each with an even share of the rows (for the fused activation: of the
+    // 16-row groups), so that no SM is left with a last partial round.
 #define GS_LAUNCH(MT, KC, STAGES)                                                                          \
     {                                                                                                      \
         const size_t smem = (size_t)STAGES * GS_ROWS * (KC * 2 + 16);                                      \
         auto kern = gemm_bf16_small_m_kernel<MT, TO, KC, STAGES>;                                          \
         cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
         if (e != cudaSuccess) return (int)e;                                                               \
-        return vl_launch(kern, grid, dim3(160), smem, s, A, W, C, M, N, K, lda, ldw, ldc, err, swiglu);    \
+        static int per_sm = 0;                                                                             \
+        if (!per_sm && (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kern, 160, smem) != cudaSuccess || per_sm < 1)) per_sm = 1; \
+        const int tiles = (N + GS_ROWS - 1) / GS_ROWS, fit = num_sms * per_sm;                             \
+        const int gran = swiglu ? GS_ROWS : 1;                                                             \
+        dim3 grid(tiles < fit ? tiles : fit);                                                              \
+        return vl_launch(kern, grid, dim3(160), smem, s, A, W, C, M, N, K, lda, ldw, ldc, err, swiglu, gran); \
     }
     // Measured on the shapes of decode steps: up to 8 rows run best with three larger stages (three
     // blocks per SM; two, with still larger stages, when the blocks are so few that all are resident
     // and K is long); more rows need the registers and keep four stages of 512 columns.
     if (M <= 8) {
-        if ((int)grid.x <= 2 * num_sms && K >= 8192) GS_LAUNCH(1, 1024, 3)
+        if ((N + GS_ROWS - 1) / GS_ROWS <= 2 * num_sms && K >= 8192) GS_LAUNCH(1, 1024, 3)
         GS_LAUNCH(1, 768, 3)
     }
     if (M <= 16) GS_LAUNCH(2, 512, 4)
