@@ -146,6 +146,39 @@ def test_gemm_bf16_tcgen05(M, N, K, out_dtype):
         assert float((out.double() - ref).abs().max()) <= 2 ** -8 * scale + 1e-6
 
 
+@pytest.mark.parametrize("M,H,K,N2,swiglu", [(1, 96, 64, 80, False), (8, 4096, 4096, 6144, False), (5, 200, 520, 48, True),
+                                               (13, 1000, 264, 64, True), (16, 4096, 12288, 24576, True)])
+def test_gemm_small_m_with_fused_norms(M, H, K, N2, swiglu):
+    """Two products with an RMS norm between them and no kernel for the norm: the first adds its
+    result into the float32 stream and leaves the norm's input times the norm's weight and the
+    sums of squares; the second scales its rows."""
+    torch.manual_seed(M + H)
+    eps = 1e-5
+    x = torch.randn(M, H, device=DEV) * 3
+    a = torch.randn(M, K, device=DEV).to(torch.bfloat16)
+    w1 = (torch.randn(H, K, device=DEV) * 0.05).to(torch.bfloat16)
+    nw = 1 + 0.1 * torch.randn(H, device=DEV)
+    w2 = (torch.randn(N2, H, device=DEV) * 0.05).to(torch.bfloat16)
+    x_new = x.double() + a.double() @ w1.double().T
+    h = x_new / torch.sqrt((x_new * x_new).mean(dim=1, keepdim=True) + eps) * nw.double()
+    y = h @ w2.double().T
+    if swiglu:                                   # rows of w2: blocks of 8 gate rows and their 8 up rows
+        y = y.view(M, N2 // 16, 2, 8)
+        y = (torch.nn.functional.silu(y[:, :, 0]) * y[:, :, 1]).reshape(M, N2 // 2)
+    stream = x.clone()
+    rows = torch.empty(M, H, device=DEV, dtype=torch.bfloat16)
+    partial = torch.full((ops().NORM_PARTIALS, 16), float("nan"), device=DEV)
+    count = ops().gemm_bf16_small_m(a, w1, rows, err_word(), sink=(stream, nw, partial))
+    assert 0 < count <= ops().NORM_PARTIALS
+    assert float((stream.double() - x_new).abs().max()) <= 1e-5 * float(x_new.abs().max()) * K ** 0.5
+    assert torch.allclose(rows.double(), x_new * nw.double(), atol=2 ** -7 * float(x_new.abs().max()), rtol=0)
+    ss = partial[:count, :M].double().sum(dim=0)
+    assert torch.allclose(ss, (x_new * x_new).sum(dim=1), rtol=1e-5)
+    out = torch.empty(M, N2 // 2 if swiglu else N2, device=DEV, dtype=torch.bfloat16)
+    ops().gemm_bf16_small_m(rows, w2, out, err_word(), swiglu=swiglu, scaled=(partial, count, eps, H))
+    assert float((out.double() - y).abs().max()) <= 2e-2 * float(y.abs().max()) + 1e-3
+
+
 @pytest.mark.parametrize("kernel,M", [("small_m", 1), ("small_m", 8), ("small_m", 13), ("tc5", 128), ("tc5", 300), ("tc5", 2048)])
 @pytest.mark.parametrize("I,K", [(160, 96), (12288, 4096), (24, 64)])
 def test_gemm_with_fused_swiglu(kernel, M, I, K):

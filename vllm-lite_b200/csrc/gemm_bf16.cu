@@ -1,7 +1,7 @@
 // bfloat16 matrix products with float32 accumulation:  C[M,N] = A[M,K] * W[N,K]^T
 // (a linear layer, y = x W^T, weight stored [out, in], no bias).
 //
-// vl_gemm_bf16_small_m: for the few rows of a decode step (M <= 64).  The product is bound by
+// vl_gemm_bf16_small_m: for the few rows of a decode step (M <= 16).  The product is bound by
 // reading W once from HBM, so the kernel is built around that stream: a block owns 16 rows of W,
 // a producer warp brings them in by bulk copies (TMA) through a ring of shared-memory stages, and
 // four consumer warps multiply on the tensor cores (mma.sync m16n8k16, W as the 16-row operand,
@@ -11,7 +11,7 @@
 // stand for any 8 of the 16 positions of a slice as long as both operands use the same
 // assignment; that is what lets each lane load whole 16-byte pieces.  The 4 warps' partial sums
 // are added in warp order, so the result does not depend on the launch.
-// K must be a multiple of 8 (16-byte rows); any M <= 64 and any N.
+// K must be a multiple of 8 (16-byte rows); any M <= 16 and any N.
 #include "common.cuh"
 
 #define GS_ROWS 16
@@ -64,6 +64,18 @@ __device__ __forceinline__ void consumer_barrier() { asm volatile("bar.sync 1, 1
 
 #define GS_CONSUMERS 4                     // consumer warps; warp 4 is the producer
 
+// Optional fusion of an RMS norm on either side of the product (both sides null: a plain product).
+//   Input side (ss_in): the rows of A are not yet normalised, A[m, k] = x[m, k] * w_norm[k]; row m of
+//   the result is scaled by 1 / sqrt(sum_b ss_in[b * 16 + m] / hidden + eps), where the ss_count
+//   vectors are the partial sums of squares that the producer of x left, block by block.
+//   Output side (res): the result is added into the float32 stream res[m, n] (each block owns its
+//   columns), C receives the next norm's unnormalised input bf16(res[m, n] * next_w[n]), and the
+//   block's partial sums of squares of its columns of res go to ss_out[block * 16 + m].
+struct NormFusion {
+    const float* ss_in; int ss_count; float eps; int hidden;
+    float* res; int ldres; const float* next_w; float* ss_out;
+};
+
 // Block = 16 rows of W.  The producer warp streams them through a ring of GS_STAGES stages of
 // GS_KC columns (a multiple of 128) with one bulk copy (TMA) per row and stage; four consumer warps
 // each take a quarter of every stage, read their tensor-core operands from shared memory (W) and
@@ -73,11 +85,13 @@ __device__ __forceinline__ void consumer_barrier() { asm volatile("bar.sync 1, 1
 template <int MT, typename TO, int GS_KC, int GS_STAGES>
 __global__ void __launch_bounds__(160)
 gemm_bf16_small_m_kernel(const bf16* __restrict__ A, const bf16* __restrict__ W, TO* __restrict__ C,
-                         int M, int N, int K, int lda, int ldw, int ldc, unsigned* err, int swiglu, int gran) {
+                         int M, int N, int K, int lda, int ldw, int ldc, unsigned* err, int swiglu, int gran,
+                         NormFusion nf) {
     static_assert(GS_KC % (32 * GS_CONSUMERS) == 0, "a stage is shared out in 32-wide slices among the consumer warps");
     constexpr int GS_ROWB = GS_KC * 2 + 16;    // bytes of a padded row of a stage: rows 16 bytes apart modulo 128
     extern __shared__ __align__(128) unsigned char gs_smem[];               // [GS_STAGES][16][GS_ROWB]
     __shared__ float red[GS_CONSUMERS][MT][GS_ROWS][8];
+    __shared__ float s_inv[16];                                             // row scales of a fused input norm
     __shared__ __align__(8) unsigned long long full_bar[GS_STAGES], empty_bar[GS_STAGES];
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     // rows of W of this block: an even share of N, in units of `gran` rows, walked in tiles of 16
@@ -126,6 +140,20 @@ gemm_bf16_small_m_kernel(const bf16* __restrict__ A, const bf16* __restrict__ W,
     // ---- consumers ----
     pdl_wait();                                                            // A comes from the kernel before
     const int g = lane >> 2, t = lane & 3;
+    if (nf.ss_in) {
+        // 8 threads per row add the producer's partial sums, each its share in a fixed order
+        const int m = tid >> 3, part = tid & 7;
+        float ss = 0.f;
+        for (int b = part; b < nf.ss_count; b += 8) ss += nf.ss_in[(size_t)b * 16 + m];
+        ss += __shfl_xor_sync(0xffffffffu, ss, 1);
+        ss += __shfl_xor_sync(0xffffffffu, ss, 2);
+        ss += __shfl_xor_sync(0xffffffffu, ss, 4);
+        if (part == 0) s_inv[m] = 1.0f / sqrtf(ss / (float)nf.hidden + nf.eps);
+        consumer_barrier();
+    }
+    float ss_run[MT];                                                      // (threads with n = 0) sums of squares of this block's columns
+#pragma unroll
+    for (int j = 0; j < MT; ++j) ss_run[j] = 0.f;
     const bf16* a_row[MT];
 #pragma unroll
     for (int j = 0; j < MT; ++j) a_row[j] = A + (size_t)min(8 * j + g, M - 1) * lda + 8 * t;
@@ -205,33 +233,60 @@ gemm_bf16_small_m_kernel(const bf16* __restrict__ A, const bf16* __restrict__ W,
         for (int idx = tid; idx < MT * 8 * 8; idx += 32 * GS_CONSUMERS) {
             const int i = idx & 7, m = idx >> 3;
             const int j = m >> 3, mm = m & 7;
-            if (m < M && n0 + 8 + i < r1) {
+            if (ok && m < M && n0 + 8 + i < r1) {
                 float gt = red[0][j][i][mm], up = red[0][j][i + 8][mm];
 #pragma unroll
                 for (int w = 1; w < GS_CONSUMERS; ++w) { gt += red[w][j][i][mm]; up += red[w][j][i + 8][mm]; }
+                if (nf.ss_in) { gt *= s_inv[m]; up *= s_inv[m]; }
                 C[(size_t)m * ldc + n0 / 2 + i] = from_f32<TO>(gt / (1.0f + expf(-gt)) * up);
             }
         }
     } else {
-        for (int idx = tid; idx < MT * 8 * GS_ROWS; idx += 32 * GS_CONSUMERS) {
+#pragma unroll
+        for (int p = 0; p < MT; ++p) {                                     // 128 threads x MT passes = MT * 8 rows x 16 columns
+            const int idx = tid + p * 32 * GS_CONSUMERS;
             const int n = idx % GS_ROWS, m = idx / GS_ROWS;                // n fastest: 16 neighbours of a row of C
             const int j = m >> 3, mm = m & 7;
-            if (ok && m < M && n0 + n < r1) {
+            const bool valid = ok && m < M && n0 + n < r1;
+            float sq = 0.f;
+            if (valid) {
                 float v = red[0][j][n][mm];
 #pragma unroll
                 for (int w = 1; w < GS_CONSUMERS; ++w) v += red[w][j][n][mm];
+                if (nf.ss_in) v *= s_inv[m];
+                if (nf.res) {
+                    float* rp = nf.res + (size_t)m * nf.ldres + n0 + n;
+                    const float r = *rp + v;
+                    *rp = r;
+                    sq = r * r;
+                    v = r * nf.next_w[n0 + n];
+                }
                 C[(size_t)m * ldc + n0 + n] = from_f32<TO>(v);
+            }
+            if (nf.res) {                                                  // (uniform) the 16 threads of a row add their squares
+                sq += __shfl_xor_sync(0xffffffffu, sq, 1);
+                sq += __shfl_xor_sync(0xffffffffu, sq, 2);
+                sq += __shfl_xor_sync(0xffffffffu, sq, 4);
+                sq += __shfl_xor_sync(0xffffffffu, sq, 8);
+                ss_run[p] += sq;
             }
         }
     }
     consumer_barrier();                                                    // `red` is free for the next tile
     if (!ok) break;                                                        // a wait ran out: the error word says so
     }
+    if (nf.ss_out && (tid & 15) == 0) {
+#pragma unroll
+        for (int p = 0; p < MT; ++p) {
+            const int m = (tid + p * 32 * GS_CONSUMERS) / GS_ROWS;
+            if (m < 16) nf.ss_out[(size_t)blockIdx.x * 16 + m] = m < M ? ss_run[p] : 0.f;
+        }
+    }
 }
 
 template <typename TO>
 static int launch_small_m(const bf16* A, const bf16* W, TO* C, int M, int N, int K, int lda, int ldw, int ldc,
-                          unsigned* err, int swiglu, cudaStream_t s) {
+                          unsigned* err, int swiglu, NormFusion nf, int* grid_out, cudaStream_t s) {
     static int num_sms = 0;
     if (!num_sms) {
         int dev = 0;
@@ -252,7 +307,8 @@ static int launch_small_m(const bf16* A, const bf16* W, TO* C, int M, int N, int
         const int tiles = (N + GS_ROWS - 1) / GS_ROWS, fit = num_sms * per_sm;                             \
         const int gran = swiglu ? GS_ROWS : 1;                                                             \
         dim3 grid(tiles < fit ? tiles : fit);                                                              \
-        return vl_launch(kern, grid, dim3(160), smem, s, A, W, C, M, N, K, lda, ldw, ldc, err, swiglu, gran); \
+        if (grid_out) *grid_out = (int)grid.x;                                                             \
+        return vl_launch(kern, grid, dim3(160), smem, s, A, W, C, M, N, K, lda, ldw, ldc, err, swiglu, gran, nf); \
     }
     // Measured on the shapes of decode steps: up to 8 rows run best with three larger stages (three
     // blocks per SM; two, with still larger stages, when the blocks are so few that all are resident
@@ -261,21 +317,42 @@ static int launch_small_m(const bf16* A, const bf16* W, TO* C, int M, int N, int
         if ((N + GS_ROWS - 1) / GS_ROWS <= 2 * num_sms && K >= 8192) GS_LAUNCH(1, 1024, 3)
         GS_LAUNCH(1, 768, 3)
     }
-    if (M <= 16) GS_LAUNCH(2, 512, 4)
-    if (M <= 32) GS_LAUNCH(4, 512, 4)
-    GS_LAUNCH(8, 512, 4)
+    GS_LAUNCH(2, 512, 4)
 #undef GS_LAUNCH
+}
+
+// The product with an RMS norm fused on its input side (ss_in != null), on its output side
+// (res != null), on both, or on neither; see NormFusion.  Fusion takes up to 16 rows, no fused
+// activation on the output side, and bfloat16 C there.  grid_out (host, may be null) receives the
+// number of blocks launched = the number of partial-sum vectors written to ss_out.
+extern "C" int vl_gemm_bf16_small_m_fused(const void* A, const void* W, void* C, int out_dtype, int M, int N, int K,
+                                          int lda, int ldw, int ldc, unsigned* err, int swiglu,
+                                          const float* ss_in, int ss_count, float eps, int hidden,
+                                          float* res, int ldres, const float* next_w, float* ss_out,
+                                          int* grid_out, void* stream) {
+    if (M <= 0 || N <= 0) return VL_OK;
+    if (swiglu && (N % 16 || ldc < N / 2)) return VL_ERR_ARGUMENT;
+    if (M > 16 || K <= 0 || K % 8 || lda % 8 || ldw % 8) return VL_ERR_UNSUPPORTED;
+    if (lda < K || ldw < K || (!swiglu && ldc < N)) return VL_ERR_ARGUMENT;
+    if (((uintptr_t)A | (uintptr_t)W) & 15) return VL_ERR_UNSUPPORTED;
+    NormFusion nf = {};
+    if (ss_in) {
+        if (ss_count <= 0 || hidden <= 0) return VL_ERR_ARGUMENT;
+        nf.ss_in = ss_in; nf.ss_count = ss_count; nf.eps = eps; nf.hidden = hidden;
+    }
+    if (res) {
+        if (swiglu || out_dtype != VL_BF16) return VL_ERR_UNSUPPORTED;
+        if (!next_w || !ss_out || ldres < N) return VL_ERR_ARGUMENT;
+        nf.res = res; nf.ldres = ldres; nf.next_w = next_w; nf.ss_out = ss_out;
+    }
+    cudaStream_t s = (cudaStream_t)stream;
+    if (out_dtype == VL_BF16) return launch_small_m<bf16>((const bf16*)A, (const bf16*)W, (bf16*)C, M, N, K, lda, ldw, ldc, err, swiglu, nf, grid_out, s);
+    if (out_dtype == VL_F32) return launch_small_m<float>((const bf16*)A, (const bf16*)W, (float*)C, M, N, K, lda, ldw, ldc, err, swiglu, nf, grid_out, s);
+    return VL_ERR_UNSUPPORTED;
 }
 
 extern "C" int vl_gemm_bf16_small_m(const void* A, const void* W, void* C, int out_dtype, int M, int N, int K,
                                     int lda, int ldw, int ldc, unsigned* err, int swiglu, void* stream) {
-    if (M <= 0 || N <= 0) return VL_OK;
-    if (swiglu && (N % 16 || ldc < N / 2)) return VL_ERR_ARGUMENT;
-    if (M > 64 || K <= 0 || K % 8 || lda % 8 || ldw % 8) return VL_ERR_UNSUPPORTED;
-    if (lda < K || ldw < K || (!swiglu && ldc < N)) return VL_ERR_ARGUMENT;
-    if (((uintptr_t)A | (uintptr_t)W) & 15) return VL_ERR_UNSUPPORTED;
-    cudaStream_t s = (cudaStream_t)stream;
-    if (out_dtype == VL_BF16) return launch_small_m<bf16>((const bf16*)A, (const bf16*)W, (bf16*)C, M, N, K, lda, ldw, ldc, err, swiglu, s);
-    if (out_dtype == VL_F32) return launch_small_m<float>((const bf16*)A, (const bf16*)W, (float*)C, M, N, K, lda, ldw, ldc, err, swiglu, s);
-    return VL_ERR_UNSUPPORTED;
+    return vl_gemm_bf16_small_m_fused(A, W, C, out_dtype, M, N, K, lda, ldw, ldc, err, swiglu,
+                                      nullptr, 0, 0.f, 0, nullptr, 0, nullptr, nullptr, nullptr, stream);
 }

@@ -61,6 +61,9 @@ _SIGNATURES = {
     ("gemm_f32", "vl_gemm_f32_nt"): [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p],
     ("gemm_bf16", "vl_gemm_bf16_small_m"): [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
                                             c_void_p, c_int, c_void_p],
+    ("gemm_bf16", "vl_gemm_bf16_small_m_fused"): [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
+                                                  c_void_p, c_int, c_void_p, c_int, c_float, c_int, c_void_p, c_int,
+                                                  c_void_p, c_void_p, c_void_p, c_void_p],
     ("gemm_tc5", "vl_gemm_bf16_tc5"): [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
                                        c_void_p, c_int, c_void_p],
     ("sampling", "vl_apply_penalties"): [c_void_p, c_longlong, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p,
@@ -406,14 +409,39 @@ def _gemm_shapes(a, w, out, swiglu):
     return M, N, K, width
 
 
-def gemm_bf16_small_m(a, w, out, err=None, swiglu=False):
+NORM_PARTIALS = 1024      # vectors of 16 partial sums a product kernel may leave (at least its number of blocks)
+
+
+def gemm_bf16_small_m(a, w, out, err=None, swiglu=False, scaled=None, sink=None):
     """out[M, N] = a[M, K] @ w[N, K]^T for M <= 16: bfloat16 operands, float32 accumulation,
     out bfloat16 or float32.  Bound by one read of w.  swiglu: w holds blocks of 8 gate rows and
-    their 8 up rows, out is [M, N/2] = silu(gate) * up."""
+    their 8 up rows, out is [M, N/2] = silu(gate) * up.
+    scaled = (partial float32 [>= count, 16], count, eps, size): the rows of `a` are an RMS norm's
+    output without its scales; row m of the result is scaled by 1/sqrt(sum_b partial[b, m]/size + eps).
+    sink = (x float32 [M, N], next_weight float32 [N], partial_out float32 [NORM_PARTIALS, 16]): the
+    result is added into x, out receives bf16(x * next_weight) and partial_out the sums of squares of x
+    block by block; returns the number of vectors written instead of out."""
     M, N, K, width = _gemm_shapes(a, w, out, swiglu)
-    _check(_fn("gemm_bf16", "vl_gemm_bf16_small_m")(_ptr(a), _ptr(w), _ptr(out), dtype_code(out.dtype), M, N, K,
-                                                    K, K, width, _ptr(err), int(swiglu), _stream()),
-           "vl_gemm_bf16_small_m")
+    ss_in, count, eps, size = (None, 0, 0.0, 0) if scaled is None else scaled
+    x, next_w, ss_out = (None, None, None) if sink is None else sink
+    if scaled is not None:
+        _need(ss_in, torch.float32, "partial", 2)
+        if ss_in.shape[1] != 16 or not 0 < count <= ss_in.shape[0] or size != K:
+            raise KernelError("gemm_bf16_small_m: partial sums do not match the product")
+    grid = ctypes.c_int(0)
+    if sink is not None:
+        _need(x, torch.float32, "x", 2); _need(next_w, torch.float32, "next_weight", 1)
+        _need(ss_out, torch.float32, "partial_out", 2)
+        if x.shape != (M, N) or next_w.shape[0] != N or ss_out.shape != (NORM_PARTIALS, 16) or swiglu:
+            raise KernelError("gemm_bf16_small_m: the stream, the next weight or the partial sums do not match")
+    _check(_fn("gemm_bf16", "vl_gemm_bf16_small_m_fused")(
+        _ptr(a), _ptr(w), _ptr(out), dtype_code(out.dtype), M, N, K, K, K, width, _ptr(err), int(swiglu),
+        _ptr(ss_in), int(count), float(eps), int(size), _ptr(x), N, _ptr(next_w), _ptr(ss_out),
+        ctypes.addressof(grid) if sink is not None else None, _stream()), "vl_gemm_bf16_small_m")
+    if sink is not None:
+        if not 0 < grid.value <= NORM_PARTIALS:
+            raise KernelError(f"gemm_bf16_small_m: {grid.value} blocks do not fit the partial sums")
+        return grid.value
     return out
 
 

@@ -63,7 +63,11 @@ class GqaAttention:
             self.position = POSITIONS.get(spec.position.kind)(spec.position, sub_weights(weights, "rotary."), ctx)
         self.scale = spec.scale if spec.scale is not None else spec.head_dim ** -0.5
 
-    def __call__(self, h, step, cache):
+    def factors_norms(self, M) -> bool:
+        """For M rows: the input may come as `ScaledRows` and the result may go `into_stream`."""
+        return self.qkv_proj.factors_norms(M) and self.o_proj.factors_norms(M)
+
+    def __call__(self, h, step, cache, sink=None):
         from ..csrc import ops
         s = self.spec
         group = step.groups[cache.group]
@@ -83,4 +87,6 @@ class GqaAttention:
         out = step.workspace.get(step.tag + "attn.out", (qkv.shape[0], s.num_heads * s.head_dim), self.dtype)
         from . import attention_dispatch
         attention_dispatch.run(qkv, out, cache, group, step, s, self.scale)
+        if sink is not None:
+            return self.o_proj.into_stream(out, sink, step, "attn.o")
         return self.o_proj(out, step, "attn.o")

@@ -122,6 +122,32 @@ class CallCache:
 class Residual:
     x: torch.Tensor                           # float32 [T, H]
     pending: Optional[torch.Tensor] = None    # not yet added into x
+    normed: Optional["ScaledRows"] = None     # output of the norm `normed_for` on x, in factored form
+    normed_for: object = None
+
+
+@dataclass
+class ScaledRows:
+    """The output of an RMS norm in factored form, as input of a linear layer: row m of the matrix is
+    rows[m] * scale[m] with scale[m] = 1 / sqrt(sum_b partial[b, m] / size + eps).  `rows` already
+    carries the norm's weight; the partial sums of squares of the stream were left by the kernel
+    that last wrote the stream, one vector per block, and the product kernel that reads `rows`
+    applies the scales to its result.  It saves the norm's own kernel in steps of few rows."""
+    rows: torch.Tensor                        # [M, size], activation dtype
+    partial: torch.Tensor                     # float32 [capacity, 16]
+    count: int
+    eps: float
+    size: int
+
+
+@dataclass
+class StreamSink:
+    """Offer to a part whose last step is a linear layer: add your result into the float32 stream `x`
+    yourself and return the next norm's output (weight `weight`) as ScaledRows."""
+    x: torch.Tensor
+    weight: torch.Tensor                      # float32 [size]
+    eps: float
+    size: int
 
 
 def sub_weights(weights: dict, prefix: str) -> dict:

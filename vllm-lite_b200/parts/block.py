@@ -2,10 +2,14 @@
 (crates/model/src/components/decoder_block/mod.rs:66-85 of the reference).
 
 The residual stream is float32.  A sub-layer's output is not added at once: it is
-left pending and the next norm's kernel adds it while it reads the stream."""
+left pending and the next norm's kernel adds it while it reads the stream.  In a
+step of few rows the norms' kernels are saved altogether where the neighbouring
+parts can: the part before a norm adds its result into the stream itself and
+leaves the norm's output in factored form (`ScaledRows`), which the part after
+the norm takes as it is."""
 from __future__ import annotations
 
-from .base import prefixed, sub_weights
+from .base import StreamSink, prefixed, sub_weights
 from .registry import BLOCKS, FEED_FORWARDS, MIXERS, NORMS
 from .spec import BlockSpec
 
@@ -36,8 +40,38 @@ class PreNormBlock:
         self.ffn = FEED_FORWARDS.get(spec.ffn.kind)(spec.ffn, sub_weights(weights, FFN), ctx)
         self.graph_safe = bool(getattr(self.mixer, "graph_safe", False) and getattr(self.ffn, "graph_safe", False))
 
-    def __call__(self, residual, step, cache):
-        h = self.norm1(residual.x, residual.pending, step, tag="norm1")
-        a = self.mixer(h, step, cache)
-        h = self.norm2(residual.x, a, step, tag="norm2")
-        residual.pending = self.ffn(h, step)
+    chains_norms = True        # __call__ takes `next_norm`
+
+    def input_norm_for_fusion(self, M):
+        """The first norm, if the block before may compute it for M rows in factored form."""
+        ok = getattr(self.norm1, "factorable", False) and _factors(self.mixer, M)
+        return self.norm1 if ok else None
+
+    def __call__(self, residual, step, cache, next_norm=None):
+        """next_norm: the norm that will read the stream after this block, when its reader can take
+        the factored form (`input_norm_for_fusion` of the next block)."""
+        M = step.num_tokens
+        if residual.normed is not None and residual.normed_for is self.norm1:
+            h = residual.normed                                   # left by the block before
+        else:
+            h = self.norm1(residual.x, residual.pending, step, tag="norm1")
+        residual.pending = residual.normed = residual.normed_for = None
+        if _factors(self.mixer, M) and getattr(self.norm2, "factorable", False) and _factors(self.ffn, M):
+            h = self.mixer(h, step, cache, sink=_sink(residual, self.norm2))
+        else:
+            a = self.mixer(h, step, cache)
+            h = self.norm2(residual.x, a, step, tag="norm2")
+        if next_norm is not None and _factors(self.ffn, M):
+            residual.normed = self.ffn(h, step, sink=_sink(residual, next_norm))
+            residual.normed_for = next_norm
+        else:
+            residual.pending = self.ffn(h, step)
+
+
+def _factors(part, M) -> bool:
+    f = getattr(part, "factors_norms", None)
+    return bool(f and f(M))
+
+
+def _sink(residual, norm) -> StreamSink:
+    return StreamSink(residual.x, norm.weight, norm.spec.eps, norm.spec.size)

@@ -9,6 +9,8 @@ from __future__ import annotations
 
 import torch
 
+from .base import ScaledRows, StreamSink
+
 
 class Linear:
     def __init__(self, weight: torch.Tensor):
@@ -17,12 +19,35 @@ class Linear:
         self.weight = weight
         self.out_features, self.in_features = weight.shape
 
+    def factors_norms(self, M) -> bool:
+        """Whether, for M rows, this layer's kernel can take an RMS norm's output in factored form
+        (`ScaledRows`) and can add its result into the stream (`into_stream`)."""
+        from ..csrc import ops
+        return self.weight.dtype == torch.bfloat16 and ops.gemm_bf16_small_m_ok(M, self.in_features)
+
+    def into_stream(self, a, sink: StreamSink, step, tag) -> ScaledRows:
+        """sink.x += a W^T; returns the next norm's output on the new stream, in factored form."""
+        from ..csrc import ops
+        M = a.shape[0]
+        ws = step.workspace
+        rows = ws.get(step.tag + tag + ".rows", (M, self.out_features), torch.bfloat16)
+        partial = ws.get(step.tag + tag + ".ss", (ops.NORM_PARTIALS, 16), torch.float32)
+        count = ops.gemm_bf16_small_m(a, self.weight, rows, step.err, sink=(sink.x, sink.weight, partial))
+        return ScaledRows(rows, partial, count, sink.eps, sink.size)
+
     def swiglu(self, a, step, tag, group):
         """silu(gate) * up of y = a W^T, W holding gate and up rows (interleaved in blocks of `group`
         rows, or gate rows then up rows when group is 0): [M, out_features / 2].  The activation runs
         inside the product kernel when that kernel can, else in a kernel of its own."""
         from ..csrc import ops
         from . import matmul
+        if isinstance(a, ScaledRows):
+            M = a.rows.shape[0]
+            if group != ops.SWIGLU_GROUP or not self.factors_norms(M):
+                raise TypeError("this layer cannot take a norm's output in factored form")
+            out = step.workspace.get(step.tag + tag + ".act", (M, self.out_features // 2), a.rows.dtype)
+            return ops.gemm_bf16_small_m(a.rows, self.weight, out, step.err, swiglu=True,
+                                         scaled=(a.partial, a.count, a.eps, a.size))
         M = a.shape[0]
         ws = step.workspace
         out = ws.get(step.tag + tag + ".act", (M, self.out_features // 2), a.dtype)
@@ -34,6 +59,12 @@ class Linear:
     def __call__(self, a, step, tag, out_dtype=None):
         from ..csrc import ops
         from . import matmul
+        if isinstance(a, ScaledRows):
+            M = a.rows.shape[0]
+            if not self.factors_norms(M):
+                raise TypeError("this layer cannot take a norm's output in factored form")
+            out = step.workspace.get(step.tag + tag, (M, self.out_features), out_dtype or a.rows.dtype)
+            return ops.gemm_bf16_small_m(a.rows, self.weight, out, step.err, scaled=(a.partial, a.count, a.eps, a.size))
         out_dtype = out_dtype or a.dtype
         M = a.shape[0]
         ws = step.workspace

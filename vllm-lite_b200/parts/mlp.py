@@ -38,6 +38,13 @@ class SwiGLU:
         self.gate_up = Linear(stacked.contiguous())
         self.down = Linear(weights["down_proj.weight"])
 
-    def __call__(self, h, step):
+    def factors_norms(self, M) -> bool:
+        """For M rows: the input may come as `ScaledRows` and the result may go `into_stream`."""
+        from ..csrc import ops
+        return self.group == ops.SWIGLU_GROUP and self.gate_up.factors_norms(M) and self.down.factors_norms(M)
+
+    def __call__(self, h, step, sink=None):
         act = self.gate_up.swiglu(h, step, "mlp.gate_up", self.group)
+        if sink is not None:
+            return self.down.into_stream(act, sink, step, "mlp.down")
         return self.down(act, step, "mlp.down")

@@ -54,10 +54,18 @@ class CausalLM:
         x = ws.get(step.tag + "residual", (step.num_tokens, self.plan.hidden_size), torch.float32)
         ops.embed(step.tokens, self.embed_table, x, step.err)
         residual = Residual(x)
-        for call, cache in zip(self.plan.order, caches):
-            self.layers[call.layer](residual, step, cache)
+        order = self.plan.order
+        for i, (call, cache) in enumerate(zip(order, caches)):
+            layer = self.layers[call.layer]
+            if getattr(layer, "chains_norms", False):
+                # a block may leave the next block's first norm in factored form (parts/base.py, ScaledRows)
+                nxt = self.layers[order[i + 1].layer] if i + 1 < len(order) else None
+                ask = getattr(nxt, "input_norm_for_fusion", None)
+                layer(residual, step, cache, next_norm=ask(step.num_tokens) if ask else None)
+            else:
+                layer(residual, step, cache)
         R = step.logit_rows.shape[0]
         if R == 0:
             return ws.get(step.tag + "logits", (0, self.plan.vocab_size), torch.float32)
-        h = self.final_norm(residual.x, residual.pending, step, rows=step.logit_rows, tag="final_norm")
+        h = self.final_norm(residual.x, residual.pending, step, rows=step.logit_rows, tag="final_norm")   # pending: the last block has no next norm
         return self.head(h, step, "logits", out_dtype=torch.float32)

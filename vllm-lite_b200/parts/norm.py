@@ -11,6 +11,8 @@ from .spec import NormSpec, TensorDecl
 
 @NORMS.register("rms_norm")
 class RmsNorm:
+    factorable = True          # h = (x * weight) * scale(x): neighbours may fuse it (parts/base.py, ScaledRows)
+
     @staticmethod
     def declare(spec: NormSpec) -> dict:
         return {"weight": TensorDecl((spec.size,), init="norm")}
