@@ -154,3 +154,42 @@ def test_random_orders_keep_the_books(make, seed):
     for rid in list(live):
         m.free(rid)
     assert m.free_pages() == [40, 14] and m.slots.free_count == 5
+
+
+def test_native_decode_step_equals_its_parts():
+    """The one-call decode step of the C++ core (check, appends, packed batch, windows) leaves the
+    same books and writes the same words as the calls it stands for; a step that does not fit, or
+    that would take a request beyond the limit, changes nothing."""
+    import numpy as np
+    lay = layout(PagedKV(1, 16), PagedKV(1, 16, window=6))
+    a = NativeCacheManager(lay, page_size=4, num_pages=[12, 9], max_requests=4)
+    b = NativeCacheManager(lay, page_size=4, num_pages=[12, 9], max_requests=4)
+    for m in (a, b):
+        for rid, n in (("x", 7), ("y", 3), ("z", 12)):
+            m.admit(rid)
+            m.append(rid, n)
+            m.release_behind_window(rid)
+    ids, toks = ["z", "x", "y"], [5, 6, 7]
+    for step in range(5):
+        out_a = np.full(4096, 77, dtype=np.int32)
+        used, off, sizes, starts = a.decode_step(ids, toks, 4, 8, 1000, out_a)
+        st = [b.append(r, 1) for r in ids]
+        out_b = np.full(4096, 77, dtype=np.int32)
+        used_b, off_b, sizes_b, _ = b.pack_step(ids, [1, 1, 1], st, toks, [0, 1, 2, 3], [0, 0, 0], 4, 0, 8, out_b)
+        for r in ids:
+            b.release_behind_window(r)
+        assert used == used_b and list(off) == list(off_b) and list(sizes) == list(sizes_b) and list(starts) == st
+        assert (out_a[:used] == out_b[:used]).all() and (out_a[used:] == 77).all()
+        for r in ids:
+            assert a.requests[r].block_tables == b.requests[r].block_tables and a.requests[r].num_tokens == b.requests[r].num_tokens
+        assert a.free_pages() == b.free_pages()
+        a.check_invariants()
+    before = (a.free_pages(), [a.requests[r].num_tokens for r in ids])
+    assert a.decode_step(ids, toks, 4, 8, a.requests["z"].num_tokens, np.zeros(4096, dtype=np.int32)) is None   # z at its limit
+    assert a.decode_step(ids, toks, 4, 8, 1000, np.zeros(8, dtype=np.int32))[0] < 0                             # buffer too small
+    small = NativeCacheManager(lay, page_size=4, num_pages=[2, 9], max_requests=2)
+    small.admit("p"); small.append("p", 4); small.admit("q"); small.append("q", 4)
+    with pytest.raises(OutOfPages):
+        small.decode_step(["p", "q"], [1, 2], 2, 8, 1000, np.zeros(4096, dtype=np.int32))
+    assert small.free_pages() == [0, 7] and small.requests["p"].num_tokens == 4
+    assert before == (a.free_pages(), [a.requests[r].num_tokens for r in ids])

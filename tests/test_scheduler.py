@@ -32,6 +32,8 @@ def run_step(cache, sched, token_of=lambda seq: 7):
         if e.seq.seq_id not in cache.requests:
             cache.admit(e.seq.seq_id)
         assert cache.requests[e.seq.seq_id].num_tokens == e.start
+        if e.start == e.seq.num_computed:              # the scheduler's own count of pages is the cache manager's
+            assert sched._pages_needed(e.seq, e.count) == cache.pages_needed(e.seq.seq_id, e.count)
         cache.append(e.seq.seq_id, e.count)            # must never raise: the scheduler counted the pages
     sampled = [token_of(e.seq) if e.samples else None for e in plan.entries]
     done = sched.update(plan, sampled)

@@ -38,6 +38,7 @@ def _core():
             "vc_is_held": (I, [V, I, I]), "vc_take_fresh_slots": (I, [V, P, I]), "vc_num_requests": (I, [V]),
             "vc_check": (I, [V]),
             "vc_pack_step": (L, [V, I, V, V, V, V, V, V, I, I, V, V, L, V, V]),
+            "vc_decode_step": (L, [V, I, V, V, I, I, L, V, L, V, V, V]),
         }
         for name, (res, args) in sig.items():
             fn = getattr(lib, name)
@@ -203,6 +204,35 @@ class NativeCacheManager:
         self._call("vc_check")
         if len(self.requests) != _core().vc_num_requests(self._h):
             raise PoolError("the host's and the core's lists of requests differ")
+
+    def decode_step(self, request_ids, tokens, pad_to: int, fixed_blocks: int, max_tokens: int, out: np.ndarray):
+        """One token for each of the requests, in one call of the core: the check that the pools can
+        take them (OutOfPages, nothing changed, if not), the appends, the packed batch (as `pack_step`
+        with pad_to) written into `out`, and the release of pages behind windows.  Returns (words
+        used, offsets, sizes, positions of the tokens); a negative first value is the size `out`
+        must have, and None is returned when a request would grow beyond max_tokens (nothing was
+        changed in either case)."""
+        B = len(request_ids)
+        G = self.num_groups
+        keys = np.fromiter((self._keys[r] for r in request_ids), dtype=np.int64, count=B)
+        tokens = np.ascontiguousarray(tokens, dtype=np.int32)
+        offsets = np.zeros(8 + 2 * G, dtype=np.int32)
+        sizes = np.zeros(8 + 2 * G, dtype=np.int32)
+        starts = np.zeros(B, dtype=np.int64)
+        ptr = lambda a: a.ctypes.data
+        used = _core().vc_decode_step(self._h, B, ptr(keys), ptr(tokens), int(pad_to), int(fixed_blocks),
+                                      int(max_tokens), ptr(out), out.shape[0], ptr(offsets), ptr(sizes), ptr(starts))
+        if used == -8:
+            return None
+        if used == -1:
+            raise OutOfPages(f"the step needs more pages than are free {self.free_pages()}")
+        if used < 0:
+            if used == -2:
+                raise KeyError(_ERR[-2])
+            raise PoolError(_ERR.get(int(used), f"native cache core error {used}"))
+        if used > out.shape[0]:
+            return -int(used), offsets, sizes, starts
+        return int(used), offsets, sizes, starts
 
     # ---- packing a step (used by the step function) ---------------------------
     def pack_step(self, request_ids, counts, starts, tokens, want_offsets, wants, pad_to, tile_rows, fixed_blocks,

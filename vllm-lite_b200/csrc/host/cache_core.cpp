@@ -25,6 +25,7 @@ enum : int {
     VC_DOUBLE_FREE = -4,     // a unit was freed twice or never handed out
     VC_ARGUMENT = -5,
     VC_GONE = -6,            // a position lies in a page that was given back
+    VC_TOO_LONG = -8,        // a request would grow beyond the caller's limit; nothing was changed
     VC_CORRUPT = -7          // the books do not balance (check)
 };
 
@@ -396,6 +397,54 @@ long long vc_pack_step(void* h, int B_real, const long long* keys, const int* co
         }
     }
     return cursor;
+}
+
+// A decode step in one call: every request brings one token and wants its logits.  Checks that
+// the pools can take all the tokens (else VC_NO_SPACE, nothing changed), appends them, packs the
+// batch as vc_pack_step does (padded to pad_to requests, block tables max_blocks_fixed wide) and
+// gives back the pages that windows have passed.  starts_out[b] receives the position of request
+// b's token.  A request that would grow beyond max_tokens: VC_TOO_LONG, nothing changed.
+long long vc_decode_step(void* h, int B, const long long* keys, const int* tokens, int pad_to, int max_blocks_fixed,
+                         long long max_tokens, int* out, long long capacity, int* offsets, int* sizes,
+                         long long* starts_out) {
+    Core* c = static_cast<Core*>(h);
+    const int G = (int)c->pools.size();
+    if (B <= 0 || pad_to < B || max_blocks_fixed <= 0) return VC_ARGUMENT;
+    std::vector<Request*> reqs(B);
+    std::vector<int> need(G, 0);
+    for (int b = 0; b < B; ++b) {
+        auto it = c->requests.find(keys[b]);
+        if (it == c->requests.end()) return VC_UNKNOWN;
+        reqs[b] = &it->second;
+        for (int a = 0; a < b; ++a)
+            if (reqs[a] == reqs[b]) return VC_ARGUMENT;
+        if (reqs[b]->num_tokens + 1 > max_tokens) return VC_TOO_LONG;
+        for (int g = 0; g < G; ++g) need[g] += c->pages_needed(*reqs[b], 1, g);
+    }
+    for (int g = 0; g < G; ++g)
+        if (need[g] > c->pools[g].free_count()) return VC_NO_SPACE;
+    long long required = 3LL * align4(pad_to) + align4(pad_to + 1) + 2LL * align4(pad_to) + 2LL * align4(1);
+    for (int g = 0; g < G; ++g) required += align4(pad_to) + align4(pad_to * max_blocks_fixed);
+    if (required > capacity) return required;        // nothing changed: call again with a larger buffer
+    std::vector<int> counts(B, 1), want_offsets(B + 1), wants(B, 0), max_blocks(G > 0 ? G : 1, max_blocks_fixed);
+    std::vector<long long> starts(B);
+    for (int b = 0; b < B; ++b) {
+        Request& r = *reqs[b];
+        for (int g = 0; g < G; ++g) c->pools[g].allocate(c->pages_needed(r, 1, g), r.tables[g]);
+        starts[b] = r.num_tokens;
+        r.num_tokens += 1;
+        want_offsets[b] = b;
+        if (starts_out) starts_out[b] = starts[b];
+    }
+    want_offsets[B] = B;
+    const long long used = vc_pack_step(h, B, keys, counts.data(), starts.data(), tokens, want_offsets.data(),
+                                        wants.data(), pad_to, 0, max_blocks.data(), out, capacity, offsets, sizes);
+    if (used < 0 || used > capacity) return used;
+    for (int b = 0; b < B; ++b) {
+        const int rc = vc_release_behind_window(h, keys[b], nullptr);
+        if (rc) return rc;
+    }
+    return used;
 }
 
 }  // extern "C"

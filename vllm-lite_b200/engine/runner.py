@@ -110,6 +110,9 @@ class ModelRunner:
         the entries and of their `want`.  The tensor is a view of a buffer that the
         next step writes again: copy what must outlive it.  Raises OutOfPages, with
         nothing changed, when the pool cannot hold the new tokens."""
+        fast = self._decode_step_native(entries)
+        if fast is not None:
+            return fast
         batch = self.prepare(entries)
         if batch.graph_bucket:
             logits = self._forward_graph(batch)[:sum(len(e.want) for e in entries)]
@@ -117,6 +120,56 @@ class ModelRunner:
             logits = self.model.forward(batch, self.storage.call_caches)
         self.finish(batch)
         return logits
+
+    def _decode_step_native(self, entries):
+        """The common step of serving: every request brings one token and wants its logits, and a graph
+        is there to run it.  One call of the C++ core checks, appends and packs; then upload and
+        replay.  None when the step is of another kind (the general path takes it)."""
+        if not (self.native_host and self.decode_graphs):
+            return None
+        cache = self.cache
+        ids = []
+        for e in entries:
+            if len(e.tokens) != 1 or len(e.want) != 1 or e.want[0] != 0 or e.request_id not in cache.requests:
+                return None
+            ids.append(e.request_id)
+        B = len(ids)
+        if B == 0 or len(set(ids)) != B:
+            return None
+        bucket = 1
+        while bucket < B:
+            bucket *= 2
+        fixed = -(-self.max_context // self.page_size)
+        G = len(cache.pools)
+        words = 64 + 8 * bucket + G * (bucket + bucket * fixed + 8)
+        while True:
+            i, pin = self._pinned_slot(words)
+            got = cache.decode_step(ids, [e.tokens[0] for e in entries], bucket, fixed, self.max_context, pin.numpy())
+            if got is None:                           # a request at the end of its context: no graph for that
+                self._flip ^= 1
+                return None
+            used, off, sizes, starts = got
+            if used >= 0:
+                break
+            self._flip ^= 1
+            words = -used
+        dev = self._to_device(i, used, bucket)
+        longest = int(starts.max()) + 1
+        bound = 1024
+        while bound < longest:
+            bound *= 2
+        bound = min(bound, self.max_context)
+        self.steps += 1
+        entry = self._graphs.get((bucket, bound))
+        if entry is not None:
+            entry[0].replay()
+            from ..csrc import ops
+            ops.launch_count += self._graph_launches[(bucket, bound)]
+            self.graph_replays += 1
+            return entry[1][:B]
+        host_entries = [Entry(r, int(s), 1, cache.requests[r].state_slot) for r, s in zip(ids, starts)]
+        batch = self._batch_from_packed(dev, off, sizes, [fixed] * G, host_entries, bucket)
+        return self._forward_graph(batch)[:B]         # records the graph
 
     def _forward_graph(self, batch: StepBatch) -> torch.Tensor:
         """Rows of padded requests come after the real ones, so the caller slices them off."""
@@ -235,8 +288,13 @@ class ModelRunner:
             self._flip ^= 1                          # the slot was not used; take it again, larger
             guess = -used
         dev = self._to_device(i, used, bucket)
+        return self._batch_from_packed(dev, off, sizes, max_blocks, host_entries, bucket)
+
+    def _batch_from_packed(self, dev, off, sizes, max_blocks, host_entries, bucket: int) -> StepBatch:
+        """Views of the uploaded buffer that the C++ core packed (sections: csrc/host/cache_core.cpp)."""
         sec = lambda k: dev[int(off[k]):int(off[k]) + int(sizes[k])]
-        Bp = bucket or B
+        counts = [h.count for h in host_entries]
+        Bp = bucket or len(host_entries)
         longest = max(h.start + h.count for h in host_entries)
         if bucket:                       # a graph is recorded for a bound on the context, not for its value
             bound = 1024

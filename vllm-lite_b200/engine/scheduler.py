@@ -180,10 +180,12 @@ class Scheduler:
         return entries, None
 
     def _pages_needed(self, seq: Sequence, n: int):
-        if seq.seq_id in self.cache.requests:
-            return self.cache.pages_needed(seq.seq_id, n)
+        """Pages that n more tokens take in every group: the blocks their positions open.  (A running
+        sequence holds num_computed tokens in the cache; a window gives pages back but keeps the
+        block table's length, so the count is the same for every group.)"""
         ps = self.cache.page_size
-        return [-(-n // ps)] * len(self.cache.pools)
+        held = seq.num_computed if seq.seq_id in self.cache.requests else 0
+        return [-(-(held + n) // ps) - -(-held // ps)] * len(self.cache.pools)
 
     def _preempt(self, seq: Sequence):
         self.running.remove(seq)
