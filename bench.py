@@ -38,8 +38,9 @@ def peaks():
     p = ROOT / "MEASURED_PEAKS.json"
     if p.is_file():
         d = json.loads(p.read_text())
-        return dict(hbm_gbs=d["hbm_gbs"], bf16_tflops=d["bf16_tflops"], source="measured")
-    return dict(hbm_gbs=6650.0, bf16_tflops=1590.0, source="fallback")
+        return dict(hbm_gbs=d["hbm_gbs"], bf16_tflops=d["bf16_tflops"],
+                    bf16_tflops_sustained=d.get("bf16_tflops_sustained", d["bf16_tflops"]), source="measured")
+    return dict(hbm_gbs=6650.0, bf16_tflops=1590.0, bf16_tflops_sustained=1400.0, source="fallback")
 
 
 class ClockSampler:
@@ -268,8 +269,11 @@ def main(argv=None):
     }
     if not args.no_points:
         pms = prefill_run(runner, vocab)
+        # frac: of the burst peak of the library product (one launch timed alone); the step itself is a
+        # long run of products under the power cap, for which the sustained figure is the fair one
         out["prefill"] = {"value": round(PREFILL_TOKENS / pms * 1000.0, 1), "tokens": PREFILL_TOKENS, "ms": round(pms, 3),
-                          "frac": round(prefill_flops / (pms * 1e-3) / (pk["bf16_tflops"] * 1e12), 4)}
+                          "frac": round(prefill_flops / (pms * 1e-3) / (pk["bf16_tflops"] * 1e12), 4),
+                          "frac_of_sustained": round(prefill_flops / (pms * 1e-3) / (pk["bf16_tflops_sustained"] * 1e12), 4)}
         ms1, _, _ = decode_run(runner, sampler, 1, args.context, warmup, args.steps, "prefill", vocab, "s")
         ms64, _, _ = decode_run(runner, sampler, 64, args.context, warmup, args.steps, args.kv_fill, vocab, "l")
         out["points"] = {"decode_b1": round(1000.0 / ms1, 1), "decode_b64": round(64 * 1000.0 / ms64, 1)}
