@@ -101,6 +101,50 @@ def test_stop_sequence_and_step_outputs():
         eng.add_request([999999], 4)
 
 
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_steps_launched_ahead_change_nothing_but_the_timing(dtype):
+    """With lookahead the engine launches the next decode step before it has read this step's
+    tokens.  Tokens, finish reasons and the books are those of the engine that waits: greedy and
+    seeded temperature requests, one that ends on a stop sequence, one that arrives later, one
+    that is cancelled while a step launched ahead holds it."""
+    from vllm_lite_b200 import SamplingParams
+    which = "B"
+    prompts = [H.tokens_for(which, n, 200 + i) for i, n in enumerate([12, 30, 7, 21])]
+    stop = plain_greedy(which, prompts[2], 6)[3:5]
+
+    def run(lookahead):
+        eng = engine(which, dtype=dtype, lookahead=lookahead, max_num_batched_tokens=64, prefill_chunk_size=16)
+        ids = [eng.add_request(prompts[0], 14),
+               eng.add_request(prompts[1], 9, SamplingParams(temperature=0.7, seed=5)),
+               eng.add_request(prompts[2], 12, SamplingParams(stop_token_sequences=[stop]))]
+        got, ahead, steps = {}, 0, 0
+        while eng.has_unfinished():
+            for o in eng.step():
+                got.setdefault(o.seq_id, []).append((o.token, o.finished, o.finish_reason))
+            ahead += eng._ahead is not None
+            steps += 1
+            if steps == 5:
+                ids.append(eng.add_request(prompts[3], 30))
+            if len(ids) == 4 and len(got.get(ids[3], [])) == 6 and eng.sequences[ids[3]].status == "running":
+                eng.cancel_request(ids[3])
+        eng.runner.check_device_errors()
+        eng.runner.cache.check_invariants()
+        assert eng.stats()["free_pages"] == [64] and eng.stats()["running"] == 0
+        return [got[i] for i in ids], ahead
+
+    waited, n0 = run(False)
+    ahead, n1 = run(True)
+    assert n0 == 0 and n1 > 5                      # steps were in fact launched ahead
+    assert waited[0][-1][1:] == (True, "length") and waited[2][-1][1:] == (True, "stop")
+    assert ahead[0][-1][1:] == (True, "length") and ahead[2][-1][1:] == (True, "stop")
+    assert [len(r) for r in ahead[:2]] == [len(r) for r in waited[:2]] == [14, 9] and len(ahead[3]) == len(waited[3]) == 6
+    if dtype == "float32":
+        # float32 results do not depend on what shares a step, so the tokens are the same to the last one
+        # (in bfloat16 a request that joins or leaves a step one step later moves roundings, and a
+        # near tie may fall the other way)
+        assert ahead[:3] == waited[:3] and ahead[3][:6] == waited[3][:6]
+
+
 def test_command_line(tmp_path):
     which = "A"
     prompt = H.tokens_for(which, 12, 95)

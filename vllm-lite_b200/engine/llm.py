@@ -22,6 +22,13 @@ from .runner import ModelRunner, StepEntry
 from .scheduler import Scheduler, SchedulerConfig, Sequence
 
 
+class _InFlight:
+    """A launched step whose tokens the host has not read yet."""
+    def __init__(self, plan, sampling):
+        self.plan, self.sampling = plan, sampling
+        self.event = self.tokens_device = self.host_tokens = self.host_logprobs = None
+
+
 @dataclass
 class StepOutput:
     seq_id: int
@@ -34,12 +41,13 @@ class StepOutput:
 class LLMEngine:
     def __init__(self, model=None, *, dtype="bfloat16", device="cuda:0", kv_blocks: int = 1024, block_size: int = 16,
                  max_batch_size: int = 256, max_num_batched_tokens: int = 4096, prefill_chunk_size: int = 512,
-                 max_model_len: Optional[int] = None, plan=None, weights=None, logprobs: bool = False):
+                 max_model_len: Optional[int] = None, plan=None, weights=None, logprobs: bool = False,
+                 lookahead: bool = True):
         """`model`: a folder with config.json and safetensors (never downloaded).  `kv_blocks`
         and `max_batch_size` carry the reference's names and defaults
         (crates/server/src/cli/args.rs:155-186); `block_size` is its BLOCK_SIZE constant
         (crates/traits/src/types.rs:13) made an option.  Alternatively pass `plan` and
-        `weights` of a model that is already on the device."""
+        `weights` of a model that is already on the device.  `lookahead`: see `step`."""
         self.dtype = parse_dtype(dtype)
         if plan is None:
             if model is None:
@@ -55,6 +63,11 @@ class LLMEngine:
         self.sampler = Sampler(device)
         self.want_logprobs = logprobs
         self.sequences: Dict[int, Sequence] = {}
+        self.lookahead = bool(lookahead)
+        self._ahead = None                      # a step that is launched but not yet reported
+        self._slot = 0
+        self._host_tok = [None, None]           # pinned read-back buffers of the two steps that can be in flight
+        self._host_lp = [None, None]
 
     # ---- requests -----------------------------------------------------------
     def add_request(self, prompt: Seq[int], max_tokens: int, sampling_params: SamplingParams = None) -> int:
@@ -70,33 +83,100 @@ class LLMEngine:
         return self.scheduler.cancel(seq_id)
 
     def has_unfinished(self) -> bool:
-        return self.scheduler.has_work()
+        return self.scheduler.has_work() or (self._ahead is not None and self._ahead_is_live())
+
+    def _ahead_is_live(self) -> bool:
+        return any(e.seq.status != "finished" for e in self._ahead.plan.entries)
 
     # ---- one step -------------------------------------------------------------
     def step(self) -> List[StepOutput]:
-        plan = self.scheduler.schedule()
-        if not plan.entries:
-            return []
+        """Outputs of one step: the new token of every request whose portion reached its end.
+
+        With `lookahead` (the default) the step after the one being reported is launched before the
+        host has read this one's tokens, whenever that step can be foretold: every request of this
+        step yields a token and goes on (none reaches max_tokens), nobody waits for admission, no
+        option needs the token on the host (penalties, biases).  Its input tokens then stay on the
+        device.  A request that turns out to have ended (stop sequence, cancel) has cost one token
+        of work that is thrown away."""
+        if self._ahead is None:
+            plan = self.scheduler.schedule()
+            if not plan.entries:
+                return []
+            self._ahead = self._launch(plan)
+        current, self._ahead = self._ahead, None
+        if self.lookahead:
+            self._ahead = self._launch_following(current)
+        return self._collect(current)
+
+    def _launch(self, plan) -> "_InFlight":
         entries = [StepEntry(e.seq.seq_id, e.seq.tokens[e.start:e.start + e.count],
                              [e.count - 1] if e.samples else []) for e in plan.entries]
         logits = self.runner.step(entries)
         sampling = [e for e in plan.entries if e.samples]
+        return self._sample(plan, sampling, logits, [len(e.seq.generated) for e in sampling])
+
+    def _sample(self, plan, sampling, logits, steps) -> "_InFlight":
+        """Queues sampling and the copy of the tokens to pinned host memory; nothing waits here."""
+        flight = _InFlight(plan, sampling)
+        if sampling:
+            tok, lp = self.sampler.sample(logits, [e.seq.params for e in sampling], [e.seq.generated for e in sampling],
+                                          self.want_logprobs, steps=steps)
+            k = self._slot
+            self._slot ^= 1
+            n = len(sampling)
+            if self._host_tok[k] is None or self._host_tok[k].numel() < n:
+                self._host_tok[k] = torch.empty(max(n, 64), dtype=torch.int32).pin_memory()
+                self._host_lp[k] = torch.empty(max(n, 64), dtype=torch.float32).pin_memory()
+            self._host_tok[k][:n].copy_(tok, non_blocking=True)              # the step's only read-back
+            if lp is not None:
+                self._host_lp[k][:n].copy_(lp, non_blocking=True)
+            flight.event = torch.cuda.Event()
+            flight.event.record()
+            flight.tokens_device, flight.host_tokens = tok, self._host_tok[k][:n]
+            flight.host_logprobs = self._host_lp[k][:n] if lp is not None else None
+        return flight
+
+    def _launch_following(self, current: "_InFlight"):
+        """The decode step that follows `current`, launched with its tokens still on the device, or
+        None when it cannot be foretold."""
+        entries = current.plan.entries
+        if not entries or len(current.sampling) != len(entries) or self.scheduler.waiting:
+            return None
+        steps = []
+        for e in entries:
+            seq = e.seq
+            produced = len(seq.tokens) - seq.prompt_len + 1            # once the token in flight has arrived
+            if seq.status != "running" or seq.params.needs_penalties or produced >= seq.max_tokens:
+                return None
+            steps.append(produced)
+        longest = max(e.start + e.count for e in entries) + 1
+        logits = self.runner.step_ahead([e.seq.seq_id for e in entries], current.tokens_device, longest)
+        if logits is None:
+            return None
+        from .scheduler import Scheduled, StepPlan
+        plan = StepPlan()
+        plan.entries = [Scheduled(e.seq, e.start + e.count, 1, True) for e in entries]
+        return self._sample(plan, plan.entries, logits, steps)
+
+    def _collect(self, flight: "_InFlight") -> List[StepOutput]:
+        plan = flight.plan
         sampled: List[Optional[int]] = [None] * len(plan.entries)
         logprobs = None
-        if sampling:
-            tok, lp = self.sampler.sample(logits, [e.seq.params for e in sampling],
-                                          [e.seq.generated for e in sampling], self.want_logprobs)
-            host = tok.cpu().tolist()                         # the step's only read-back
-            logprobs = lp.cpu().tolist() if lp is not None else None
+        if flight.sampling:
+            flight.event.synchronize()
+            host = flight.host_tokens.tolist()
+            logprobs = flight.host_logprobs.tolist() if flight.host_logprobs is not None else None
             it = iter(host)
             sampled = [next(it) if e.samples else None for e in plan.entries]
-        finished = self.scheduler.update(plan, sampled)
+        live = [e.seq.status != "finished" for e in plan.entries]     # a step launched ahead may hold ended requests
+        self.scheduler.update(plan, sampled)
         out, k = [], 0
-        for e, t in zip(plan.entries, sampled):
+        for e, t, alive in zip(plan.entries, sampled, live):
             if t is None:
                 continue
-            out.append(StepOutput(e.seq.seq_id, t, e.seq.status == "finished", e.seq.finish_reason,
-                                  logprobs[k] if logprobs else None))
+            if alive:
+                out.append(StepOutput(e.seq.seq_id, t, e.seq.status == "finished", e.seq.finish_reason,
+                                      logprobs[k] if logprobs else None))
             k += 1
         return out
 
@@ -108,6 +188,7 @@ class LLMEngine:
         ids = [self.add_request(p, max_tokens, sp) for p, sp in zip(prompts, sampling_params)]
         while self.has_unfinished():
             self.step()
+        self._ahead = None                      # at most a step launched ahead for requests that have ended since
         self.runner.check_device_errors()
         out = [list(self.sequences[i].generated) for i in ids]
         for i in ids:

@@ -171,6 +171,47 @@ class ModelRunner:
         batch = self._batch_from_packed(dev, off, sizes, [fixed] * G, host_entries, bucket)
         return self._forward_graph(batch)[:B]         # records the graph
 
+    def step_ahead(self, request_ids, token_source: torch.Tensor, longest: int):
+        """A decode step launched before the host knows its tokens: request i's token is
+        token_source[i] (int32 on the device, written by work already queued on the stream), every
+        request wants its logits, and `longest` bounds position + 1 of the new tokens.  Returns the
+        logits, or None with nothing changed when this cannot be done (no graph recorded for the
+        shape yet, pages or context exhausted): the caller then steps the ordinary way."""
+        if not (self.native_host and self.decode_graphs):
+            return None
+        B = len(request_ids)
+        bucket = 1
+        while bucket < B:
+            bucket *= 2
+        bound = 1024
+        while bound < longest:
+            bound *= 2
+        bound = min(bound, self.max_context)
+        entry = self._graphs.get((bucket, bound))
+        if entry is None or longest > self.max_context or any(r not in self.cache.requests for r in request_ids):
+            return None
+        fixed = -(-self.max_context // self.page_size)
+        G = len(self.cache.pools)
+        i, pin = self._pinned_slot(64 + 8 * bucket + G * (bucket + bucket * fixed + 8))
+        try:
+            got = self.cache.decode_step(request_ids, [0] * B, bucket, fixed, self.max_context, pin.numpy())
+        except OutOfPages:
+            got = None
+        if got is None or got[0] < 0:
+            self._flip ^= 1
+            return None
+        used, off, sizes, starts = got
+        if int(starts.max()) + 1 > longest:
+            raise StepError("step_ahead: the caller's bound on the context is too small")
+        dev = self._to_device(i, used, bucket)
+        dev[int(off[0]):int(off[0]) + B].copy_(token_source[:B])
+        self.steps += 1
+        entry[0].replay()
+        from ..csrc import ops
+        ops.launch_count += self._graph_launches[(bucket, bound)]
+        self.graph_replays += 1
+        return entry[1][:B]
+
     def _forward_graph(self, batch: StepBatch) -> torch.Tensor:
         """Rows of padded requests come after the real ones, so the caller slices them off."""
         key = (batch.graph_bucket, batch.groups[0].max_context if batch.groups else 0)

@@ -205,6 +205,8 @@ class Scheduler:
         self.stats["steps"] += 1
         for entry, token in zip(plan.entries, sampled):
             seq = entry.seq
+            if seq.status == "finished":                   # ended (stop, cancel) while a step launched ahead held it
+                continue
             seq.num_computed += entry.count
             self.stats["decode_tokens" if entry.count == 1 and entry.start >= seq.prompt_len else "prefill_tokens"] += entry.count
             if not entry.samples:

@@ -35,10 +35,11 @@ class Sampler:
         return seeded_uniform(params.seed, step)
 
     def sample(self, logits: torch.Tensor, params: Sequence[SamplingParams], generated: Sequence[Sequence[int]],
-               want_logprobs: bool = False):
+               want_logprobs: bool = False, steps: Optional[Sequence[int]] = None):
         """logits float32 [R, V] (modified in place when penalties apply); `generated[r]`
         are the tokens row r's request has produced so far (their count is the step of
-        its random stream).  Returns (tokens int32 [R] on the device, logprobs or None)."""
+        its random stream, unless `steps` gives the counts).  Returns (tokens int32 [R] on the
+        device, logprobs or None); both are views of buffers that the next call writes again."""
         from ..csrc import ops
         R = logits.shape[0]
         out_tok, out_lp = self._buffers(R)
@@ -51,7 +52,7 @@ class Sampler:
         k = np.zeros(R, dtype=np.int32)
         for r, p in enumerate(params):
             f[0, r], f[1, r] = p.temperature, p.top_p
-            f[2, r] = self.uniform_for(p, len(generated[r])) if p.temperature > 0 else 0.0
+            f[2, r] = self.uniform_for(p, steps[r] if steps is not None else len(generated[r])) if p.temperature > 0 else 0.0
             k[r] = p.top_k
         fd = torch.from_numpy(f).to(self.device, non_blocking=True)
         kd = torch.from_numpy(k).to(self.device, non_blocking=True)
