@@ -126,17 +126,19 @@ def test_gemm_bf16_small_m(M, N, K, out_dtype):
     assert torch.equal(again[m2 - 1], out[M - 1])
 
 
+@pytest.mark.parametrize("kernel", ["gemm_bf16_tc5", "gemm_bf16_tc5_pair"])
 @pytest.mark.parametrize("out_dtype", [torch.bfloat16, torch.float32])
 @pytest.mark.parametrize("M,N,K", [(128, 256, 64), (128, 256, 512), (2048, 6144, 4096), (300, 1000, 264), (1, 333, 96),
                                    (130, 128, 72), (17, 40, 8), (257, 4096, 12288)])
-def test_gemm_bf16_tcgen05(M, N, K, out_dtype):
-    """Tiles of 128 x 256 (or 128 x 128) through TMA and TMEM; ragged M, N and K are zero-filled."""
+def test_gemm_bf16_tcgen05(kernel, M, N, K, out_dtype):
+    """Tiles of 128 x 256 (or 128 x 128) on one SM, or of 256 x 256 on a pair of SMs, through TMA and
+    TMEM; ragged M, N and K are zero-filled."""
     torch.manual_seed(M + N + K)
     a = torch.randn(M, K, device=DEV).to(torch.bfloat16)
     w = (torch.randn(N, K, device=DEV) * 0.05).to(torch.bfloat16)
     out = torch.full((M, N), float("nan"), device=DEV, dtype=out_dtype)
     e = err_word()
-    ops().gemm_bf16_tc5(a, w, out, e)
+    getattr(ops(), kernel)(a, w, out, e)
     assert int(e.item()) == 0
     ref = a.double() @ w.double().T
     scale = float(ref.abs().max())

@@ -146,61 +146,7 @@ gemm_tc5_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
             for (int c0 = 0; c0 < BN; c0 += 32) {
                 unsigned v[32];
                 tc5_ld32(tmem_base + ((unsigned)(quarter * 32) << 16) + (unsigned)(acc * BN + c0), v);
-                if (row < M && swiglu) {
-                    // 32 columns = two blocks of 8 gate and 8 up columns -> 16 columns of C at (n0 + c0) / 2
-                    TO* dst = C + (size_t)row * ldc + (n0 + c0) / 2;
-#pragma unroll
-                    for (int blk = 0; blk < 2; ++blk) {
-                        if (n0 + c0 + 16 * blk + 16 <= N) {
-                            float o[8];
-#pragma unroll
-                            for (int i = 0; i < 8; ++i) {
-                                const float gt = __uint_as_float(v[16 * blk + i]), up = __uint_as_float(v[16 * blk + 8 + i]);
-                                o[i] = gt / (1.0f + __expf(-gt)) * up;
-                            }
-                            if constexpr (sizeof(TO) == 2) {
-                                uint4 q;
-                                unsigned* w = reinterpret_cast<unsigned*>(&q);
-#pragma unroll
-                                for (int i = 0; i < 4; ++i) {
-                                    __nv_bfloat162 p = __floats2bfloat162_rn(o[2 * i], o[2 * i + 1]);
-                                    w[i] = *reinterpret_cast<unsigned*>(&p);
-                                }
-                                if ((((uintptr_t)(dst + 8 * blk)) & 15) == 0) {
-                                    *reinterpret_cast<uint4*>(dst + 8 * blk) = q;
-                                } else {
-#pragma unroll
-                                    for (int i = 0; i < 8; ++i) dst[8 * blk + i] = from_f32<TO>(o[i]);
-                                }
-                            } else {
-#pragma unroll
-                                for (int i = 0; i < 8; ++i) dst[8 * blk + i] = from_f32<TO>(o[i]);
-                            }
-                        }
-                    }
-                } else if (row < M) {
-                    TO* dst = C + (size_t)row * ldc + n0 + c0;
-                    if (n0 + c0 + 32 <= N && (((uintptr_t)dst) & 15) == 0) {
-                        if constexpr (sizeof(TO) == 2) {
-                            uint4 q[4];
-                            unsigned* w = reinterpret_cast<unsigned*>(q);
-#pragma unroll
-                            for (int i = 0; i < 16; ++i) {
-                                __nv_bfloat162 p = __floats2bfloat162_rn(__uint_as_float(v[2 * i]), __uint_as_float(v[2 * i + 1]));
-                                w[i] = *reinterpret_cast<unsigned*>(&p);
-                            }
-#pragma unroll
-                            for (int i = 0; i < 4; ++i) reinterpret_cast<uint4*>(dst)[i] = q[i];
-                        } else {
-#pragma unroll
-                            for (int i = 0; i < 8; ++i)
-                                reinterpret_cast<uint4*>(dst)[i] = make_uint4(v[4 * i], v[4 * i + 1], v[4 * i + 2], v[4 * i + 3]);
-                        }
-                    } else {
-                        for (int i = 0; i < 32; ++i)
-                            if (n0 + c0 + i < N) dst[i] = from_f32<TO>(__uint_as_float(v[i]));
-                    }
-                }
+                if (row < M) store_chunk32<TO>(v, C + (size_t)row * ldc, n0 + c0, N, swiglu);
             }
             tc5_fence_before();
             mbar_arrive(&acc_empty_bar[acc]);                // 128 arrivals hand the accumulator back

@@ -66,6 +66,8 @@ _SIGNATURES = {
                                                   c_void_p, c_void_p, c_void_p, c_void_p],
     ("gemm_tc5", "vl_gemm_bf16_tc5"): [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
                                        c_void_p, c_int, c_void_p],
+    ("gemm_tc5_pair", "vl_gemm_bf16_tc5_pair"): [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
+                                                 c_void_p, c_int, c_void_p],
     ("sampling", "vl_apply_penalties"): [c_void_p, c_longlong, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p,
                                          c_void_p, c_void_p, c_void_p, c_void_p],
     ("sampling", "vl_sample"): [c_void_p, c_longlong, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p,
@@ -459,6 +461,27 @@ def gemm_bf16_tc5(a, w, out, err=None, swiglu=False):
     M, N, K, width = _gemm_shapes(a, w, out, swiglu)
     _check(_fn("gemm_tc5", "vl_gemm_bf16_tc5")(_ptr(a), _ptr(w), _ptr(out), dtype_code(out.dtype), M, N, K,
                                                K, K, width, _ptr(err), int(swiglu), _stream()), "vl_gemm_bf16_tc5")
+    return out
+
+
+_sm_pairs = None
+
+
+def sm_pairs() -> int:
+    """Pairs of SMs of the current device (what a kernel of two-block clusters can keep busy)."""
+    global _sm_pairs
+    if _sm_pairs is None:
+        _sm_pairs = torch.cuda.get_device_properties(torch.cuda.current_device()).multi_processor_count // 2
+    return _sm_pairs
+
+
+def gemm_bf16_tc5_pair(a, w, out, err=None, swiglu=False):
+    """As `gemm_bf16_tc5`, with two SMs on one 256 x 256 tile (tcgen05.mma.cta_group::2): each SM
+    brings its rows of a and half of the tile's rows of w into shared memory."""
+    M, N, K, width = _gemm_shapes(a, w, out, swiglu)
+    _check(_fn("gemm_tc5_pair", "vl_gemm_bf16_tc5_pair")(_ptr(a), _ptr(w), _ptr(out), dtype_code(out.dtype), M, N, K,
+                                                         K, K, width, _ptr(err), int(swiglu), _stream()),
+           "vl_gemm_bf16_tc5_pair")
     return out
 
 

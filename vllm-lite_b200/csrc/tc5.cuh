@@ -133,6 +133,66 @@ constexpr unsigned IDESC_B_MN_MAJOR = 1u << 16;      // B is stored with N conti
 __host__ __device__ constexpr unsigned make_idesc(int m, int n) {
     return (1u << 4) | (1u << 7) | (1u << 10) | ((unsigned)(n >> 3) << 17) | ((unsigned)(m >> 4) << 24);
 }
+// Stores 32 neighbouring columns (from column `col` of the product) of one row of the accumulator.
+// swiglu: the 32 columns are two blocks of 8 gate and 8 up columns and become 16 columns of C at col / 2:
+// C[8b + i] = silu(y[16b + i]) * y[16b + 8 + i].  `crow` points at the row of C.
+template <typename TO>
+__device__ __forceinline__ void store_chunk32(const unsigned (&v)[32], TO* crow, int col, int N, int swiglu) {
+    if (swiglu) {
+        TO* dst = crow + col / 2;
+#pragma unroll
+        for (int blk = 0; blk < 2; ++blk) {
+            if (col + 16 * blk + 16 <= N) {
+                float o[8];
+#pragma unroll
+                for (int i = 0; i < 8; ++i) {
+                    const float gt = __uint_as_float(v[16 * blk + i]), up = __uint_as_float(v[16 * blk + 8 + i]);
+                    o[i] = gt / (1.0f + __expf(-gt)) * up;
+                }
+                if constexpr (sizeof(TO) == 2) {
+                    uint4 q;
+                    unsigned* w = reinterpret_cast<unsigned*>(&q);
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) {
+                        __nv_bfloat162 p = __floats2bfloat162_rn(o[2 * i], o[2 * i + 1]);
+                        w[i] = *reinterpret_cast<unsigned*>(&p);
+                    }
+                    if ((((uintptr_t)(dst + 8 * blk)) & 15) == 0) {
+                        *reinterpret_cast<uint4*>(dst + 8 * blk) = q;
+                    } else {
+#pragma unroll
+                        for (int i = 0; i < 8; ++i) dst[8 * blk + i] = from_f32<TO>(o[i]);
+                    }
+                } else {
+#pragma unroll
+                    for (int i = 0; i < 8; ++i) dst[8 * blk + i] = from_f32<TO>(o[i]);
+                }
+            }
+        }
+        return;
+    }
+    TO* dst = crow + col;
+    if (col + 32 <= N && (((uintptr_t)dst) & 15) == 0) {
+        if constexpr (sizeof(TO) == 2) {
+            uint4 q[4];
+            unsigned* w = reinterpret_cast<unsigned*>(q);
+#pragma unroll
+            for (int i = 0; i < 16; ++i) {
+                __nv_bfloat162 p = __floats2bfloat162_rn(__uint_as_float(v[2 * i]), __uint_as_float(v[2 * i + 1]));
+                w[i] = *reinterpret_cast<unsigned*>(&p);
+            }
+#pragma unroll
+            for (int i = 0; i < 4; ++i) reinterpret_cast<uint4*>(dst)[i] = q[i];
+        } else {
+#pragma unroll
+            for (int i = 0; i < 8; ++i)
+                reinterpret_cast<uint4*>(dst)[i] = make_uint4(v[4 * i], v[4 * i + 1], v[4 * i + 2], v[4 * i + 3]);
+        }
+    } else {
+        for (int i = 0; i < 32; ++i)
+            if (col + i < N) dst[i] = from_f32<TO>(__uint_as_float(v[i]));
+    }
+}
 }  // namespace tc5
 
 // ---- host side -------------------------------------------------------------------------------

@@ -1,7 +1,7 @@
 """bfloat16 matrix product out[M, N] = a[M, K] @ w[N, K]^T with float32 accumulation.
 
 Few rows (a decode step) go to the engine's weight-streaming kernel, many rows (a prompt
-portion of a thousand tokens or more) to its tcgen05 kernel.  What lies between goes to
+portion of a thousand tokens or more) to its tcgen05 kernels (one SM or a pair of SMs per tile).  What lies between goes to
 the library product (cuBLAS through torch), as the reference hands its matrix products to
 its tensor library's GEMM.
 """
@@ -24,6 +24,11 @@ def gemm_bf16(a, w, out, err=None, swiglu=False):
     if ops.gemm_bf16_small_m_ok(M, K):
         return ops.gemm_bf16_small_m(a, w, out, err, swiglu)
     if ops.gemm_bf16_tc5_ok(M, K):
+        # Two SMs on a 256 x 256 tile halve the rows of w each SM copies; measured faster (3 to 7 %) when
+        # there are tiles for every pair of SMs or K is long, slower (2 to 6 %) for the short, narrow products.
+        N = w.shape[0]
+        if -(-M // 256) * -(-N // 256) >= ops.sm_pairs() or K >= 8192:
+            return ops.gemm_bf16_tc5_pair(a, w, out, err, swiglu)
         return ops.gemm_bf16_tc5(a, w, out, err, swiglu)
     if swiglu:
         raise ValueError("the library product has no fused activation; ask fuses_swiglu() first")
