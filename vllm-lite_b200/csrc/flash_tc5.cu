@@ -20,10 +20,11 @@
 //        that the block table does not hold, is fetched from beyond the end of the tensor, which
 //        the TMA unit fills with zeros; the rows of V behind the tile's last key (another request's
 //        leftovers, possibly NaN) are zeroed in shared memory once the last key tile has landed;
-//   warp 5, one thread   issues the products: S_j = Q K_j^T (M 128, N 64, K = head size; both
-//        operands K-major) into one of two score buffers, so that the scores of the next tile are
-//        computed while the rows of this one are exponentiated, and O += P_j V_j (M 128, N = head
-//        size, K 64; V is read as stored, i.e. with its N index contiguous).
+//   warp 5, one thread   issues S_j = Q K_j^T (M 128, N 64, K = head size; both operands K-major)
+//        into one of two score buffers, as soon as the rows of the tile two before have been read,
+//        so that scores are computed while the rows of the tile before are exponentiated;
+//   warp 6, one thread   issues O += P_j V_j (M 128, N = head size, K 64; V is read as stored, i.e.
+//        with its N index contiguous) once P_j lies in shared memory.
 // Two blocks fit on an SM (112 KB of shared memory and 256 TMEM columns each at head size 128):
 // one block's softmax runs beside the other's products.
 // A row keeps a stale maximum until the true one exceeds it by more than 8 (in log2 units): the
@@ -43,13 +44,13 @@ namespace {
 constexpr int HD = FA_HD;
 static_assert(HD == 64 || HD == 128, "this kernel is built for head sizes 64 and 128");
 constexpr int BM = 128, BN = 64, CB = HD / 64;       // CB: blocks of 64 columns (one swizzled row) per head
-constexpr int NTHREADS = 192;
+constexpr int NTHREADS = 224;
 constexpr unsigned ROW_BYTES = 128;
 constexpr unsigned Q_BYTES = BM * HD * 2;            // CB blocks of [128 rows][128 bytes]
 constexpr unsigned KV_STAGE = BN * HD * 2;           // CB blocks of [64 rows][128 bytes]
 constexpr unsigned P_BYTES = BM * BN * 2;            // [128 rows][128 bytes]
 constexpr unsigned TILE_BYTES = Q_BYTES + 4 * KV_STAGE + P_BYTES;
-constexpr unsigned SMEM_BYTES = TILE_BYTES + 128;    // + barriers; two blocks per SM only without any slack
+constexpr unsigned SMEM_BYTES = TILE_BYTES + 160;    // + barriers; two blocks per SM only without any slack
 constexpr unsigned TMEM_COLS = 256;                  // scores 2 x 64, output HD (a power of two >= their sum)
 constexpr unsigned O_COL = 2 * BN;
 constexpr float RESCALE_ABOVE = 8.0f;
@@ -119,8 +120,9 @@ flash_tc5_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constan
     unsigned long long* bars = reinterpret_cast<unsigned long long*>(smem + TILE_BYTES);
     unsigned long long *k_full = bars, *k_empty = bars + 2, *v_full = bars + 4, *v_empty = bars + 6, *s_full = bars + 8;
     unsigned long long &p_full = bars[10], &pv_done = bars[11], &v_fixed = bars[12];
-    unsigned& tmem_base_slot = *reinterpret_cast<unsigned*>(bars + 13);
-    int& failed = *reinterpret_cast<int*>(bars + 14);
+    unsigned long long* s_free = bars + 13;
+    unsigned& tmem_base_slot = *reinterpret_cast<unsigned*>(bars + 15);
+    int& failed = *reinterpret_cast<int*>(bars + 16);
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     if (smem_u32(smem) & 1023u) {                    // (uniform) never expected; the tiles would be misread
         if (tid == 0 && err) atomicOr(err, VL_DEV_WAIT_EXPIRED);
@@ -132,6 +134,7 @@ flash_tc5_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constan
             mbar_init(&k_full[i], 1); mbar_init(&k_empty[i], 1);
             mbar_init(&v_full[i], 1); mbar_init(&v_empty[i], 1);
             mbar_init(&s_full[i], 1);
+            mbar_init(&s_free[i], BM);
         }
         mbar_init(&p_full, BM);
         mbar_init(&pv_done, 1);
@@ -226,18 +229,17 @@ flash_tc5_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constan
             else atomicExch(&failed, 1);
         }
     } else if (warp == 5) {
-        if (lane == 0) {                                         // ---- MMA issuer ----
+        if (lane == 0) {                                         // ---- issuer of the scores S = Q K^T ----
             constexpr unsigned idesc_qk = make_idesc(BM, BN);
-            constexpr unsigned idesc_pv = make_idesc(BM, HD) | IDESC_B_MN_MAJOR;
             // descriptors: upper words once, lower words (the address field, in 16-byte units) by addition
-            const unsigned long long dq = make_smem_desc(Qs), dk = make_smem_desc(Ks), dp = make_smem_desc(Ps);
-            const unsigned long long dv = make_smem_desc_lbo_sbo(Vs, BN * ROW_BYTES, 8 * ROW_BYTES);
-            const unsigned q_lo = (unsigned)dq, k_lo = (unsigned)dk, p_lo = (unsigned)dp, v_lo = (unsigned)dv;
-            const unsigned kmaj_hi = (unsigned)(dq >> 32), v_hi = (unsigned)(dv >> 32);
+            const unsigned long long dq = make_smem_desc(Qs), dk = make_smem_desc(Ks);
+            const unsigned q_lo = (unsigned)dq, k_lo = (unsigned)dk, kmaj_hi = (unsigned)(dq >> 32);
             bool ok = true;
-            auto issue_qk = [&](int it) {
+            for (int it = 0; it < n_tiles; ++it) {
                 const int s = it & 1;
-                if (!mbar_wait_bounded(&k_full[s], (unsigned)((it / 2) & 1))) { ok = false; return; }
+                // the score buffer is free once every row of the tile two before has been read
+                if ((it >= 2 && !mbar_wait_bounded(&s_free[s], (unsigned)((it / 2 - 1) & 1))) ||
+                    !mbar_wait_bounded(&k_full[s], (unsigned)((it / 2) & 1))) { ok = false; break; }
                 tc5_fence_after();
                 const unsigned kb = k_lo + (unsigned)s * (KV_STAGE >> 4), tc = tmem_base + (unsigned)(s * BN);
 #pragma unroll
@@ -250,12 +252,19 @@ flash_tc5_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constan
                 }
                 tc5_commit(&k_empty[s]);
                 tc5_commit(&s_full[s]);
-            };
-            issue_qk(0);
-            for (int it = 0; it < n_tiles && ok; ++it) {
+            }
+            if (!ok) atomicExch(&failed, 1);
+        }
+    } else if (warp == 6) {
+        if (lane == 0) {                                         // ---- issuer of the output O += P V ----
+            constexpr unsigned idesc_pv = make_idesc(BM, HD) | IDESC_B_MN_MAJOR;
+            const unsigned long long dp = make_smem_desc(Ps);
+            const unsigned long long dv = make_smem_desc_lbo_sbo(Vs, BN * ROW_BYTES, 8 * ROW_BYTES);
+            const unsigned p_lo = (unsigned)dp, v_lo = (unsigned)dv;
+            const unsigned kmaj_hi = (unsigned)(dp >> 32), v_hi = (unsigned)(dv >> 32);
+            bool ok = true;
+            for (int it = 0; it < n_tiles; ++it) {
                 const int s = it & 1;
-                if (it + 1 < n_tiles) issue_qk(it + 1);          // the next scores run during this tile's softmax
-                if (!ok) break;
                 if (!mbar_wait_bounded(&p_full, (unsigned)(it & 1)) ||
                     !mbar_wait_bounded(&v_full[s], (unsigned)((it / 2) & 1)) ||
                     (it == n_tiles - 1 && !mbar_wait_bounded(&v_fixed, 0u))) { ok = false; break; }
@@ -287,6 +296,8 @@ flash_tc5_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constan
             tc5_ld32_nowait(tmem_base + lane_base + (unsigned)(s * BN), sv);
             tc5_ld32_nowait(tmem_base + lane_base + (unsigned)(s * BN + 32), sv + 32);
             tc5_wait_ld();
+            tc5_fence_before();
+            mbar_arrive(&s_free[s]);                             // the scores are in registers: the buffer may be written again
             const int j0 = (jt0 + it) * BN;
             // (warp-uniform) does any row of this warp see a key of the tile that it must not read?
             const bool edge = (j0 + BN - 1 > pos0 + warp * 32) || (window > 0 && j0 < pos0 + warp * 32 + 31 - window + 1);
