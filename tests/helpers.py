@@ -19,8 +19,14 @@ TINY_A = dict(architectures=["Qwen3ForCausalLM"], model_type="qwen3", hidden_siz
 TINY_B = dict(architectures=["Qwen3ForCausalLM"], model_type="qwen3", hidden_size=96, num_hidden_layers=3,
               num_attention_heads=8, num_key_value_heads=2, head_dim=32, intermediate_size=160, vocab_size=333,
               rope_theta=1000000.0, rms_norm_eps=1e-5, tie_word_embeddings=False, max_position_embeddings=512)
+# head size 64: the size class of the tcgen05 / TMA attention kernels (used for long portions and, with
+# pages of 64 positions, for decoding); the other sizes are again no powers of two
+TINY_C = dict(architectures=["Qwen3ForCausalLM"], model_type="qwen3", hidden_size=72, num_hidden_layers=2,
+              num_attention_heads=6, num_key_value_heads=2, head_dim=64, intermediate_size=104, vocab_size=301,
+              rope_theta=50000.0, rms_norm_eps=3e-6, tie_word_embeddings=False, max_position_embeddings=640)
 TINY = {"A": dict(config=TINY_A, seed=0, std=0.02, page_size=16),
-        "B": dict(config=TINY_B, seed=1, std=0.05, page_size=8)}
+        "B": dict(config=TINY_B, seed=1, std=0.05, page_size=8),
+        "C": dict(config=TINY_C, seed=2, std=0.04, page_size=16)}
 
 # max |engine - plain| allowed, as a fraction of max |plain| over the compared rows
 TOL = {"float32": 2e-5, "bfloat16": 4e-2}

@@ -2,7 +2,7 @@
 each request alone and whole; most of it in one step and the last 32 tokens one by
 one; portions of changing size down to two tokens; and up to four live requests
 mixed, portions of some beside decoded tokens of others, with so few pages that
-they are used again.  In float32 and in bfloat16, on both tiny configurations."""
+they are used again.  In float32 and in bfloat16, on the tiny configurations."""
 import json
 import os
 import subprocess
@@ -17,8 +17,8 @@ import helpers as H
 
 pytestmark = pytest.mark.gpu
 ROOT = Path(__file__).resolve().parent.parent
-CASES = [(w, d) for w in ("A", "B") for d in ("float32", "bfloat16")]
-LENGTHS = {"A": [5, 17, 33, 70], "B": [1, 9, 40, 64, 100]}
+CASES = [(w, d) for w in ("A", "B", "C") for d in ("float32", "bfloat16")]
+LENGTHS = {"A": [5, 17, 33, 70], "B": [1, 9, 40, 64, 100], "C": [3, 64, 65, 128]}
 
 
 def pages_for(which, tokens):
@@ -118,6 +118,36 @@ def test_mixed_with_page_reuse(which, dtype):
     assert runner.cache.free_pages() == [live_peak]
 
 
+@pytest.mark.parametrize("page_size", [16, 64])
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_long_portions_and_head_size_64(dtype, page_size):
+    """A configuration with 64-wide heads and prompts of several hundred tokens: in bfloat16 the
+    portions of more than 64 tokens run on the tcgen05 attention kernel and, with pages of 64
+    positions, decoding on the persistent TMA kernel.  Whole prompt; two long portions and 32 tokens
+    one by one; and steps that hold a long portion of one request beside decoded tokens of two others."""
+    which = "C"
+    toks = H.tokens_for(which, 332, 41)
+    pages = -(-400 // page_size) + 2
+    runner = H.make_runner(which, dtype, num_pages=pages, page_size=page_size)
+    rows = H.run_schedule(runner, [([("r", toks, [0, 63, 64, 127, 128, 200, 331])], ["r"])])
+    H.assert_rows_match(rows, which, {"r": toks}, dtype, "whole, long")
+    schedule = [([("r", toks[:130], [129])], []), ([("r", toks[130:300], [0, 100, 169])], [])]
+    schedule += [([("r", [toks[p]], [0])], []) for p in range(300, 332)]
+    rows = H.run_schedule(runner, schedule + [([("r", [5], [])], ["r"])])
+    assert len(rows) == 36
+    H.assert_rows_match(rows, which, {"r": toks + [5]}, dtype, "long portions, then decode")
+    reqs = {"a": H.tokens_for(which, 90, 42), "b": H.tokens_for(which, 150, 43), "c": H.tokens_for(which, 260, 44)}
+    need = sum(-(-len(t) // page_size) for t in reqs.values())
+    runner = H.make_runner(which, dtype, num_pages=need, page_size=page_size)
+    S = [([("a", reqs["a"][:80], [79]), ("b", reqs["b"][:140], [139])], []),
+         ([("a", reqs["a"][80:81], [0]), ("b", reqs["b"][140:141], [0]), ("c", reqs["c"][:129], [0, 128])], []),
+         ([("a", reqs["a"][81:82], [0]), ("c", reqs["c"][129:259], [129]), ("b", reqs["b"][141:142], [0])], []),
+         ([("c", reqs["c"][259:], [0]), ("a", reqs["a"][82:], [7]), ("b", reqs["b"][142:], [7])], ["a", "b", "c"])]
+    rows = H.run_schedule(runner, S)
+    H.assert_rows_match(rows, which, reqs, dtype, "long portions beside decoded tokens")
+    assert runner.cache.free_pages() == [need]
+
+
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 def test_python_and_native_host_paths_agree(dtype):
     """The batch laid out by the Python reference code and by the C++ core gives the same logits, bit for bit."""
@@ -129,7 +159,7 @@ def test_python_and_native_host_paths_agree(dtype):
         assert torch.equal(a[k], b[k]), k
 
 
-@pytest.mark.parametrize("which", ["A", "B"])
+@pytest.mark.parametrize("which", ["A", "B", "C"])
 def test_cuts_agree_bitwise_in_float32(which):
     """The float32 kernels add in an order that depends on positions alone, so a
     position's logits are bit-for-bit the same however the tokens were cut."""
