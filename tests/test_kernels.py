@@ -247,6 +247,51 @@ def test_qk_norm_rope_write(dtype, nq, nkv, hd, rot, page):
     assert int(e.item()) & 2
 
 
+@pytest.mark.parametrize("nq,nkv,hd", [(8, 2, 128), (3, 1, 64), (5, 5, 32), (2, 1, 256)])
+def test_qk_norm_rope_write_many_tokens(nq, nkv, hd):
+    """From 256 tokens on, bfloat16 steps with wholly rotated heads of a power-of-two size take the
+    kernel with 16-byte accesses: against the plain functions and against the other kernel."""
+    dtype = torch.bfloat16
+    T, page, theta, eps = 300, 16, 1e6, 1e-6
+    pages = T // page + 2
+    torch.manual_seed(hd)
+    qkv = torch.randn(T, (nq + 2 * nkv) * hd, device=DEV).to(dtype)
+    pos = torch.arange(T, dtype=torch.int32, device=DEV) + 17
+    perm = torch.randperm(pages * page)[:T]
+    perm[5] = -1                                        # a token that writes no cache
+    slots = perm.to(torch.int32).to(DEV)
+    qw, kw = 1 + 0.1 * torch.randn(hd, device=DEV), 1 + 0.1 * torch.randn(hd, device=DEV)
+    from vllm_lite_b200.parts.rope import inverse_frequencies
+    inv = torch.from_numpy(inverse_frequencies(hd, theta)).to(DEV)
+    src = qkv.float().cpu()
+    outs = []
+    for rows in (T, 100):                               # 300 rows: the wide kernel; 3 x 100 rows: the other one
+        q2 = qkv.clone()
+        kc = torch.full((pages, nkv, page, hd), 77.0, device=DEV, dtype=dtype)
+        vc = torch.full((pages, nkv, page, hd), 77.0, device=DEV, dtype=dtype)
+        e = err_word()
+        for lo_ in range(0, T, rows):
+            ops().qk_norm_rope_write(q2[lo_:lo_ + rows], pos[lo_:lo_ + rows], slots[lo_:lo_ + rows], qw, kw, eps, inv, hd,
+                                     kc, vc, nq, nkv, hd, e)
+        assert int(e.item()) == 0
+        outs.append((q2[:, :nq * hd].float().cpu(), kc.float().cpu(), vc.float().cpu()))
+    q_ref = plain_head_norm_rope(src[:, :nq * hd].view(T, nq, hd), qw.cpu(), eps, pos.tolist(), theta, hd)
+    k_ref = plain_head_norm_rope(src[:, nq * hd:(nq + nkv) * hd].view(T, nkv, hd), kw.cpu(), eps, pos.tolist(), theta, hd)
+    v_ref = src[:, (nq + nkv) * hd:].view(T, nkv, hd)
+    for q_out, kc, vc in outs:
+        assert torch.allclose(q_out.view(T, nq, hd), q_ref, **tol(dtype))
+        for t in range(T):
+            s_ = int(slots[t])
+            if s_ < 0:
+                continue
+            assert torch.allclose(kc[s_ // page, :, s_ % page], k_ref[t], **tol(dtype)), t
+            assert torch.equal(vc[s_ // page, :, s_ % page], v_ref[t]), t
+        written = torch.zeros(pages * page, dtype=torch.bool)
+        written[slots[slots >= 0].long().cpu()] = True
+        assert bool((kc.permute(0, 2, 1, 3).reshape(pages * page, -1)[~written] == 77.0).all())
+    assert torch.allclose(outs[0][0], outs[1][0], atol=2e-2, rtol=2e-2) and torch.equal(outs[0][2], outs[1][2])
+
+
 def paged_reference(q, keys, values, pos, scale, window):
     """q [nq, hd] at position pos against keys/values [n, nkv, hd] (n > pos)."""
     nq, nkv = q.shape[0], keys.shape[1]
