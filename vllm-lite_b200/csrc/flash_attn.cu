@@ -94,7 +94,7 @@ __device__ __forceinline__ void load_kv_tiles(bf16* ktile, bf16* vtile, const bf
 }  // namespace
 
 // tiles[i] = {row of the block table, index of the tile's first token in the step, tokens, position of the first};
-// block x serves the tokens 64 * (x % parts) ... of tile x / parts
+// blocks (h, y) serve head h and, of the list walked from its end, the tokens 64 * (y' % parts) ... of tile y' / parts
 extern "C" __global__ void __launch_bounds__(NTHREADS)
 flash_prefill_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restrict__ out,
                      const bf16* __restrict__ kcache, const bf16* __restrict__ vcache,
@@ -105,11 +105,14 @@ flash_prefill_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restrict_
     bf16* Ks = Qs + BM * LDS;                                    // [2][BN][LDS]
     bf16* Vs = Ks + 2 * BN * LDS;                                // [2][BN][LDS]
     __shared__ int s_rows[2][BN];                                // cache rows of the tile being loaded / the next one
-    const int4 tile = tiles[blockIdx.x / parts];
-    const int part0 = (int)(blockIdx.x % parts) * BM;
+    // blocks start in the order of their number (x fastest); the list is in order of position, so it
+    // is walked from its end: the tiles with the longest rows of keys start first, for all heads
+    const int which = (int)gridDim.y - 1 - (int)blockIdx.y;
+    const int4 tile = tiles[which / parts];
+    const int part0 = (which % parts) * BM;
     if (part0 >= tile.z) return;
     const int req = tile.x, tok0 = tile.y + part0, count = min(BM, tile.z - part0), pos0 = tile.w + part0;
-    const int h = blockIdx.y, kvh = h / (nq / nkv);
+    const int h = blockIdx.x, kvh = h / (nq / nkv);
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, t = lane & 3;
     const int* table = block_table + (size_t)req * max_blocks;
     const int hi = pos0 + count - 1;                             // the last key any row reads
@@ -265,11 +268,11 @@ extern "C" int vl_flash_prefill(const void* q, int q_stride, void* out, const vo
     if (nq <= 0 || nkv <= 0 || nq % nkv || page_size <= 0 || max_blocks <= 0 || q_stride % 8) return VL_ERR_ARGUMENT;
     if (tile_rows <= 0 || tile_rows > 65536) return VL_ERR_ARGUMENT;
     const int parts = (tile_rows + BM - 1) / BM;                 // blocks per tile of the list
-    if (nq > 65535) return VL_ERR_UNSUPPORTED;
+    if ((long long)num_tiles * parts > 65535) return VL_ERR_UNSUPPORTED;
     const size_t smem = (size_t)(BM + 4 * BN) * LDS * sizeof(bf16);
     cudaError_t e = cudaFuncSetAttribute(flash_prefill_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return (int)e;
-    flash_prefill_kernel<<<dim3(num_tiles * parts, nq), NTHREADS, smem, (cudaStream_t)stream>>>(
+    flash_prefill_kernel<<<dim3(nq, num_tiles * parts), NTHREADS, smem, (cudaStream_t)stream>>>(
         (const bf16*)q, q_stride, (bf16*)out, (const bf16*)kcache, (const bf16*)vcache, block_table, max_blocks,
         (const int4*)tiles, parts, nq, nkv, page_size, num_pages, scale * 1.4426950408889634f, window, err);
     return vl_launch_status();

@@ -150,9 +150,12 @@ flash_tc5_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constan
     pdl_launch_dependents();
     pdl_wait();                                      // q and the cache are written by the kernel before
 
-    const int4 tile = tiles[num_tiles - 1 - (int)blockIdx.x];   // the list is in order of position: long rows of keys first
+    // The list is in order of position and blocks start in the order of their number (x fastest): the
+    // tiles with the longest rows of keys go first, for all heads, so that the longest blocks do not
+    // start last.
+    const int4 tile = tiles[num_tiles - 1 - (int)blockIdx.y];
     const int req = tile.x, tok0 = tile.y, count = tile.z, pos0 = tile.w;
-    const int h = blockIdx.y, kvh = h / (nq / nkv);
+    const int h = blockIdx.x, kvh = h / (nq / nkv);
     const int hi = pos0 + count - 1;                             // the last key any row reads
     const int lo = (window > 0 && pos0 - window + 1 > 0) ? pos0 - window + 1 : 0;   // the first key any row reads
     const int jt0 = lo / BN, n_tiles = hi / BN - jt0 + 1;
@@ -395,7 +398,7 @@ extern "C" int vl_flash_prefill_tc5(const void* q, int q_stride, void* out, cons
     if (nq <= 0 || nkv <= 0 || nq % nkv || page_size <= 0 || max_blocks <= 0 || num_pages <= 0) return VL_ERR_ARGUMENT;
     if (page_size % 8 || (page_size < BN ? BN % page_size : page_size % BN)) return VL_ERR_UNSUPPORTED;
     if (q_stride % 8 || (((uintptr_t)q | (uintptr_t)out | (uintptr_t)kcache | (uintptr_t)vcache) & 15)) return VL_ERR_UNSUPPORTED;
-    if (nq > 65535) return VL_ERR_UNSUPPORTED;
+    if (num_tiles > 65535) return VL_ERR_UNSUPPORTED;
     const long long rows = (long long)num_pages * nkv * page_size;
     if (rows + BN >= (1ll << 31)) return VL_ERR_UNSUPPORTED;
     const int box_rows = page_size < BN ? page_size : BN;
@@ -406,7 +409,7 @@ extern "C" int vl_flash_prefill_tc5(const void* q, int q_stride, void* out, cons
     if (rc) return rc;
     cudaError_t e = cudaFuncSetAttribute(flash_tc5_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM_BYTES);
     if (e != cudaSuccess) return (int)e;
-    return vl_launch(flash_tc5_kernel, dim3(num_tiles, nq), dim3(NTHREADS), SMEM_BYTES, (cudaStream_t)stream,
+    return vl_launch(flash_tc5_kernel, dim3(nq, num_tiles), dim3(NTHREADS), SMEM_BYTES, (cudaStream_t)stream,
                      map_k, map_v, (const bf16*)q, q_stride, (bf16*)out, block_table, max_blocks, (const int4*)tiles,
                      num_tiles, nq, nkv, page_size, num_pages, scale * 1.4426950408889634f, window, err);
 }
