@@ -7,13 +7,15 @@ import pytest
 from vllm_lite_b200.cache import CacheLayout, CacheManager, PagedKV
 from vllm_lite_b200.cache.native import NativeCacheManager
 
-BACKEND = {"cls": CacheManager}
+BACKEND = {"cls": CacheManager, "native_policy": None}
 
 
-@pytest.fixture(autouse=True, params=["python", "native"])
+@pytest.fixture(autouse=True, params=["python", "native", "native cache, python policy"])
 def cache_backend(request):
-    """Every test runs with the Python cache manager and with the C++ core under the scheduler."""
+    """Every test runs with the Python cache manager and policy, with the C++ core for both, and
+    with the C++ cache core under the Python policy."""
     BACKEND["cls"] = CacheManager if request.param == "python" else NativeCacheManager
+    BACKEND["native_policy"] = {"python": False, "native": True}.get(request.param, False)
     yield
 from vllm_lite_b200.engine.scheduler import AdmissionError, Scheduler, SchedulerConfig
 from vllm_lite_b200.sampling import SamplingParams
@@ -22,7 +24,7 @@ from vllm_lite_b200.sampling import SamplingParams
 def make(num_pages=64, page_size=4, max_requests=8, **cfg):
     lay = CacheLayout.from_needs([PagedKV(2, 16)], [None])
     cache = BACKEND["cls"](lay, page_size, num_pages, max_requests)
-    return cache, Scheduler(cache, SchedulerConfig(**cfg))
+    return cache, Scheduler(cache, SchedulerConfig(**cfg), native=BACKEND["native_policy"])
 
 
 def run_step(cache, sched, token_of=lambda seq: 7):
@@ -149,3 +151,42 @@ def test_random_traffic_never_leaks_or_exceeds_limits(seed):
         run_step(cache, s)
     assert all(q.status == "finished" and len(q.generated) == q.max_tokens for q in seqs)
     assert cache.free_pages() == [30] and cache.slots.free_count == 6
+
+
+@pytest.mark.parametrize("seed", range(5))
+def test_the_native_policy_decides_as_the_python_policy(seed):
+    """Two engines' worth of host state fed the same traffic, one deciding in Python and one in the
+    C++ core: the same entries, the same victims, step by step, through admissions, portions,
+    pre-emptions and a pool with a window."""
+    rng = random.Random(100 + seed)
+    lay = CacheLayout.from_needs([PagedKV(2, 16), PagedKV(1, 8, window=11)], [None, None])
+    cfg = dict(max_num_seqs=5, max_num_batched_tokens=20, prefill_chunk_size=7)
+    pair = []
+    for native in (False, True):
+        cache = NativeCacheManager(lay, 4, [26, 40], 5)
+        pair.append((cache, Scheduler(cache, SchedulerConfig(**cfg), native=native)))
+    assert pair[0][1].native is False and pair[1][1].native is True
+    added = 0
+    for step in range(300):
+        if rng.random() < 0.35 and added < 30:
+            prompt, mt = [rng.randrange(50) for _ in range(rng.randint(1, 30))], rng.randint(1, 25)
+            for _, s in pair:
+                s.add_request(prompt, mt)
+            added += 1
+        plans = []
+        for cache, s in pair:
+            if not s.has_work():
+                plans.append(None)
+                continue
+            plan = s.schedule()
+            for e in plan.entries:
+                if e.seq.seq_id not in cache.requests:
+                    cache.admit(e.seq.seq_id)
+                cache.append(e.seq.seq_id, e.count)
+                cache.release_behind_window(e.seq.seq_id)
+            s.update(plan, [7 if e.samples else None for e in plan.entries])
+            cache.check_invariants()
+            plans.append(([(e.seq.seq_id, e.start, e.count, e.samples) for e in plan.entries],
+                          [v.seq_id for v in plan.preempted]))
+        assert plans[0] == plans[1], (step, plans)
+    assert pair[0][1].stats == pair[1][1].stats and pair[0][1].stats["preemptions"] > 0

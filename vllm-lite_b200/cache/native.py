@@ -39,6 +39,7 @@ def _core():
             "vc_check": (I, [V]),
             "vc_pack_step": (L, [V, I, V, V, V, V, V, V, I, I, V, V, L, V, V]),
             "vc_decode_step": (L, [V, I, V, V, I, I, L, V, L, V, V, V]),
+            "vs_schedule": (I, [V, I, L, L, I, I, V, V, V, V, V, V, V, V, V, V, V]),
         }
         for name, (res, args) in sig.items():
             fn = getattr(lib, name)
@@ -204,6 +205,33 @@ class NativeCacheManager:
         self._call("vc_check")
         if len(self.requests) != _core().vc_num_requests(self._h):
             raise PoolError("the host's and the core's lists of requests differ")
+
+    def schedule(self, max_num_seqs, max_num_batched_tokens, prefill_chunk_size, n_run, remaining, computed,
+                 request_ids, arrival):
+        """The scheduler's decision in the C++ core (csrc/host/cache_core.cpp, vs_schedule): sequences
+        0 .. n_run - 1 run (in order of arrival), the rest wait (from the head of the queue);
+        request_ids[i] is None for a sequence that holds nothing in the cache.  Returns
+        (entries [(sequence, tokens)], victims, admitted); raises OutOfPages when a sequence that runs
+        alone cannot get its pages."""
+        n = len(remaining)
+        rem = np.ascontiguousarray(remaining, dtype=np.int64)
+        comp = np.ascontiguousarray(computed, dtype=np.int64)
+        keys = np.fromiter((self._keys[r] if r is not None else 0 for r in request_ids), dtype=np.int64, count=n)
+        arr = np.ascontiguousarray(arrival, dtype=np.int64)
+        e_seq, e_cnt = np.zeros(max(n, 1), dtype=np.int32), np.zeros(max(n, 1), dtype=np.int64)
+        victims, admitted = np.zeros(max(n, 1), dtype=np.int32), np.zeros(max(n, 1), dtype=np.int32)
+        ne, nv, na = c_int(), c_int(), c_int()
+        ptr = lambda a: a.ctypes.data
+        rc = _core().vs_schedule(self._h, int(max_num_seqs), int(max_num_batched_tokens), int(prefill_chunk_size),
+                                 int(n_run), n - int(n_run), ptr(rem), ptr(comp), ptr(keys), ptr(arr), ptr(e_seq),
+                                 ptr(e_cnt), ctypes.addressof(ne), ptr(victims), ctypes.addressof(nv), ptr(admitted),
+                                 ctypes.addressof(na))
+        if rc == -1:
+            raise OutOfPages("a sequence cannot get its pages although it runs alone")
+        if rc < 0:
+            raise PoolError(_ERR.get(rc, f"native cache core error {rc}"))
+        return (list(zip(e_seq[:ne.value].tolist(), e_cnt[:ne.value].tolist())), victims[:nv.value].tolist(),
+                admitted[:na.value].tolist())
 
     def decode_step(self, request_ids, tokens, pad_to: int, fixed_blocks: int, max_tokens: int, out: np.ndarray):
         """One token for each of the requests, in one call of the core: the check that the pools can

@@ -13,6 +13,7 @@
 #include <cstdint>
 #include <cstring>
 #include <unordered_map>
+#include <algorithm>
 #include <vector>
 
 namespace {
@@ -445,6 +446,121 @@ long long vc_decode_step(void* h, int B, const long long* keys, const int* token
         if (rc) return rc;
     }
     return used;
+}
+
+// ---- the scheduler's decision ---------------------------------------------------------------------
+// What one step holds, decided from the state of the queues and of the pools (engine/scheduler.py
+// states the policy and is the reference implementation; both run the same tests).  Nothing is
+// changed here: the caller applies the answer (pre-empts the victims, moves the admitted).
+//   Sequences are numbered 0 .. n_run + n_wait - 1: the running ones in order of arrival, then the
+//   queue from its head.  remaining[i] = tokens not yet in the cache (1: decoding), computed[i] =
+//   tokens in the cache, keys[i] = the cache's key of the request or 0 when it holds nothing,
+//   arrival[i] = its arrival number.
+//   A step holds the next token of every decoding request, then portions of running prompts, then
+//   admissions from the head of the queue, under max_num_batched_tokens / max_num_seqs /
+//   prefill_chunk_size; a running sequence that cannot get its pages makes the most recently arrived
+//   running sequence a victim (its pages count as free, it goes back to the head of the queue with
+//   all its tokens to compute) and the step is composed again.
+//   Out: entries (sequence number, tokens) in step order, victims in the order they were chosen, and
+//   admitted sequence numbers in order.  Returns the number of entries, or VC_NO_SPACE when a sequence
+//   that runs alone cannot get its pages, VC_ARGUMENT for inconsistent input.
+int vs_schedule(void* h, int max_num_seqs, long long max_num_batched_tokens, long long prefill_chunk_size,
+                int n_run, int n_wait, const long long* remaining, const long long* computed, const long long* keys,
+                const long long* arrival, int* entry_seq, long long* entry_count, int* n_entries,
+                int* victims, int* n_victims, int* admitted, int* n_admitted) {
+    Core* c = static_cast<Core*>(h);
+    const int G = (int)c->pools.size();
+    const long long ps = c->page_size;
+    if (n_run < 0 || n_wait < 0 || max_num_seqs <= 0 || max_num_batched_tokens <= 0 || prefill_chunk_size <= 0) return VC_ARGUMENT;
+    const int n = n_run + n_wait;
+    std::vector<long long> rem(remaining, remaining + n), comp(computed, computed + n);
+    std::vector<char> holds(n, 0);                   // the sequence holds pages (and a slot) in the cache
+    std::vector<int> running, waiting;
+    for (int i = 0; i < n; ++i) {
+        if (keys[i]) {
+            if (!c->requests.count(keys[i])) return VC_UNKNOWN;
+            holds[i] = 1;
+        }
+        (i < n_run ? running : waiting).push_back(i);
+    }
+    std::vector<int> extra_free(G, 0);               // pages of the victims chosen so far
+    int extra_slots = 0;
+    *n_victims = 0;
+    auto pages_for = [&](int i, long long count) {    // the blocks that count more positions open
+        const long long held = holds[i] ? comp[i] : 0;
+        return (int)((held + count + ps - 1) / ps - (held + ps - 1) / ps);
+    };
+    auto chunk = [&](int i, long long room) {
+        long long k = rem[i] < room ? rem[i] : room;
+        if (rem[i] > 1 && k > prefill_chunk_size) k = prefill_chunk_size;
+        return k;
+    };
+    for (;;) {
+        std::vector<int> free(G);
+        for (int g = 0; g < G; ++g) free[g] = c->pools[g].free_count() + extra_free[g];
+        int free_slots = c->slots.free_count() + extra_slots;
+        long long room = max_num_batched_tokens;
+        std::vector<int> es;
+        std::vector<long long> ec;
+        std::vector<int> run_now = running, wait_now = waiting, adm;
+        int starved = -1;
+        std::vector<int> order;
+        for (int i : run_now) if (rem[i] == 1) order.push_back(i);
+        for (int i : run_now) if (rem[i] > 1) order.push_back(i);
+        for (int i : order) {
+            const long long k = chunk(i, room);
+            if (k <= 0) continue;
+            const int need = pages_for(i, k);
+            bool fits = true;
+            for (int g = 0; g < G; ++g) fits = fits && need <= free[g];
+            if (!fits) {
+                if (run_now.size() == 1 && es.empty()) return VC_NO_SPACE;
+                starved = i;
+                break;
+            }
+            for (int g = 0; g < G; ++g) free[g] -= need;
+            room -= k;
+            es.push_back(i); ec.push_back(k);
+        }
+        if (starved < 0) {
+            size_t head = 0;
+            while (head < wait_now.size() && room > 0 && (int)run_now.size() < max_num_seqs) {
+                const int i = wait_now[head];
+                const long long k = chunk(i, room);
+                const int need = pages_for(i, k);
+                bool fits = true;
+                for (int g = 0; g < G; ++g) fits = fits && need <= free[g];
+                if (!fits || (!holds[i] && free_slots < 1)) break;     // head of line: never admit what cannot get pages
+                ++head;
+                run_now.push_back(i);
+                if (!holds[i]) --free_slots;
+                for (int g = 0; g < G; ++g) free[g] -= need;
+                room -= k;
+                es.push_back(i); ec.push_back(k);
+                adm.push_back(i);
+            }
+            *n_entries = (int)es.size();
+            for (size_t e = 0; e < es.size(); ++e) { entry_seq[e] = es[e]; entry_count[e] = ec[e]; }
+            *n_admitted = (int)adm.size();
+            for (size_t a = 0; a < adm.size(); ++a) admitted[a] = adm[a];
+            return (int)es.size();
+        }
+        // the most recently arrived running sequence yields
+        int v = running[0];
+        for (int i : running) if (arrival[i] > arrival[v]) v = i;
+        running.erase(std::find(running.begin(), running.end(), v));
+        if (holds[v]) {
+            const Request& r = c->requests[keys[v]];
+            for (int g = 0; g < G; ++g)
+                for (int page : r.tables[g]) if (page >= 0) ++extra_free[g];
+            ++extra_slots;
+            holds[v] = 0;
+        }
+        rem[v] += comp[v];                            // everything is computed again
+        comp[v] = 0;
+        waiting.insert(waiting.begin(), v);
+        victims[(*n_victims)++] = v;
+    }
 }
 
 }  // extern "C"

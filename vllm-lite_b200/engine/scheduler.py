@@ -85,9 +85,16 @@ class AdmissionError(ValueError):
 
 
 class Scheduler:
-    def __init__(self, cache, config: SchedulerConfig = None):
+    def __init__(self, cache, config: SchedulerConfig = None, native: Optional[bool] = None):
+        """`native`: take each step's decision in the C++ core (the cache manager must be the native
+        one; default: whenever it is).  The Python policy below is the reference; both are run by
+        the same tests and must decide alike."""
         self.cache = cache
         self.config = (config or SchedulerConfig()).validate()
+        can = hasattr(cache, "schedule")
+        if native and not can:
+            raise ValueError("the native scheduler needs the native cache manager")
+        self.native = can if native is None else bool(native)
         self.waiting: Deque[Sequence] = deque()
         self.running: List[Sequence] = []
         self.finished: List[Sequence] = []
@@ -123,6 +130,8 @@ class Scheduler:
 
     # ---- one step -----------------------------------------------------------
     def schedule(self) -> StepPlan:
+        if self.native:
+            return self._schedule_native()
         plan = StepPlan()
         while True:
             entries, starved = self._compose()
@@ -132,6 +141,38 @@ class Scheduler:
             self._preempt(victim)
             plan.preempted.append(victim)
         plan.entries = entries
+        return plan
+
+    def _schedule_native(self) -> StepPlan:
+        """The same decision taken by the C++ core; what it answers is applied here."""
+        cfg = self.config
+        seqs = list(self.running) + list(self.waiting)
+        if not seqs:
+            return StepPlan()
+        held = [s.seq_id if s.seq_id in self.cache.requests else None for s in seqs]
+        try:
+            entries, victims, admitted = self.cache.schedule(
+                cfg.max_num_seqs, cfg.max_num_batched_tokens, cfg.prefill_chunk_size, len(self.running),
+                [s.remaining for s in seqs], [s.num_computed for s in seqs], held, [s.arrival for s in seqs])
+        except Exception as e:
+            if type(e).__name__ == "OutOfPages":
+                raise RuntimeError(f"a sequence cannot get its pages although it runs alone") from e
+            raise
+        plan = StepPlan()
+        for v in victims:
+            self._preempt(seqs[v])
+            plan.preempted.append(seqs[v])
+        for a in admitted:
+            seq = seqs[a]
+            if not self.waiting or self.waiting[0] is not seq:
+                raise RuntimeError("the native scheduler admitted a sequence that is not at the head of the queue")
+            self.waiting.popleft()
+            seq.status = "running"
+            self.running.append(seq)
+        if admitted:
+            self.running.sort(key=lambda s: s.arrival)
+        plan.entries = [Scheduled(seqs[i], seqs[i].num_computed, int(n), seqs[i].num_computed + int(n) == len(seqs[i].tokens))
+                        for i, n in entries]
         return plan
 
     def _chunk(self, seq: Sequence, room: int) -> int:
