@@ -251,7 +251,7 @@ def main(argv=None):
     step_bytes = weight_bytes + args.batch * mean_ctx * kv_per_token
     achieved = step_bytes / (ms * 1e-3) / 1e9
     out = {
-        "metric": METRIC.replace("8B", args.size.upper()), "value": round(value, 1), "unit": "tokens/s", "n_gpus": 1, "steps": args.steps,
+        "metric": METRIC.replace("8B", args.size.upper()).replace("batch 8", f"batch {args.batch}"), "value": round(value, 1), "unit": "tokens/s", "n_gpus": 1, "steps": args.steps,
         "warmup": warmup, "ms_per_step": round(ms, 4), "higher_is_better": True, "scaling": "weak",
         "vs_baseline": None, "dtype": "bf16", "data": "synthetic (random weights N(0,0.02), uniform token ids)",
         "config": {"model": f"Qwen3-{args.size.upper()} layer sizes", "layers": args.layers, "layers_full": full_layers,
