@@ -9,8 +9,8 @@
 // chunk) each block's start-up (positions, block table, first copies) and wind-down are paid once
 // per 128 KB of stream.  Here one block per SM walks many such work items:
 //   warp 4   producer: looks up the pages of a work item and copies its K and V rows, 64 keys a
-//        stage, by TMA boxes (cp.async.bulk.tensor.2d, 128-byte swizzle, one box per page and 64
-//        columns) into a ring of stages that runs on across work items; it also brings the item's
+//        stage, by TMA boxes (cp.async.bulk.tensor.3d, 128-byte swizzle, one box per page: its blocks
+//        of 64 columns one after the other) into a ring of stages that runs on across work items; it also brings the item's
 //        query rows (bulk copies) and its description into one of two slots.  The producer runs
 //        ahead of the arithmetic by the depth of the ring, so the start-up of the next item is
 //        hidden behind the stream of this one;
@@ -180,11 +180,10 @@ flash_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_
                 }
                 ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
                 if (ok && lane < nbox) {
-                    unsigned char* kt = ring + (unsigned)s * STAGE_BYTES + (unsigned)(lane * box_rows) * ROW_BYTES;
-                    for (int cb = 0; cb < CB; ++cb) {
-                        tma_load_2d(kt + (unsigned)cb * (BN * ROW_BYTES), &map_k, cb * 64, row, &full[s]);
-                        tma_load_2d(kt + KV_BYTES + (unsigned)cb * (BN * ROW_BYTES), &map_v, cb * 64, row, &full[s]);
-                    }
+                    // the box of page b: its blocks of 64 columns one after the other, box_rows rows of 128 bytes each
+                    unsigned char* kt = ring + (unsigned)s * STAGE_BYTES + (unsigned)(lane * CB * box_rows) * ROW_BYTES;
+                    tma_load_3d(kt, &map_k, 0, row, 0, &full[s]);
+                    tma_load_3d(kt + KV_BYTES, &map_v, 0, row, 0, &full[s]);
                 }
                 row = row_next;
             }
@@ -195,8 +194,13 @@ flash_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_
         const unsigned ring_u32 = smem_u32(ring);
         const int kr0 = warp * 16;                       // this warp's 16 keys of every stage
         // byte offsets of this lane's ldmatrix rows inside a [64 rows][128 bytes] block and its swizzle
-        const unsigned k_row = (unsigned)(kr0 + (lane & 7) + 8 * (lane >> 4)) * ROW_BYTES;
-        const unsigned v_row = (unsigned)(kr0 + (lane & 7) + 8 * ((lane >> 3) & 1)) * ROW_BYTES;
+        // a stage holds, for K and for V, box after box (a page, or 64 rows of one), in a box the blocks of
+        // 64 columns one after the other, in a block its rows of 128 bytes
+        const int box_rows = page_size < BN ? page_size : BN;
+        const unsigned blk_bytes = (unsigned)box_rows * ROW_BYTES;           // from one block of 64 columns to the next
+        auto row_offset = [&](int r) { return (unsigned)(r / box_rows) * CB * blk_bytes + (unsigned)(r % box_rows) * ROW_BYTES; };
+        const unsigned k_row = row_offset(kr0 + (lane & 7) + 8 * (lane >> 4));
+        const unsigned v_row = row_offset(kr0 + (lane & 7) + 8 * ((lane >> 3) & 1));
         const unsigned sw = (unsigned)(lane & 7);
         int stage_it = 0, n = 0;
         bool ok = true;
@@ -229,7 +233,7 @@ flash_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_
                     unsigned char* vs = ring + (unsigned)s * STAGE_BYTES + KV_BYTES;
                     for (int r = max(ii.c1 - st * BN, kr0); r < kr0 + 16; ++r)
                         if (lane < CB * 8)
-                            *reinterpret_cast<uint4*>(vs + (unsigned)(lane >> 3) * (BN * ROW_BYTES) + (unsigned)r * ROW_BYTES + ((lane & 7) << 4)) = make_uint4(0u, 0u, 0u, 0u);
+                            *reinterpret_cast<uint4*>(vs + (unsigned)(lane >> 3) * blk_bytes + row_offset(r) + ((lane & 7) << 4)) = make_uint4(0u, 0u, 0u, 0u);
                     fence_proxy_async_smem();            // the stage is next written by the TMA unit
                     __syncwarp();
                 }
@@ -238,7 +242,7 @@ flash_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_
                 for (int ks = 0; ks < KSTEPS; ++ks) {
                     unsigned kb[4];
                     const unsigned chunk16 = (unsigned)(2 * ks + ((lane >> 3) & 1));      // 16-byte piece of the key row
-                    ldmatrix_x4(kb, kt + (chunk16 >> 3) * (BN * ROW_BYTES) + k_row + (((chunk16 & 7) ^ sw) << 4));
+                    ldmatrix_x4(kb, kt + (chunk16 >> 3) * blk_bytes + k_row + (((chunk16 & 7) ^ sw) << 4));
                     mma16816(sc[0], qf[ks], kb[0], kb[1]);
                     mma16816(sc[1], qf[ks], kb[2], kb[3]);
                 }
@@ -278,7 +282,7 @@ flash_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_
                 for (int dp = 0; dp < DTILES / 2; ++dp) {
                     unsigned vb[4];
                     const unsigned chunk16 = (unsigned)(2 * dp + (lane >> 4));            // 16-byte piece of the value row
-                    ldmatrix_x4_trans(vb, vt + (chunk16 >> 3) * (BN * ROW_BYTES) + v_row + (((chunk16 & 7) ^ sw) << 4));
+                    ldmatrix_x4_trans(vb, vt + (chunk16 >> 3) * blk_bytes + v_row + (((chunk16 & 7) ^ sw) << 4));
                     o[2 * dp][0] *= corr[0]; o[2 * dp][1] *= corr[0]; o[2 * dp][2] *= corr[1]; o[2 * dp][3] *= corr[1];
                     o[2 * dp + 1][0] *= corr[0]; o[2 * dp + 1][1] *= corr[0]; o[2 * dp + 1][2] *= corr[1]; o[2 * dp + 1][3] *= corr[1];
                     mma16816(o[2 * dp], pf, vb[0], vb[1]);
@@ -353,9 +357,9 @@ extern "C" int vl_flash_decode_tma(const void* q, int q_stride, const void* kcac
     if (rows + BN >= (1ll << 31) || items >= (1ll << 31)) return VL_ERR_UNSUPPORTED;
     const int box_rows = page_size < BN ? page_size : BN;
     CUtensorMap map_k, map_v;
-    int rc = tc5_make_map(&map_k, kcache, (int)rows, HD, HD, box_rows);
+    int rc = tc5_make_map_blocks(&map_k, kcache, (int)rows, HD, HD, box_rows);
     if (rc) return rc;
-    rc = tc5_make_map(&map_v, vcache, (int)rows, HD, HD, box_rows);
+    rc = tc5_make_map_blocks(&map_v, vcache, (int)rows, HD, HD, box_rows);
     if (rc) return rc;
     static int num_sms = 0;
     if (!num_sms) {

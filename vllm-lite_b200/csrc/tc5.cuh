@@ -38,6 +38,12 @@ __device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, i
         "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
         ::"r"(smem_u32(dst)), "l"(map), "r"(x), "r"(y), "r"(smem_u32(bar)) : "memory");
 }
+// the same with a third coordinate (z: the block of 64 columns of a row that the box takes first)
+__device__ __forceinline__ void tma_load_3d(void* dst, const CUtensorMap* map, int x, int y, int z, unsigned long long* bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4}], [%5];"
+        ::"r"(smem_u32(dst)), "l"(map), "r"(x), "r"(y), "r"(z), "r"(smem_u32(bar)) : "memory");
+}
 __device__ __forceinline__ void tc5_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void tc5_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void tc5_alloc(unsigned* smem_result, unsigned ncols) {          // whole warp
@@ -226,3 +232,19 @@ static inline int tc5_make_map(CUtensorMap* map, const void* base, int rows, int
     return r == CUDA_SUCCESS ? 0 : VL_ERR_ARGUMENT;
 }
 
+// A [rows, cols] bfloat16 matrix (cols a multiple of 64, row stride ld elements) seen as
+// (64 columns, rows, blocks of 64 columns): one box brings box_rows rows of all the blocks and lays
+// them down block after block, each block as box_rows rows of 128 bytes with the 128-byte swizzle.
+static inline int tc5_make_map_blocks(CUtensorMap* map, const void* base, int rows, int cols, int ld, int box_rows) {
+    EncodeTiledFn enc = encode_tiled_fn();
+    if (!enc) return VL_ERR_UNSUPPORTED;
+    if (cols % tc5::SWIZZLE_COLS) return VL_ERR_UNSUPPORTED;
+    cuuint64_t dims[3] = {(cuuint64_t)tc5::SWIZZLE_COLS, (cuuint64_t)rows, (cuuint64_t)(cols / tc5::SWIZZLE_COLS)};
+    cuuint64_t strides[2] = {(cuuint64_t)ld * 2, (cuuint64_t)tc5::SWIZZLE_COLS * 2};
+    cuuint32_t box[3] = {(cuuint32_t)tc5::SWIZZLE_COLS, (cuuint32_t)box_rows, (cuuint32_t)(cols / tc5::SWIZZLE_COLS)};
+    cuuint32_t estr[3] = {1, 1, 1};
+    CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(base), dims, strides, box, estr,
+                     CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                     CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    return r == CUDA_SUCCESS ? 0 : VL_ERR_ARGUMENT;
+}
