@@ -393,7 +393,8 @@ def gemm_f32(a, w, out):
     return out
 
 
-SMALL_M = 16              # most rows the weight-streaming product takes
+SMALL_M = 8               # most rows the engine gives the weight-streaming product (the kernel takes 16, but from
+                          # 9 rows on the library product is faster: batch 16 decodes in 5.82 ms against 6.15 ms)
 
 
 def gemm_bf16_small_m_ok(M, K) -> bool:
