@@ -43,6 +43,13 @@ def _align4(n: int) -> int:
     return (n + 3) & ~3
 
 
+def _pow2_at_least(n: int, floor: int = 1) -> int:
+    p = floor
+    while p < n:
+        p *= 2
+    return p
+
+
 class ModelRunner:
     def __init__(self, plan, weights: dict, *, dtype=torch.bfloat16, device="cuda:0", page_size: int = 16,
                  num_pages=1024, max_requests: int = 256, decode_graphs: bool = True,
@@ -136,9 +143,7 @@ class ModelRunner:
         B = len(ids)
         if B == 0 or len(set(ids)) != B:
             return None
-        bucket = 1
-        while bucket < B:
-            bucket *= 2
+        bucket = _pow2_at_least(B)
         fixed = -(-self.max_context // self.page_size)
         G = len(cache.pools)
         words = 64 + 8 * bucket + G * (bucket + bucket * fixed + 8)
@@ -154,11 +159,7 @@ class ModelRunner:
             self._flip ^= 1
             words = -used
         dev = self._to_device(i, used, bucket)
-        longest = int(starts.max()) + 1
-        bound = 1024
-        while bound < longest:
-            bound *= 2
-        bound = min(bound, self.max_context)
+        bound = self._context_bound(int(starts.max()) + 1)
         self.steps += 1
         entry = self._graphs.get((bucket, bound))
         if entry is not None:
@@ -180,13 +181,7 @@ class ModelRunner:
         if not (self.native_host and self.decode_graphs):
             return None
         B = len(request_ids)
-        bucket = 1
-        while bucket < B:
-            bucket *= 2
-        bound = 1024
-        while bound < longest:
-            bound *= 2
-        bound = min(bound, self.max_context)
+        bucket, bound = _pow2_at_least(B), self._context_bound(longest)
         entry = self._graphs.get((bucket, bound))
         if entry is None or longest > self.max_context or any(r not in self.cache.requests for r in request_ids):
             return None
@@ -267,10 +262,12 @@ class ModelRunner:
             return 0
         if any(len(e.want) != 1 for e in entries) or any(h.start + 1 > self.max_context for h in host_entries):
             return 0
-        bucket = 1
-        while bucket < len(entries):
-            bucket *= 2
-        return bucket
+        return _pow2_at_least(len(entries))
+
+    def _context_bound(self, longest: int) -> int:
+        """A graph is recorded for a bound on the context, not for its value: the next power of two
+        from 1,024 on, at most the longest context the runner takes."""
+        return min(_pow2_at_least(longest, 1024), self.max_context)
 
     def _layout_batch(self, entries, host_entries, bucket: int = 0) -> StepBatch:
         if self.native_host:
@@ -337,11 +334,8 @@ class ModelRunner:
         counts = [h.count for h in host_entries]
         Bp = bucket or len(host_entries)
         longest = max(h.start + h.count for h in host_entries)
-        if bucket:                       # a graph is recorded for a bound on the context, not for its value
-            bound = 1024
-            while bound < longest:
-                bound *= 2
-            longest = min(bound, self.max_context)
+        if bucket:
+            longest = self._context_bound(longest)
         groups = [GroupView(page_size=self.page_size, block_table=sec(9 + 2 * g).view(Bp, int(max_blocks[g])),
                             slots=sec(8 + 2 * g), max_context=longest) for g in range(len(self.cache.pools))]
         tiles, single = sec(6), sec(7)
@@ -439,11 +433,8 @@ class ModelRunner:
             return dev[o:o + n]
         groups = []
         longest = max(h.start + h.count for h in host_entries)
-        if bucket:                       # a graph is recorded for a bound on the context, not for its value
-            bound = 1024
-            while bound < longest:
-                bound *= 2
-            longest = min(bound, self.max_context)
+        if bucket:
+            longest = self._context_bound(longest)
         for g in range(G):
             groups.append(GroupView(page_size=ps, block_table=dview(f"table{g}").view(B, max_blocks[g]),
                                     slots=dview(f"slots{g}"), max_context=longest))

@@ -24,6 +24,7 @@ from collections import deque
 from dataclasses import dataclass, field
 from typing import Deque, List, Optional
 
+from ..cache.manager import OutOfPages
 from ..sampling.params import SamplingParams
 
 
@@ -154,10 +155,8 @@ class Scheduler:
             entries, victims, admitted = self.cache.schedule(
                 cfg.max_num_seqs, cfg.max_num_batched_tokens, cfg.prefill_chunk_size, len(self.running),
                 [s.remaining for s in seqs], [s.num_computed for s in seqs], held, [s.arrival for s in seqs])
-        except Exception as e:
-            if type(e).__name__ == "OutOfPages":
-                raise RuntimeError(f"a sequence cannot get its pages although it runs alone") from e
-            raise
+        except OutOfPages as e:
+            raise RuntimeError("a sequence cannot get its pages although it runs alone") from e
         plan = StepPlan()
         for v in victims:
             self._preempt(seqs[v])
