@@ -301,7 +301,8 @@ flash_decode_kernel(const bf16* __restrict__ q, int q_stride,
     __shared__ float s_m[4][DEC_ROWS], s_l[4][DEC_ROWS];
     __shared__ int s_rows[DEC_MAX_CHUNK + BN];                   // cache rows of the chunk's positions, tile aligned
     pdl_launch_dependents();
-    pdl_wait();
+    // What follows reads the step's description only (positions, block tables: uploaded before the
+    // step's first kernel); the wait for the kernel before stands where q and the cache are first read.
     // token_index (optional) picks the tokens of the step that this launch serves; partial results
     // are stored by the number of the token within the launch
     const int split = blockIdx.x, tok = token_index ? token_index[blockIdx.z] : (int)blockIdx.z;
@@ -320,15 +321,16 @@ flash_decode_kernel(const bf16* __restrict__ q, int q_stride,
     const int* table = block_table + (size_t)req_index[tok] * max_blocks;
     const int st0 = c0 / BN, st1 = (c1 - 1) / BN;
 
+    for (int i = tid; i < (st1 - st0 + 1) * BN; i += NTHREADS)
+        s_rows[i] = cache_row(table, max_blocks, st0 * BN + i, c0, pos, kvh, nkv, page_size, num_pages, err);
+    pdl_wait();
     for (int idx = tid; idx < DEC_ROWS * CPR; idx += NTHREADS) {
         const int r = idx / CPR, c = idx - r * CPR;
         const bool valid = r < nvalid;
         const bf16* src = valid ? q + (size_t)tok * q_stride + (size_t)(h0 + r) * HD + c * 8 : q;
         cp_async16(Qs + (size_t)r * LDS + c * 8, src, valid);
     }
-    for (int i = tid; i < (st1 - st0 + 1) * BN; i += NTHREADS)
-        s_rows[i] = cache_row(table, max_blocks, st0 * BN + i, c0, pos, kvh, nkv, page_size, num_pages, err);
-    __syncthreads();
+    __syncthreads();                                             // s_rows
     auto load_stage = [&](int st, int buf) {
         bf16* kt = ring + (size_t)buf * 2 * BN * LDS;
         load_kv_tiles(kt, kt + BN * LDS, kcache, vcache, s_rows + (st - st0) * BN, BN);

@@ -148,11 +148,11 @@ qk_norm_rope_write_kernel(
     const int head_lo = blockIdx.y * heads_per_block;
     const int head_hi = min(nq + 2 * nkv, head_lo + heads_per_block);
     const int half = rot / 2;
-    pdl_wait();
-    if (inv_freq) {
+    if (inv_freq) {                                  // positions are part of the step's description: no wait needed
         const float pos = (float)positions[t];
         for (int i = threadIdx.x; i < half; i += ROPE_THREADS) sincosf(pos * inv_freq[i], &s_sin[i], &s_cos[i]);
     }
+    pdl_wait();                                      // qkv comes from the kernel before
     __syncthreads();
     const int slot = slots ? slots[t] : -1;
     bool slot_ok = slot >= 0;
@@ -238,11 +238,11 @@ qk_norm_rope_write_wide_kernel(
     const int half = hd / 2;
     const int lph = hd / 16, hpw = 32 / lph;                      // lanes per head, heads per warp
     const int nheads = nq + 2 * nkv;
-    pdl_wait();
-    if (inv_freq) {
+    if (inv_freq) {                                  // positions are part of the step's description: no wait needed
         const float pos = (float)positions[t];
         for (int i = threadIdx.x; i < half; i += ROPE_THREADS) sincosf(pos * inv_freq[i], &s_sin[i], &s_cos[i]);
     }
+    pdl_wait();                                      // qkv comes from the kernel before
     __syncthreads();
     const int slot = slots ? slots[t] : -1;
     bool slot_ok = slot >= 0;
