@@ -363,7 +363,8 @@ def test_paged_attention_ragged(kernel, dtype, nq, nkv, hd, page, window):
             ops().flash_decode(qkv, out, kc, vc, table, torch.tensor(req, dtype=torch.int32, device=DEV),
                                torch.tensor(pos, dtype=torch.int32, device=DEV), nq, nkv, hd, scale, window, ctx,
                                torch.full((n_acc,), float("nan"), device=DEV), torch.full((n_ml,), float("nan"), device=DEV),
-                               e, chunk=64, token_index=torch.tensor(single, dtype=torch.int32, device=DEV))
+                               e, chunk=64, token_index=torch.tensor(single, dtype=torch.int32, device=DEV),
+                               arrivals=torch.zeros(ops().flash_decode_arrivals(len(single), nq, nkv), dtype=torch.int32, device=DEV))
     else:
         ops().paged_attention(qkv, out, kc, vc, table, torch.tensor(req, dtype=torch.int32, device=DEV),
                               torch.tensor(pos, dtype=torch.int32, device=DEV), nq, nkv, hd, scale, window, e)
@@ -428,16 +429,23 @@ def run_attention(kernel, qkv, out, kc, vc, table, req, pos, nq, nkv, hd, scale,
     pa = torch.full((n_acc,), float("nan"), device=DEV)
     pm = torch.full((n_ml,), float("nan"), device=DEV)
     if kernel.startswith("flash_decode"):       # "flash_decode", "flash_decode64", "flash_decode1024": the chunk size;
-        stream = kernel.endswith("tma")         # "...tma": the persistent TMA kernel, else a block per chunk
-        kernel = kernel[:-3] if stream else kernel
+        stream = kernel.endswith("tma")         # "...tma": the persistent TMA kernel, else a block per chunk;
+        own = kernel.endswith("own")            # "...own": the chunks are merged by the kernel's last block
+        kernel = kernel[:-3] if stream or own else kernel
         if stream and not ops().flash_tc5_supported(qkv.dtype, hd, kc.shape[2]):
             pytest.skip("the TMA kernel does not take this head or page size")
         chunk = int(kernel[len("flash_decode"):] or 256)
         S, n_acc, n_ml = ops().decode_attention_scratch(qkv.shape[0], nq, hd, ctx, chunk)
         pa = torch.full((n_acc,), float("nan"), device=DEV)
         pm = torch.full((n_ml,), float("nan"), device=DEV)
+        arrivals = torch.zeros(ops().flash_decode_arrivals(qkv.shape[0], nq, nkv), dtype=torch.int32, device=DEV) if own else None
+        if own:                                 # a launch before this one has left the counters as it must
+            ops().flash_decode(qkv, torch.empty_like(out), kc, vc, table, req, pos, nq, nkv, hd, scale, window, ctx, pa, pm, e,
+                               chunk=chunk, stream_kernel=False, arrivals=arrivals)
+            assert int(arrivals.abs().sum()) == 0
+            pa.fill_(float("nan")); pm.fill_(float("nan"))
         return ops().flash_decode(qkv, out, kc, vc, table, req, pos, nq, nkv, hd, scale, window, ctx, pa, pm, e, chunk=chunk,
-                                  stream_kernel=stream)
+                                  stream_kernel=stream, arrivals=arrivals)
     return ops().decode_attention(qkv, out, kc, vc, table, req, pos, nq, nkv, hd, scale, window, ctx, pa, pm, e)
 
 
@@ -445,6 +453,7 @@ def attention_cases():
     """(kernel, dtype): the tensor-core kernels exist in bfloat16 only."""
     return [("paged", torch.float32), ("paged", torch.bfloat16), ("decode", torch.float32), ("decode", torch.bfloat16),
             ("flash_decode", torch.bfloat16), ("flash_decode64", torch.bfloat16), ("flash_decode1024", torch.bfloat16),
+            ("flash_decodeown", torch.bfloat16), ("flash_decode64own", torch.bfloat16), ("flash_decode1024own", torch.bfloat16),
             ("flash_decodetma", torch.bfloat16), ("flash_decode64tma", torch.bfloat16), ("flash_decode1024tma", torch.bfloat16),
             ("flash_prefill", torch.bfloat16)]
 

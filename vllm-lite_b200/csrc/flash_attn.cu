@@ -294,7 +294,7 @@ flash_decode_kernel(const bf16* __restrict__ q, int q_stride,
                     const int* __restrict__ req_index, const int* __restrict__ positions,
                     int nq, int nkv, int page_size, int num_pages, float scale_log2, int window,
                     int chunk, int S, float* __restrict__ part_acc, float* __restrict__ part_ml, unsigned* err,
-                    const int* __restrict__ token_index) {
+                    const int* __restrict__ token_index, bf16* __restrict__ out, int* __restrict__ arrivals) {
     extern __shared__ __align__(128) unsigned char fa_smem[];
     bf16* Qs = reinterpret_cast<bf16*>(fa_smem);                 // [16][LDS]
     bf16* ring = Qs + DEC_ROWS * LDS;                            // [NST][2][BN][LDS]
@@ -312,12 +312,19 @@ flash_decode_kernel(const bf16* __restrict__ q, int q_stride,
     const int h0 = kvh * grp + htile * DEC_ROWS;
     const int nvalid = min(DEC_ROWS, grp - htile * DEC_ROWS);
     const int pos = positions[tok];
-    if (pos < 0) return;
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, t = lane & 3;
+    if (pos < 0) {                                               // a place of the batch that holds no request
+        if (arrivals && split == 0) {
+            pdl_wait();                                          // earlier kernels may still read the rows
+            for (int i = tid; i < nvalid * HD; i += NTHREADS)
+                out[((size_t)tok * nq + h0 + i / HD) * HD + i % HD] = __float2bfloat16(0.f);
+        }
+        return;
+    }
     const int lo = (window > 0 && pos - window + 1 > 0) ? pos - window + 1 : 0;
     const int c0 = max(split * chunk, lo);
     const int c1 = min((split + 1) * chunk, pos + 1);
     if (c0 >= c1) return;
-    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, t = lane & 3;
     const int* table = block_table + (size_t)req_index[tok] * max_blocks;
     const int st0 = c0 / BN, st1 = (c1 - 1) / BN;
 
@@ -448,20 +455,55 @@ flash_decode_kernel(const bf16* __restrict__ q, int q_stride,
             part_ml[row * 2 + 1] = L;
         }
     }
+    if (!arrivals) return;                                       // the caller merges with a kernel of its own
+    // The block that arrives last among those of this token and these heads merges their partial
+    // results (in the order of the chunks, whoever it is: the result does not depend on the order of
+    // arrival) and writes the output rows.
+    __shared__ int s_last;
+    const int sp0 = lo / chunk, sp1 = pos / chunk;               // the chunks that hold keys of this token
+    __threadfence();
+    __syncthreads();
+    if (tid == 0) {
+        int* counter = arrivals + (size_t)blockIdx.z * gridDim.y + blockIdx.y;
+        const int last = atomicAdd(counter, 1) == sp1 - sp0;
+        if (last) *counter = 0;                                  // zero again for the next launch
+        s_last = last;
+    }
+    __syncthreads();
+    if (!s_last) return;
+    __threadfence();
+    for (int idx = tid; idx < nvalid * HD; idx += NTHREADS) {
+        const int r = idx / HD, e = idx - r * HD;
+        const size_t row0 = ((size_t)blockIdx.z * nq + (h0 + r)) * S;
+        float M = -INFINITY;
+        for (int sp = sp0; sp <= sp1; ++sp) M = fmaxf(M, __ldcg(part_ml + (row0 + sp) * 2));
+        float L = 0.f, acc = 0.f;
+        for (int sp = sp0; sp <= sp1; ++sp) {
+            const float ms = __ldcg(part_ml + (row0 + sp) * 2);
+            if (ms == -INFINITY) continue;
+            const float wgt = __expf(ms - M);
+            L += __ldcg(part_ml + (row0 + sp) * 2 + 1) * wgt;
+            acc += __ldcg(part_acc + (row0 + sp) * HD + e) * wgt;
+        }
+        out[((size_t)tok * nq + h0 + r) * HD + e] = __float2bfloat16(acc * (L > 0.f ? 1.0f / L : 0.f));
+    }
 }
 
 // Scratch as for vl_decode_attention: part_acc [T, nq, S, hd], part_ml [T, nq, S, 2] float32,
-// S = ceil(max_context / chunk); follow with vl_decode_attention_merge.  T counts the tokens served: all
-// tokens of the step, or those that token_index (T entries) names.
+// S = ceil(max_context / chunk).  T counts the tokens served: all tokens of the step, or those that
+// token_index (T entries) names.  With out (bfloat16 [tokens of the step, nq * hd]) and arrivals (int32,
+// T * nkv * ceil(group / 16) counters, zero before the first launch and left zero by every launch) the
+// kernel merges the chunks itself; with both null, follow with vl_decode_attention_merge.
 extern "C" int vl_flash_decode(const void* q, int q_stride, const void* kcache, const void* vcache,
                                const int* block_table, int max_blocks, const int* req_index, const int* positions,
                                int T, int nq, int nkv, int hd, int page_size, int num_pages, float scale, int window,
                                int chunk, int S, float* part_acc, float* part_ml, unsigned* err,
-                               const int* token_index, void* stream) {
+                               const int* token_index, void* out, int* arrivals, void* stream) {
     if (T <= 0) return VL_OK;
     if (hd != HD) return VL_ERR_UNSUPPORTED;
     if (nq <= 0 || nkv <= 0 || nq % nkv || page_size <= 0 || max_blocks <= 0 || q_stride % 8) return VL_ERR_ARGUMENT;
     if (chunk <= 0 || chunk % BN || chunk > DEC_MAX_CHUNK || S <= 0 || S > 65535 || T > 65535) return VL_ERR_ARGUMENT;
+    if ((out == nullptr) != (arrivals == nullptr)) return VL_ERR_ARGUMENT;
     const int grp = nq / nkv;
     const int htiles = (grp + DEC_ROWS - 1) / DEC_ROWS;
     const size_t ring = (size_t)DEC_NST * 2 * BN * LDS * sizeof(bf16);
@@ -472,5 +514,5 @@ extern "C" int vl_flash_decode(const void* q, int q_stride, const void* kcache, 
     return vl_launch(flash_decode_kernel, dim3(S, nkv * htiles, T), dim3(NTHREADS), smem, (cudaStream_t)stream,
                      (const bf16*)q, q_stride, (const bf16*)kcache, (const bf16*)vcache, block_table, max_blocks,
                      req_index, positions, nq, nkv, page_size, num_pages, scale * 1.4426950408889634f, window, chunk, S,
-                     part_acc, part_ml, err, token_index);
+                     part_acc, part_ml, err, token_index, (bf16*)out, arrivals);
 }

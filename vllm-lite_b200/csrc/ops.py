@@ -53,7 +53,7 @@ _SIGNATURES = {
                                             c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_void_p, c_void_p],
     ("flash_attn", "vl_flash_decode"): [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p,
                                         c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_int, c_int,
-                                        c_void_p, c_void_p, c_void_p, c_void_p, c_void_p],
+                                        c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p],
     ("flash_decode_tma", "vl_flash_decode_tma"): [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p,
                                                   c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_int, c_int,
                                                   c_void_p, c_void_p, c_void_p, c_void_p, c_void_p],
@@ -328,13 +328,21 @@ def flash_prefill_tc5(qkv, out, k_cache, v_cache, block_table, tiles, num_heads,
     return out
 
 
+def flash_decode_arrivals(num_tokens, num_heads, num_kv_heads) -> int:
+    """Counters (int32) that `flash_decode` needs in `arrivals` for this many tokens."""
+    return num_tokens * num_kv_heads * -(-(num_heads // num_kv_heads) // 16)
+
+
 def flash_decode(qkv, out, k_cache, v_cache, block_table, req_index, positions, num_heads, num_kv_heads,
                  head_dim, scale, window, max_context, part_acc, part_ml, err, chunk=DECODE_CHUNK, token_index=None,
-                 stream_kernel=None):
-    """Tensor-core version of `decode_attention` (bfloat16): the split pass, then the merge.
+                 stream_kernel=None, arrivals=None):
+    """Tensor-core version of `decode_attention` (bfloat16): every block takes a chunk of a token's
+    keys; the chunks are merged by the block that finishes last (`arrivals`: int32 counters,
+    `flash_decode_arrivals` of them, zero before the first call and left zero) or, without
+    `arrivals`, by a second kernel.
     The split pass is the persistent TMA kernel where it takes the head size and pages hold at
-    least 64 positions (`stream_kernel`: None = that rule, True / False to force), else a block
-    per chunk.
+    least 64 positions (`stream_kernel`: None = that rule, True / False to force; it always merges
+    with the second kernel), else a block per chunk.
     `token_index` (int32) restricts the launch to some tokens of the step (the others' rows of `out`
     are left alone); the scratch is then sized for that many tokens."""
     _flash_checks(qkv, k_cache, v_cache, block_table, num_heads, num_kv_heads, head_dim)
@@ -352,13 +360,20 @@ def flash_decode(qkv, out, k_cache, v_cache, block_table, req_index, positions, 
         raise KernelError(f"flash_decode: scratch too small ({part_acc.numel()} < {need_acc})")
     if stream_kernel is None:           # measured: it wins from 64-position pages on (TMA boxes of 8 KB, not 2 KB)
         stream_kernel = flash_tc5_supported(qkv.dtype, head_dim, k_cache.shape[2]) and k_cache.shape[2] >= 64
-    split = (_fn("flash_decode_tma", "vl_flash_decode_tma", {"FA_HD": head_dim}) if stream_kernel
-             else _fn("flash_attn", "vl_flash_decode", {"FA_HD": head_dim}))
-    _check(split(
-        _ptr(qkv), qkv.shape[1], _ptr(k_cache), _ptr(v_cache), _ptr(block_table), block_table.shape[1],
-        _ptr(req_index), _ptr(positions), T, num_heads, num_kv_heads, head_dim, k_cache.shape[2], k_cache.shape[0],
-        float(scale), int(window or 0), chunk, S, _ptr(part_acc), _ptr(part_ml), _ptr(err), _ptr(token_index),
-        _stream()), "vl_flash_decode")
+    args = (_ptr(qkv), qkv.shape[1], _ptr(k_cache), _ptr(v_cache), _ptr(block_table), block_table.shape[1],
+            _ptr(req_index), _ptr(positions), T, num_heads, num_kv_heads, head_dim, k_cache.shape[2], k_cache.shape[0],
+            float(scale), int(window or 0), chunk, S, _ptr(part_acc), _ptr(part_ml), _ptr(err), _ptr(token_index))
+    if stream_kernel:
+        _check(_fn("flash_decode_tma", "vl_flash_decode_tma", {"FA_HD": head_dim})(*args, _stream()), "vl_flash_decode_tma")
+    else:
+        if arrivals is not None:
+            _need(arrivals, torch.int32, "arrivals", 1)
+            if arrivals.numel() < flash_decode_arrivals(T, num_heads, num_kv_heads):
+                raise KernelError("flash_decode: too few arrival counters")
+        _check(_fn("flash_attn", "vl_flash_decode", {"FA_HD": head_dim})(
+            *args, _ptr(out) if arrivals is not None else None, _ptr(arrivals), _stream()), "vl_flash_decode")
+        if arrivals is not None:
+            return out
     _check(_fn("attention", "vl_decode_attention_merge")(
         _ptr(part_acc), _ptr(part_ml), _ptr(positions), _ptr(out), dtype_code(out.dtype), T, num_heads, head_dim,
         chunk, S, int(window or 0), _ptr(token_index), _stream()), "vl_decode_attention_merge")

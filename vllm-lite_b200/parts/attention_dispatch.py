@@ -23,7 +23,11 @@ def _decode(ops, args, step, spec, group, num_tokens, max_context, token_index=N
     S, n_acc, n_ml = ops.decode_attention_scratch(num_tokens, spec.num_heads, spec.head_dim, max_context, chunk)
     part_acc = step.workspace.get(step.tag + "attn.part_acc", (n_acc,), torch.float32)
     part_ml = step.workspace.get(step.tag + "attn.part_ml", (n_ml,), torch.float32)
-    return ops.flash_decode(*args, max_context, part_acc, part_ml, step.err, chunk=chunk, token_index=token_index)
+    # one set of counters for all layers of a step shape: every launch leaves them zero
+    arrivals = step.workspace.zeros(step.tag + "attn.arrivals", ops.flash_decode_arrivals(num_tokens, spec.num_heads, spec.num_kv_heads),
+                                    torch.int32)
+    return ops.flash_decode(*args, max_context, part_acc, part_ml, step.err, chunk=chunk, token_index=token_index,
+                            arrivals=arrivals)
 
 
 def run(qkv, out, cache, group, step, spec, scale):

@@ -54,6 +54,16 @@ class Workspace:
             self._buffers[key] = buf
         return buf[:n].view(*shape)
 
+    def zeros(self, tag: str, n: int, dtype) -> torch.Tensor:
+        """A buffer that is zero when first handed out and that its users leave zero (counters that
+        the kernels reset themselves); it only grows."""
+        key = (tag, dtype, "zeros")
+        buf = self._buffers.get(key)
+        if buf is None or buf.numel() < n:
+            buf = torch.zeros(max(n, 1), dtype=dtype, device=self.device)
+            self._buffers[key] = buf
+        return buf
+
     def bytes(self) -> int:
         return sum(b.numel() * b.element_size() for b in self._buffers.values())
 
