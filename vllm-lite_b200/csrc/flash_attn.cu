@@ -472,21 +472,50 @@ flash_decode_kernel(const bf16* __restrict__ q, int q_stride,
     __syncthreads();
     if (!s_last) return;
     __threadfence();
+    // Weights of the chunks first (8 threads per row share the chunks out, maximum and sum by a fixed
+    // butterfly), into the shared memory that held the keys; then every thread adds up its elements
+    // over the chunks with the loads of several chunks in flight.
+    float* s_w = reinterpret_cast<float*>(ring);                 // [DEC_ROWS][nsp]
+    float* s_inv = s_l[0];                                       // [DEC_ROWS]: 1 / sum of a row
+    const int nsp = sp1 - sp0 + 1;
+    {
+        const int r = tid >> 3, part = tid & 7;                  // 128 threads = 16 rows x 8
+        const size_t row0 = ((size_t)blockIdx.z * nq + (h0 + min(r, nvalid - 1))) * S + sp0;
+        float M = -INFINITY;
+        for (int i = part; i < nsp; i += 8) M = fmaxf(M, __ldcg(part_ml + (row0 + i) * 2));
+        M = fmaxf(M, __shfl_xor_sync(0xffffffffu, M, 1));
+        M = fmaxf(M, __shfl_xor_sync(0xffffffffu, M, 2));
+        M = fmaxf(M, __shfl_xor_sync(0xffffffffu, M, 4));
+        float L = 0.f;
+        for (int i = part; i < nsp; i += 8) {
+            const float ms = __ldcg(part_ml + (row0 + i) * 2);
+            const float wgt = (ms == -INFINITY) ? 0.f : __expf(ms - M);
+            L += __ldcg(part_ml + (row0 + i) * 2 + 1) * wgt;
+            s_w[r * nsp + i] = wgt;
+        }
+        L += __shfl_xor_sync(0xffffffffu, L, 1);
+        L += __shfl_xor_sync(0xffffffffu, L, 2);
+        L += __shfl_xor_sync(0xffffffffu, L, 4);
+        if (part == 0) s_inv[r] = L > 0.f ? 1.0f / L : 0.f;
+    }
+    __syncthreads();
     for (int idx = tid; idx < nvalid * HD; idx += NTHREADS) {
         const int r = idx / HD, e = idx - r * HD;
-        const size_t row0 = ((size_t)blockIdx.z * nq + (h0 + r)) * S;
-        float M = -INFINITY;
-        for (int sp = sp0; sp <= sp1; ++sp) M = fmaxf(M, __ldcg(part_ml + (row0 + sp) * 2));
-        float L = 0.f, acc = 0.f;
-        for (int sp = sp0; sp <= sp1; ++sp) {
-            const float ms = __ldcg(part_ml + (row0 + sp) * 2);
-            if (ms == -INFINITY) continue;
-            const float wgt = __expf(ms - M);
-            L += __ldcg(part_ml + (row0 + sp) * 2 + 1) * wgt;
-            acc += __ldcg(part_acc + (row0 + sp) * HD + e) * wgt;
-        }
-        out[((size_t)tok * nq + h0 + r) * HD + e] = __float2bfloat16(acc * (L > 0.f ? 1.0f / L : 0.f));
+        const float* pa = part_acc + (((size_t)blockIdx.z * nq + (h0 + r)) * S + sp0) * HD + e;
+        const float* w = s_w + r * nsp;
+        float acc = 0.f;
+#pragma unroll 8
+        for (int i = 0; i < nsp; ++i) acc += __ldcg(pa + (size_t)i * HD) * w[i];
+        out[((size_t)tok * nq + h0 + r) * HD + e] = __float2bfloat16(acc * s_inv[r]);
     }
+}
+
+// Most chunks per token that vl_flash_decode merges itself: their weights, for 16 rows, have to fit the
+// shared memory that held the keys.
+extern "C" int vl_flash_decode_own_merge_cap() {
+    const size_t ring = (size_t)DEC_NST * 2 * BN * LDS * sizeof(bf16);
+    const size_t merge = (size_t)4 * DEC_ROWS * (HD + 4) * sizeof(float);
+    return (int)((ring > merge ? ring : merge) / (DEC_ROWS * sizeof(float)));
 }
 
 // Scratch as for vl_decode_attention: part_acc [T, nq, S, hd], part_ml [T, nq, S, 2] float32,
@@ -504,6 +533,7 @@ extern "C" int vl_flash_decode(const void* q, int q_stride, const void* kcache, 
     if (nq <= 0 || nkv <= 0 || nq % nkv || page_size <= 0 || max_blocks <= 0 || q_stride % 8) return VL_ERR_ARGUMENT;
     if (chunk <= 0 || chunk % BN || chunk > DEC_MAX_CHUNK || S <= 0 || S > 65535 || T > 65535) return VL_ERR_ARGUMENT;
     if ((out == nullptr) != (arrivals == nullptr)) return VL_ERR_ARGUMENT;
+    if (arrivals && S > vl_flash_decode_own_merge_cap()) return VL_ERR_UNSUPPORTED;
     const int grp = nq / nkv;
     const int htiles = (grp + DEC_ROWS - 1) / DEC_ROWS;
     const size_t ring = (size_t)DEC_NST * 2 * BN * LDS * sizeof(bf16);

@@ -328,6 +328,17 @@ def flash_prefill_tc5(qkv, out, k_cache, v_cache, block_table, tiles, num_heads,
     return out
 
 
+_merge_caps = {}
+
+
+def _own_merge_cap(head_dim) -> int:
+    """Most chunks per token that `vl_flash_decode` of this head size merges itself."""
+    cap = _merge_caps.get(head_dim)
+    if cap is None:
+        cap = _merge_caps[head_dim] = int(build.load("flash_attn", {"FA_HD": head_dim}).vl_flash_decode_own_merge_cap())
+    return cap
+
+
 def flash_decode_arrivals(num_tokens, num_heads, num_kv_heads) -> int:
     """Counters (int32) that `flash_decode` needs in `arrivals` for this many tokens."""
     return num_tokens * num_kv_heads * -(-(num_heads // num_kv_heads) // 16)
@@ -366,6 +377,8 @@ def flash_decode(qkv, out, k_cache, v_cache, block_table, req_index, positions, 
     if stream_kernel:
         _check(_fn("flash_decode_tma", "vl_flash_decode_tma", {"FA_HD": head_dim})(*args, _stream()), "vl_flash_decode_tma")
     else:
+        if arrivals is not None and S > _own_merge_cap(head_dim):
+            arrivals = None
         if arrivals is not None:
             _need(arrivals, torch.int32, "arrivals", 1)
             if arrivals.numel() < flash_decode_arrivals(T, num_heads, num_kv_heads):
