@@ -436,6 +436,7 @@ flash_decode_kernel(const bf16* __restrict__ q, int q_stride,
         s_m[warp][g + 8] = m_run[1]; s_l[warp][g + 8] = l_run[1];
     }
     __syncthreads();
+    const bool alone = arrivals && lo / chunk == pos / chunk;    // this chunk holds all the keys of the token
     for (int idx = tid; idx < nvalid * HD; idx += NTHREADS) {
         const int r = idx / HD, e = idx - r * HD;
         float M = -INFINITY;
@@ -448,6 +449,10 @@ flash_decode_kernel(const bf16* __restrict__ q, int q_stride,
             acc += sO[((size_t)w * DEC_ROWS + r) * OLD + e] * wgt;
             L += s_l[w][r] * wgt;
         }
+        if (alone) {                                             // nothing to merge with: the output row itself
+            out[((size_t)tok * nq + h0 + r) * HD + e] = __float2bfloat16(acc * (L > 0.f ? 1.0f / L : 0.f));
+            continue;
+        }
         const size_t row = ((size_t)blockIdx.z * nq + (h0 + r)) * S + split;
         part_acc[row * HD + e] = acc;
         if (e == 0) {
@@ -455,7 +460,7 @@ flash_decode_kernel(const bf16* __restrict__ q, int q_stride,
             part_ml[row * 2 + 1] = L;
         }
     }
-    if (!arrivals) return;                                       // the caller merges with a kernel of its own
+    if (!arrivals || alone) return;                              // (no arrivals: the caller merges with a kernel of its own)
     // The block that arrives last among those of this token and these heads merges their partial
     // results (in the order of the chunks, whoever it is: the result does not depend on the order of
     // arrival) and writes the output rows.
