@@ -1,6 +1,7 @@
 """Decode and prefill throughput of the engine at Qwen3-8B layer sizes on one B200.
 
     python bench.py [--gpus 1] [--steps K] [--warmup W] [--batch 8] [--context 4096] [--layers 36]
+    python bench.py --size 14b --context 8192 --continuous 32      (continuous batching, a line of its own)
 
 Prints ONE JSON line.  `value` is decoded tokens per second of K decode steps at the
 given batch, timed on the device with CUDA events (weights, 16 GB, are far larger than
@@ -190,6 +191,43 @@ def e2e_run(engine, batch, context, warmup, steps, vocab):
     return produced / dt, h2d, 4 * batch
 
 
+def continuous_run(engine, requests, vocab, prompt_range, out_len):
+    """Continuous batching through LLMEngine: all requests arrive at once with prompts of seeded
+    uniform length, each generates `out_len` tokens.  Wall clock around the whole run, host token
+    ids in and out.  Returns the figures of the JSON line."""
+    import random
+    import torch
+    rng = random.Random(0)
+    gen = torch.Generator().manual_seed(0)
+    prompts = [torch.randint(0, vocab, (rng.randint(*prompt_range),), generator=gen).tolist() for _ in range(requests)]
+    torch.cuda.synchronize()
+    t0 = time.perf_counter()
+    for p in prompts:
+        engine.add_request(p, out_len)
+    kinds = {"prompt": [0, 0.0], "mixed": [0, 0.0], "decode": [0, 0.0]}
+    produced = 0
+    before = dict(engine.scheduler.stats)
+    while engine.has_unfinished():
+        s0 = time.perf_counter()
+        produced += len(engine.step())
+        now = dict(engine.scheduler.stats)
+        pre, dec = now["prefill_tokens"] - before["prefill_tokens"], now["decode_tokens"] - before["decode_tokens"]
+        kind = "mixed" if pre and dec else "prompt" if pre else "decode"
+        kinds[kind][0] += 1
+        kinds[kind][1] += time.perf_counter() - s0
+        before = now
+    torch.cuda.synchronize()
+    dt = time.perf_counter() - t0
+    engine.runner.check_device_errors()
+    prompt_tokens = sum(len(p) for p in prompts)
+    return {"value": round(produced / dt, 1), "unit": "generated tokens/s", "requests": requests,
+            "prompt_tokens": prompt_tokens, "generated_tokens": produced, "seconds": round(dt, 3),
+            "all_tokens_per_s": round((prompt_tokens + produced) / dt, 1),
+            "steps": {k: v[0] for k, v in kinds.items()},
+            "ms_per_step": {k: round(v[1] / v[0] * 1e3, 3) if v[0] else None for k, v in kinds.items()},
+            "preemptions": engine.scheduler.stats["preemptions"]}
+
+
 def main(argv=None):
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -205,6 +243,9 @@ def main(argv=None):
     ap.add_argument("--no-e2e", action="store_true", help="skip the run through the Python entry point (for profiling)")
     ap.add_argument("--kv-fill", default="prefill", choices=["prefill", "random"],
                     help="what the cache holds before decoding: what real prompts leave, or random numbers (for profiling)")
+    ap.add_argument("--continuous", type=int, default=0, metavar="REQUESTS",
+                    help="instead of the decode steps: continuous batching of this many requests through LLMEngine, prompts "
+                         "uniform in [256, context/2], 512 generated tokens each (steps and warmup are not used)")
     args = ap.parse_args(argv)
     if args.impl == "reference":
         return reference_arm()
@@ -223,6 +264,26 @@ def main(argv=None):
                intermediate_size=inter)
     vocab = cfg["vocab_size"]
     _, plan, weights = random_model(cfg, seed=0, dtype="bfloat16", device="cuda:0")
+    if args.continuous:
+        R, out_len, prompt_range = args.continuous, 512, (256, args.context // 2)
+        pages = R * (-(-(prompt_range[1] + out_len) // 16) + 1) + 64
+        engine = LLMEngine(plan=plan, weights=weights, dtype="bfloat16", kv_blocks=pages, block_size=16, max_batch_size=R,
+                           max_num_batched_tokens=4096, prefill_chunk_size=512, max_model_len=args.context)
+        del weights
+        continuous_run(engine, min(R, 4), vocab, (256, 512), 16)          # warm-up: builds, graphs of the small buckets
+        clocks = ClockSampler().start()
+        w0 = time.time()
+        out = continuous_run(engine, R, vocab, prompt_range, out_len)
+        clocks.stop()
+        out = {"metric": f"continuous batching, generated tok/s (Qwen3-{args.size.upper()}, bf16)", **out, "n_gpus": 1,
+               "dtype": "bf16", "data": "synthetic (random weights N(0,0.02), uniform token ids)",
+               "config": {"model": f"Qwen3-{args.size.upper()} layer sizes", "layers": args.layers, "layers_full": full_layers,
+                          "context": args.context, "prompt_lengths": f"uniform in [{prompt_range[0]}, {prompt_range[1]}]",
+                          "generated_each": out_len, "block_size": 16, "max_num_batched_tokens": 4096,
+                          "prefill_chunk_size": 512, "timing": "wall clock around the whole run, host ids in and out"},
+               "clocks": clocks.summary(w0, time.time())}
+        print(json.dumps(out))
+        return 0
     big = args.batch if args.no_points else max(args.batch, 64)
     pages = big * (-(-args.context // 16) + 1) + PREFILL_TOKENS // 16 + 64
     engine = LLMEngine(plan=plan, weights=weights, dtype="bfloat16", kv_blocks=pages, block_size=16, max_batch_size=big,

@@ -125,7 +125,7 @@ def test_steps_launched_ahead_change_nothing_but_the_timing(dtype):
             steps += 1
             if steps == 5:
                 ids.append(eng.add_request(prompts[3], 30))
-            if len(ids) == 4 and len(got.get(ids[3], [])) == 6 and eng.sequences[ids[3]].status == "running":
+            if len(ids) == 4 and len(got.get(ids[3], [])) == 6 and ids[3] in eng.sequences and eng.sequences[ids[3]].status == "running":
                 eng.cancel_request(ids[3])
         eng.runner.check_device_errors()
         eng.runner.cache.check_invariants()

@@ -73,14 +73,24 @@ __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;"
 __device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 
 #include <cstdlib>
-static inline bool vl_pdl_enabled() {
-    static int on = -1;
-    if (on < 0) {
-        const char* v = getenv("VLLM_LITE_B200_PDL");        // "0" turns dependent launches off
-        on = (v && v[0] == '0') ? 0 : 1;
-    }
-    return on == 1;
+// -1: not decided yet.  The environment's VLLM_LITE_B200_PDL=0 turns dependent launches off for good;
+// otherwise they are on until vl_set_pdl says otherwise.
+static int g_vl_pdl = -1;
+static inline bool vl_pdl_forbidden() {
+    const char* v = getenv("VLLM_LITE_B200_PDL");
+    return v && v[0] == '0';
 }
+static inline bool vl_pdl_enabled() {
+    if (g_vl_pdl < 0) g_vl_pdl = vl_pdl_forbidden() ? 0 : 1;
+    return g_vl_pdl == 1;
+}
+// The engine launches the kernels of a step of few tokens with the attribute (their launch gaps are
+// what it hides) and those of a step of many tokens without it.  Steps of a thousand tokens and more,
+// whose products run as clusters of two blocks on the tcgen05 kernels, stopped on the device now and
+// then with the attribute on every launch (about once in a few hundred launches of the paired
+// product at 1,588 or 4,096 rows; never without the attribute); the cause is not known, and what
+// the attribute hides there is a few microseconds beside kernels of a hundred.
+extern "C" void vl_set_pdl(int on) { g_vl_pdl = (on && !vl_pdl_forbidden()) ? 1 : 0; }
 
 template <typename... KArgs, typename... Args>
 static inline int vl_launch(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,

@@ -77,11 +77,32 @@ _functions = {}
 launch_count = 0          # kernels of this library launched so far (graph replays add theirs)
 
 
+_pdl = True               # whether launches carry the programmatic-dependent-launch attribute
+_pdl_libs = {}
+
+
+def set_pdl(on: bool):
+    """Launch the kernels that follow with (or without) the attribute that lets a kernel start while
+    the one before it in the stream drains.  Every library holds the switch for its own launches."""
+    global _pdl
+    on = bool(on)
+    if on != _pdl:
+        _pdl = on
+        for setter in _pdl_libs.values():
+            setter(int(on))
+
+
 def _fn(lib: str, name: str, defines=None):
     key = (lib, name, build._variant(defines))
     f = _functions.get(key)
     if f is None:
-        f = getattr(build.load(lib, defines), name)
+        handle = build.load(lib, defines)
+        if key[::2] not in _pdl_libs and hasattr(handle, "vl_set_pdl"):
+            setter = handle.vl_set_pdl
+            setter.argtypes, setter.restype = [c_int], None
+            setter(int(_pdl))
+            _pdl_libs[key[::2]] = setter
+        f = getattr(handle, name)
         f.argtypes = _SIGNATURES[(lib, name)]
         f.restype = c_int
         _functions[key] = f

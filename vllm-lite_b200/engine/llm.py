@@ -80,6 +80,7 @@ class LLMEngine:
         return seq.seq_id
 
     def cancel_request(self, seq_id: int) -> bool:
+        self.sequences.pop(seq_id, None)
         return self.scheduler.cancel(seq_id)
 
     def has_unfinished(self) -> bool:
@@ -177,6 +178,8 @@ class LLMEngine:
             if alive:
                 out.append(StepOutput(e.seq.seq_id, t, e.seq.status == "finished", e.seq.finish_reason,
                                       logprobs[k] if logprobs else None))
+                if e.seq.status == "finished":                       # reported: the engine keeps it no longer
+                    self.sequences.pop(e.seq.seq_id, None)
             k += 1
         return out
 
@@ -185,15 +188,12 @@ class LLMEngine:
         """Generated token ids for every prompt, in the order given."""
         if sampling_params is None or isinstance(sampling_params, SamplingParams):
             sampling_params = [sampling_params] * len(prompts)
-        ids = [self.add_request(p, max_tokens, sp) for p, sp in zip(prompts, sampling_params)]
+        seqs = [self.sequences[self.add_request(p, max_tokens, sp)] for p, sp in zip(prompts, sampling_params)]
         while self.has_unfinished():
             self.step()
         self._ahead = None                      # at most a step launched ahead for requests that have ended since
         self.runner.check_device_errors()
-        out = [list(self.sequences[i].generated) for i in ids]
-        for i in ids:
-            self.sequences.pop(i, None)
-        return out
+        return [list(seq.generated) for seq in seqs]
 
     def stats(self) -> dict:
         s = dict(self.scheduler.stats)

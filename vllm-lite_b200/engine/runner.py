@@ -39,6 +39,12 @@ _DEVICE_ERRORS = {1: "a token id outside the vocabulary", 2: "a cache slot outsi
                   4: "a block table entry that names no page", 8: "a wait inside a kernel ran out"}
 
 
+# Steps of up to this many tokens launch their kernels with programmatic dependent launch (each kernel's
+# start-up overlaps the end of the one before: what a step of few tokens spends between kernels); longer
+# steps, whose kernels run for tens of microseconds and more, are launched the plain way (csrc/common.cuh).
+PDL_MAX_TOKENS = 64
+
+
 def _align4(n: int) -> int:
     return (n + 3) & ~3
 
@@ -124,6 +130,8 @@ class ModelRunner:
         if batch.graph_bucket:
             logits = self._forward_graph(batch)[:sum(len(e.want) for e in entries)]
         else:
+            from ..csrc import ops
+            ops.set_pdl(batch.num_tokens <= PDL_MAX_TOKENS)
             logits = self.model.forward(batch, self.storage.call_caches)
         self.finish(batch)
         return logits
@@ -213,9 +221,10 @@ class ModelRunner:
         entry = self._graphs.get(key)
         if entry is None:
             # first sight of this bucket: run it as it is (also sizes the workspace), then record
+            from ..csrc import ops
+            ops.set_pdl(True)                          # a decode step: one token a request
             logits = self.model.forward(batch, self.storage.call_caches)
             torch.cuda.current_stream().synchronize()
-            from ..csrc import ops
             before = ops.launch_count
             graph = torch.cuda.CUDAGraph()
             with torch.cuda.graph(graph):
