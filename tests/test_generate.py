@@ -145,6 +145,27 @@ def test_steps_launched_ahead_change_nothing_but_the_timing(dtype):
         assert ahead[:3] == waited[:3] and ahead[3][:6] == waited[3][:6]
 
 
+def test_long_steps_are_launched_without_dependent_launch():
+    """Steps of few tokens overlap each kernel's start with the end of the one before (programmatic
+    dependent launch); steps of many tokens are launched the plain way.  The switch follows the step."""
+    from vllm_lite_b200.csrc import ops
+    from vllm_lite_b200.engine import StepEntry
+    from vllm_lite_b200.engine.runner import PDL_MAX_TOKENS
+    which = "B"
+    runner = engine(which, dtype="bfloat16").runner
+    long = H.tokens_for(which, PDL_MAX_TOKENS + 6, 300)
+    whole = runner.step([StepEntry("a", long, [len(long) - 1])]).clone()
+    assert ops._pdl is False
+    runner.step([StepEntry("a", [5], [0])])
+    assert ops._pdl is True
+    runner.step([StepEntry("b", long[:10], [])])
+    assert ops._pdl is True
+    cut = runner.step([StepEntry("b", long[10:], [len(long) - 11])])      # 60 tokens, with the attribute
+    runner.check_device_errors()
+    tol = H.TOL["bfloat16"] * float(whole.abs().max())
+    assert float((whole - cut).abs().max()) <= tol
+
+
 def test_command_line(tmp_path):
     which = "A"
     prompt = H.tokens_for(which, 12, 95)

@@ -298,6 +298,9 @@ class ModelRunner:
         if bucket:                                  # a graph reads its batch from a buffer of its own
             dev = self._graph_meta.get(bucket)
             if dev is None or dev.numel() < n:
+                # graphs recorded for this bucket read the old buffer: they are recorded again
+                for key in [k for k in self._graphs if k[0] == bucket]:
+                    del self._graphs[key]
                 dev = self._graph_meta[bucket] = torch.empty(n, dtype=torch.int32, device=self.device)
         else:
             if self._meta_dev is None or self._meta_dev.numel() < n:
