@@ -73,3 +73,20 @@ def test_sampling_functions():
     assert P.temperature_sample(logits, 0.0, 0.3) == 1
     keep = P.top_p_keep([0.0, 3.0, 1.0, 2.0], 0.8)
     assert keep == [1, 3]
+
+
+def test_plain_implementation_reproduces_its_committed_numbers():
+    """tests/golden/plain_tiny.json (written by tests/golden/make_plain_golden.py) pins the oracle and
+    the seeded weights: an edit to either shows here instead of moving every comparison silently."""
+    import json
+    from pathlib import Path
+    golden = json.loads((Path(__file__).resolve().parent / "golden" / "plain_tiny.json").read_text())
+    for which, want in golden.items():
+        cfg, w = H.plain_model(which)
+        assert H.tokens_for(which, len(want["tokens"]), 7) == want["tokens"]
+        logits = P.forward(cfg, w, want["tokens"], dtype=torch.float64)
+        scale = float(logits.abs().max())
+        assert np.allclose(logits[0, :8].numpy(), want["first"], atol=1e-9 * scale, rtol=1e-7)
+        assert np.allclose(logits[-1, :8].numpy(), want["last"], atol=1e-9 * scale, rtol=1e-7)
+        assert math.isclose(float((logits * logits).sum()), want["sum_squares"], rel_tol=1e-9)
+        assert abs(float(logits.sum()) - want["sum"]) <= 1e-9 * scale * logits.numel()
