@@ -234,12 +234,14 @@ __device__ __forceinline__ void bulk_copy_g2s(void* dst, const void* src, unsign
     asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
                  ::"r"(smem_u32(dst)), "l"(src), "r"(bytes), "r"(smem_u32(bar)) : "memory");
 }
-// A wait gives up after this many polls (a fraction of a second): the block then records
-// VL_DEV_WAIT_EXPIRED and leaves instead of hanging the device.
-#define MBAR_SPIN_LIMIT (1 << 22)
+// A wait gives up after a bounded number of polls and of cycles (common.cuh) instead of hanging the device.
 __device__ __forceinline__ bool mbar_wait_bounded(unsigned long long* bar, unsigned parity) {
-    for (int i = 0; i < MBAR_SPIN_LIMIT; ++i)
+    if (mbar_try_wait(bar, parity)) return true;
+    const long long t0 = clock64();
+    for (int i = 0; i < VL_WAIT_POLL_LIMIT; ++i) {
         if (mbar_try_wait(bar, parity)) return true;
+        if (vl_wait_gave_up(i, t0)) return false;
+    }
     return false;
 }
 

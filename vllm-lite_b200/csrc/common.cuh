@@ -61,6 +61,17 @@ __device__ __forceinline__ float block_sum(float v, float* scratch) {
 
 static inline int vl_launch_status() { return (int)cudaGetLastError(); }
 
+// ---- bounded waits ----------------------------------------------------------------------------------
+// A wait on an mbarrier ends after this many polls or this many SM cycles (about two seconds),
+// whichever comes first: one poll may itself be suspended by the hardware for a time that no
+// document bounds, so a count of polls alone does not bound the time.  The block that gave up records
+// VL_DEV_WAIT_EXPIRED, waits (again bounded) for its own copies in flight and leaves.
+#define VL_WAIT_POLL_LIMIT (1 << 22)
+#define VL_WAIT_CYCLE_LIMIT 4000000000ll
+__device__ __forceinline__ bool vl_wait_gave_up(int poll, long long t0) {
+    return (poll & 31) == 31 && clock64() - t0 > VL_WAIT_CYCLE_LIMIT;
+}
+
 // ---- programmatic dependent launch ---------------------------------------------------------------
 // Kernels of a step are launched with the attribute that lets the next kernel of the stream start
 // while this one is still running.  A kernel calls pdl_launch_dependents() at once (the next grid

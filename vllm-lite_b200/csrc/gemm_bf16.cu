@@ -48,11 +48,14 @@ __device__ __forceinline__ bool mbar_try_wait(unsigned long long* bar, unsigned 
         : "=r"(ok) : "r"(smem_u32(bar)), "r"(parity) : "memory");
     return ok != 0;
 }
-// A wait gives up after this many polls (a fraction of a second) instead of hanging the device.
-#define MBAR_SPIN_LIMIT (1 << 22)
+// A wait gives up after a bounded number of polls and of cycles (common.cuh) instead of hanging the device.
 __device__ __forceinline__ bool mbar_wait_bounded(unsigned long long* bar, unsigned parity) {
-    for (int i = 0; i < MBAR_SPIN_LIMIT; ++i)
+    if (mbar_try_wait(bar, parity)) return true;
+    const long long t0 = clock64();
+    for (int i = 0; i < VL_WAIT_POLL_LIMIT; ++i) {
         if (mbar_try_wait(bar, parity)) return true;
+        if (vl_wait_gave_up(i, t0)) return false;
+    }
     return false;
 }
 // Both addresses 16-byte aligned, bytes a multiple of 16.

@@ -6,7 +6,6 @@
 #include <cuda.h>
 
 namespace tc5 {
-constexpr int SPIN_LIMIT = 1 << 22;
 constexpr int SWIZZLE_COLS = 64;             // one 128-byte swizzle row of bfloat16
 
 __device__ __forceinline__ unsigned smem_u32(const void* p) { return (unsigned)__cvta_generic_to_shared(p); }
@@ -28,8 +27,12 @@ __device__ __forceinline__ bool mbar_try_wait(unsigned long long* bar, unsigned 
     return ok != 0;
 }
 __device__ __forceinline__ bool mbar_wait_bounded(unsigned long long* bar, unsigned parity) {
-    for (int i = 0; i < SPIN_LIMIT; ++i)
+    if (mbar_try_wait(bar, parity)) return true;
+    const long long t0 = clock64();
+    for (int i = 0; i < VL_WAIT_POLL_LIMIT; ++i) {
         if (mbar_try_wait(bar, parity)) return true;
+        if (vl_wait_gave_up(i, t0)) return false;
+    }
     return false;
 }
 // x = element index along K (a multiple of 8: the copy starts on a 16-byte boundary), y = row
