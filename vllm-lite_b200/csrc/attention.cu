@@ -345,7 +345,7 @@ decode_attention_split_kernel(const T* __restrict__ q, int q_stride,
         const bool arrived = mbar_wait_bounded(&full_bar[buf], (unsigned)((it / nstages) & 1));
         if (__syncthreads_or(!arrived)) {                 // the copy never came: flag it and leave
             if (tid == 0) {
-                atomicOr(err, VL_DEV_WAIT_EXPIRED);
+                atomicOr(err, VL_DEV_WAIT_EXPIRED | VL_DEV_IN_DECODE_ATTENTION);
                 // give the copies that are still in flight a bounded time to land before the block's
                 // shared memory is handed to another block
                 for (int k = 1; k < nstages && st + k <= st1; ++k)

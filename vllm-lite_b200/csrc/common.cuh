@@ -19,6 +19,17 @@
 #define VL_DEV_BAD_SLOT 2u
 #define VL_DEV_BAD_PAGE 4u
 #define VL_DEV_WAIT_EXPIRED 8u
+// with VL_DEV_WAIT_EXPIRED: the kernel whose wait ran out ...
+#define VL_DEV_IN_DECODE_ATTENTION 0x100u
+#define VL_DEV_IN_GEMM_SMALL_M 0x200u
+#define VL_DEV_IN_GEMM_TC5 0x400u
+#define VL_DEV_IN_GEMM_TC5_PAIR 0x800u
+#define VL_DEV_IN_FLASH_TC5 0x1000u
+#define VL_DEV_IN_FLASH_DECODE_TMA 0x2000u
+// ... and, in the two tcgen05 products, which waits gave up in the block (shifted left by 16):
+// 1 a free stage (copying thread), 2 a free accumulator, 4 a filled stage (both: issuing thread),
+// 8 a complete accumulator (epilogue)
+#define VL_DEV_ROLE_SHIFT 16
 
 // dtype codes shared with csrc/ops.py
 #define VL_F32 0

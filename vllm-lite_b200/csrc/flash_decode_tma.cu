@@ -333,7 +333,7 @@ flash_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_
         if (!ok && lane == 0) atomicExch(&failed, 1);
     }
     __syncthreads();
-    if (tid == 0 && failed && err) atomicOr(err, VL_DEV_WAIT_EXPIRED);
+    if (tid == 0 && failed && err) atomicOr(err, VL_DEV_WAIT_EXPIRED | VL_DEV_IN_FLASH_DECODE_TMA);
 }
 
 extern "C" int vl_flash_decode_tma_head_dim() { return HD; }

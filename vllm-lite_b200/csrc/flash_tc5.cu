@@ -382,7 +382,7 @@ flash_tc5_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constan
     __syncthreads();
     tc5_fence_after();
     if (warp == 5) tc5_dealloc(tmem_base, TMEM_COLS);
-    if (tid == 0 && failed && err) atomicOr(err, VL_DEV_WAIT_EXPIRED);
+    if (tid == 0 && failed && err) atomicOr(err, VL_DEV_WAIT_EXPIRED | VL_DEV_IN_FLASH_TC5);
 }
 
 extern "C" int vl_flash_tc5_head_dim() { return HD; }

@@ -123,7 +123,7 @@ gemm_bf16_small_m_kernel(const bf16* __restrict__ A, const bf16* __restrict__ W,
                         if (lane == 0) ok = mbar_wait_bounded(&empty_bar[s], (unsigned)((git / GS_STAGES - 1) & 1)) ? 1 : 0;
                         ok = __shfl_sync(0x0000ffffu, ok, 0);
                         if (!ok) {
-                            if (lane == 0 && err) atomicOr(err, VL_DEV_WAIT_EXPIRED);
+                            if (lane == 0 && err) atomicOr(err, VL_DEV_WAIT_EXPIRED | VL_DEV_IN_GEMM_SMALL_M);
                             stop = true;
                             break;
                         }
@@ -186,7 +186,7 @@ gemm_bf16_small_m_kernel(const bf16* __restrict__ A, const bf16* __restrict__ W,
         const int s = git % GS_STAGES;
         const int kbase = it * GS_KC + warp * (GS_KC / GS_CONSUMERS);
         if (!mbar_wait_bounded(&full_bar[s], (unsigned)((git / GS_STAGES) & 1))) {
-            if (lane == 0 && err) atomicOr(err, VL_DEV_WAIT_EXPIRED);
+            if (lane == 0 && err) atomicOr(err, VL_DEV_WAIT_EXPIRED | VL_DEV_IN_GEMM_SMALL_M);
             return false;
         }
         const unsigned char* stage = gs_smem + (size_t)s * GS_ROWS * GS_ROWB + (size_t)warp * (GS_KC / GS_CONSUMERS) * 2;

@@ -85,7 +85,7 @@ gemm_tc5_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
                 for (int kb = 0; kb < k_blocks; ++kb, ++it) {
                     const int s = it % STAGES;
                     if (it >= STAGES && !mbar_wait_bounded(&empty_bar[s], (unsigned)((it / STAGES - 1) & 1))) {
-                        atomicExch(&failed, 1);
+                        atomicOr(&failed, 1);
                         ok = false;
                         break;
                     }
@@ -104,7 +104,7 @@ gemm_tc5_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
             for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x, ++local) {
                 const int acc = local & 1;
                 if (local >= 2 && !mbar_wait_bounded(&acc_empty_bar[acc], (unsigned)((local / 2 - 1) & 1))) {
-                    atomicExch(&failed, 1);
+                    atomicOr(&failed, 2);
                     break;
                 }
                 tc5_fence_after();
@@ -112,7 +112,7 @@ gemm_tc5_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
                 for (int kb = 0; kb < k_blocks; ++kb, ++it) {
                     const int s = it % STAGES;
                     if (!mbar_wait_bounded(&full_bar[s], (unsigned)((it / STAGES) & 1))) {
-                        atomicExch(&failed, 1);
+                        atomicOr(&failed, 4);
                         ok = false;
                         break;
                     }
@@ -136,7 +136,7 @@ gemm_tc5_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
         for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x, ++local) {
             const int acc = local & 1;
             if (!mbar_wait_bounded(&acc_full_bar[acc], (unsigned)((local / 2) & 1))) {
-                atomicExch(&failed, 1);
+                atomicOr(&failed, 8);
                 break;
             }
             tc5_fence_after();
@@ -156,7 +156,8 @@ gemm_tc5_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
     __syncthreads();
     tc5_fence_after();
     if (warp == 1) tc5_dealloc(tmem_base, 2 * BN);
-    if (threadIdx.x == 0 && failed && err) atomicOr(err, VL_DEV_WAIT_EXPIRED);
+    if (threadIdx.x == 0 && failed && err)
+        atomicOr(err, VL_DEV_WAIT_EXPIRED | VL_DEV_IN_GEMM_TC5 | ((unsigned)failed << VL_DEV_ROLE_SHIFT));
 }
 
 // ---- host side -------------------------------------------------------------------------------

@@ -127,7 +127,7 @@ gemm_tc5_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_con
                 for (int kb = 0; kb < k_blocks; ++kb, ++it) {
                     const int s = it % STAGES;
                     if (it >= STAGES && !mbar_wait_bounded(&empty_bar[s], (unsigned)((it / STAGES - 1) & 1))) {
-                        atomicExch(&failed, 1);
+                        atomicOr(&failed, 1);
                         ok = false;
                         break;
                     }
@@ -147,7 +147,7 @@ gemm_tc5_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_con
             for (int tile = pair; tile < total_tiles && ok; tile += num_pairs, ++local) {
                 const int acc = local & 1;
                 if (local >= 2 && !mbar_wait_bounded(&acc_empty_bar[acc], (unsigned)((local / 2 - 1) & 1))) {
-                    atomicExch(&failed, 1);
+                    atomicOr(&failed, 2);
                     break;
                 }
                 tc5_fence_after();
@@ -155,7 +155,7 @@ gemm_tc5_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_con
                 for (int kb = 0; kb < k_blocks; ++kb, ++it) {
                     const int s = it % STAGES;
                     if (!mbar_wait_bounded(&full_bar[s], (unsigned)((it / STAGES) & 1))) {
-                        atomicExch(&failed, 1);
+                        atomicOr(&failed, 4);
                         ok = false;
                         break;
                     }
@@ -178,7 +178,7 @@ gemm_tc5_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_con
         for (int tile = pair; tile < total_tiles; tile += num_pairs, ++local) {
             const int acc = local & 1;
             if (!mbar_wait_bounded(&acc_full_bar[acc], (unsigned)((local / 2) & 1))) {
-                atomicExch(&failed, 1);
+                atomicOr(&failed, 8);
                 break;
             }
             tc5_fence_after();
@@ -199,7 +199,8 @@ gemm_tc5_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_con
     cluster_sync();                                          // neither block frees or leaves while the other may still read it
     tc5_fence_after();
     if (warp == 1) dealloc_pair(tmem_base, TMEM_COLS);
-    if (threadIdx.x == 0 && failed && err) atomicOr(err, VL_DEV_WAIT_EXPIRED);
+    if (threadIdx.x == 0 && failed && err)
+        atomicOr(err, VL_DEV_WAIT_EXPIRED | VL_DEV_IN_GEMM_TC5_PAIR | ((unsigned)failed << VL_DEV_ROLE_SHIFT));
 }
 
 template <typename TO>

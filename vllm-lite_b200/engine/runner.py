@@ -36,7 +36,14 @@ class StepEntry:
 
 
 _DEVICE_ERRORS = {1: "a token id outside the vocabulary", 2: "a cache slot outside the pool",
-                  4: "a block table entry that names no page", 8: "a wait inside a kernel ran out"}
+                  4: "a block table entry that names no page", 8: "a wait inside a kernel ran out",
+                  # which kernel waited in vain (csrc/common.cuh) ...
+                  0x100: "in the float32 decode attention", 0x200: "in the weight-streaming product",
+                  0x400: "in the tcgen05 product", 0x800: "in the paired tcgen05 product",
+                  0x1000: "in the tcgen05 attention", 0x2000: "in the streaming decode attention",
+                  # ... and, in the tcgen05 products, for what
+                  0x10000: "for a free stage", 0x20000: "for a free accumulator", 0x40000: "for a filled stage",
+                  0x80000: "for a complete accumulator"}
 
 
 # Steps of up to this many tokens launch their kernels with programmatic dependent launch (each kernel's
