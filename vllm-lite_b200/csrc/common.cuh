@@ -107,11 +107,11 @@ static inline bool vl_pdl_enabled() {
     return g_vl_pdl == 1;
 }
 // The engine launches the kernels of a step of few tokens with the attribute (their launch gaps are
-// what it hides) and those of a step of many tokens without it.  Steps of a thousand tokens and more,
-// whose products run as clusters of two blocks on the tcgen05 kernels, stopped on the device now and
-// then with the attribute on every launch (about once in a few hundred launches of the paired
-// product at 1,588 or 4,096 rows; never without the attribute); the cause is not known, and what
-// the attribute hides there is a few microseconds beside kernels of a hundred.
+// what it hides) and those of a step of many tokens without it.  Steps of a thousand tokens and more
+// stopped on the device now and then with the attribute on every launch: the product that runs as
+// clusters of two blocks (gemm_tc5_pair.cu), started as a dependent while earlier kernels still ran,
+// never finished (about once in a few hundred of its launches at 1,588 or 4,096 rows; not once in
+// thousands when it alone was launched without the attribute).  Why is not known.
 extern "C" void vl_set_pdl(int on) { g_vl_pdl = (on && !vl_pdl_forbidden()) ? 1 : 0; }
 
 template <typename... KArgs, typename... Args>
