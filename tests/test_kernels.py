@@ -181,7 +181,8 @@ def test_gemm_small_m_with_fused_norms(M, H, K, N2, swiglu):
     assert float((out.double() - y).abs().max()) <= 2e-2 * float(y.abs().max()) + 1e-3
 
 
-@pytest.mark.parametrize("kernel,M", [("small_m", 1), ("small_m", 8), ("small_m", 13), ("tc5", 128), ("tc5", 300), ("tc5", 2048)])
+@pytest.mark.parametrize("kernel,M", [("small_m", 1), ("small_m", 8), ("small_m", 13), ("tc5", 128), ("tc5", 300), ("tc5", 2048),
+                                      ("tc5_pair", 300), ("tc5_pair", 1588)])
 @pytest.mark.parametrize("I,K", [(160, 96), (12288, 4096), (24, 64)])
 def test_gemm_with_fused_swiglu(kernel, M, I, K):
     """W interleaves 8 gate rows with their 8 up rows; the kernel writes silu(gate) * up."""
@@ -192,7 +193,7 @@ def test_gemm_with_fused_swiglu(kernel, M, I, K):
     w = torch.stack([gate.view(I // 8, 8, K), up.view(I // 8, 8, K)], dim=1).reshape(2 * I, K).contiguous()
     out = torch.full((M, I), float("nan"), device=DEV, dtype=torch.bfloat16)
     e = err_word()
-    fn = ops().gemm_bf16_small_m if kernel == "small_m" else ops().gemm_bf16_tc5
+    fn = {"small_m": ops().gemm_bf16_small_m, "tc5": ops().gemm_bf16_tc5, "tc5_pair": ops().gemm_bf16_tc5_pair}[kernel]
     fn(a, w, out, e, swiglu=True)
     assert int(e.item()) == 0
     g, u = a.double() @ gate.double().T, a.double() @ up.double().T

@@ -98,7 +98,6 @@ class Scheduler:
         self.native = can if native is None else bool(native)
         self.waiting: Deque[Sequence] = deque()
         self.running: List[Sequence] = []
-        self.finished: List[Sequence] = []
         self._next_id = 1                 # ids start at 1, as the reference's do
         self._arrivals = 0
         self.stats = dict(steps=0, prefill_tokens=0, decode_tokens=0, preemptions=0, finished=0)
@@ -277,7 +276,6 @@ class Scheduler:
             self.running.remove(seq)
         if seq.seq_id in self.cache.requests:
             self.cache.free(seq.seq_id)
-        self.finished.append(seq)
         self.stats["finished"] += 1
 
     def cancel(self, seq_id: int) -> bool:
