@@ -1,7 +1,8 @@
 """Draws one token per logits row on the device.
 
-The options of all rows are packed into one pinned host array and uploaded in one
-copy; penalties and biases go as ragged lists (each distinct generated id once,
+Rows that are all greedy need no upload at all.  Otherwise the options of all rows
+(temperature, top-p, the uniform number of the draw; top-k) go up as two small arrays;
+penalties and biases go as ragged lists (each distinct generated id once,
 as the reference's set does, crates/core/src/sampling.rs:670-688); the kernels of
 csrc/sampling.cu do the rest and only the chosen ids come back to the host."""
 from __future__ import annotations
