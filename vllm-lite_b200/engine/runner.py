@@ -469,9 +469,28 @@ class ModelRunner:
 
     def _upload(self, meta: np.ndarray, bucket: int = 0) -> torch.Tensor:
         n = meta.shape[0]
-        i, pin = self._pinned_slot(n)
+        i = self._flip
+        self._flip ^= 1
+        if self._meta_evt[i] is not None:
+            self._meta_evt[i].synchronize()
+        if self._meta_pin[i] is None or self._meta_pin[i].numel() < n:
+            self._meta_pin[i] = torch.empty(max(n, 4096) * 2, dtype=torch.int32).pin_memory()
+        if self._meta_dev is None or self._meta_dev.numel() < n:
+            self._meta_dev = torch.empty(max(n, 4096) * 2, dtype=torch.int32, device=self.device)
+        pin = self._meta_pin[i]
         pin[:n].numpy()[:] = meta
-        return self._to_device(i, n, bucket)
+        if bucket:                                  # a graph reads its batch from a buffer of its own
+            dev = self._graph_meta.get(bucket)
+            if dev is None:
+                dev = self._graph_meta[bucket] = torch.empty(n, dtype=torch.int32, device=self.device)
+        else:
+            dev = self._meta_dev
+        dev[:n].copy_(pin[:n], non_blocking=True)
+        self.uploaded_bytes += 4 * n
+        if self._meta_evt[i] is None:
+            self._meta_evt[i] = torch.cuda.Event()
+        self._meta_evt[i].record()
+        return dev[:n]
 
     def finish(self, batch: StepBatch):
         """Bookkeeping after the step's kernels are queued: windows move on."""
