@@ -15,7 +15,6 @@ from typing import Dict, List, Optional, Sequence as Seq
 
 import torch
 
-from ..cache.manager import OutOfPages
 from ..sampling import Sampler, SamplingParams
 from .loading import load_model_dir, parse_dtype
 from .runner import ModelRunner, StepEntry

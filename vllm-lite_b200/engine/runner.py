@@ -18,7 +18,7 @@ import numpy as np
 import torch
 
 from ..cache import make_cache_manager
-from ..cache.manager import CacheLayout, CacheManager, OutOfPages
+from ..cache.manager import CacheLayout, OutOfPages
 from ..cache.storage import CacheStorage
 from ..parts.base import QUERY_TILE, BuildContext, Entry, GroupView, StepBatch, Workspace
 from ..parts.model import CausalLM, cache_needs

@@ -23,7 +23,7 @@ tensors, the step's batch and the cache of its own call.
 """
 from __future__ import annotations
 
-from dataclasses import dataclass, field
+from dataclasses import dataclass
 from typing import List, Optional
 
 import torch

@@ -6,7 +6,7 @@ from __future__ import annotations
 
 import torch
 
-from .base import BuildContext, CallCache, Residual, prefixed, sub_weights
+from .base import BuildContext, Residual, prefixed, sub_weights
 from .linear import Linear
 from .registry import BLOCKS, NORMS
 from .spec import ModelPlan, TensorDecl

@@ -4,7 +4,7 @@
 part of what its sampler draws with, and have no counterpart here."""
 from __future__ import annotations
 
-from dataclasses import dataclass, field
+from dataclasses import dataclass
 from typing import Dict, List, Optional
 
 

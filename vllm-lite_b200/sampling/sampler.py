@@ -8,7 +8,7 @@ csrc/sampling.cu do the rest and only the chosen ids come back to the host."""
 from __future__ import annotations
 
 import random
-from typing import List, Optional, Sequence
+from typing import Optional, Sequence
 
 import numpy as np
 import torch

@@ -18,7 +18,7 @@ from pathlib import Path
 
 import torch
 
-from .safetensors_io import DTYPES, SafetensorsError, SafetensorsFile
+from .safetensors_io import SafetensorsError, SafetensorsFile
 
 _SKIPPED = ("visual.", "vision_", "img_")
 _FLOATS = ("F32", "BF16", "F16")
