@@ -36,3 +36,59 @@ def test_set_pdl_reaches_the_libraries_that_are_loaded():
         ops._pdl_libs.clear()
         ops._pdl_libs.update(saved)
         ops._pdl = saved_flag
+
+
+def test_ctypes_signatures_match_the_c_declarations():
+    """The engine calls its libraries through ctypes, where nothing checks an argument list: a float
+    passed where the C side reads an int goes wrong silently.  So the declarations are read from the
+    sources and compared, kind by kind (pointer, int, 64-bit int, float), with what ops.py binds."""
+    import re
+    declared = {}
+    for path in build.CSRC.glob("*.cu"):
+        for m in re.finditer(r'extern "C" int (\w+)\(([^)]*)\)\s*\{', path.read_text(), re.S):
+            declared[(path.stem, m.group(1))] = [a.strip() for a in m.group(2).replace("\n", " ").split(",") if a.strip()]
+
+    def c_kind(arg):
+        if "*" in arg:
+            return "pointer"
+        type_words = " ".join(arg.split()[:-1])
+        if "float" in type_words:
+            return "float"
+        if "long long" in type_words or "size_t" in type_words or "int64" in type_words:
+            return "int64"
+        return "int"
+
+    py_kind = {ctypes.c_void_p: "pointer", ctypes.c_float: "float", ctypes.c_int: "int",
+               ctypes.c_longlong: "int64", ctypes.c_size_t: "int64"}
+    assert ops._SIGNATURES
+    for key, bound in ops._SIGNATURES.items():
+        assert key in declared, f"{key} is bound but not declared extern C in its source"
+        assert [c_kind(a) for a in declared[key]] == [py_kind[t] for t in bound], key
+
+
+def test_host_core_bindings_match_the_c_declarations():
+    """The same check for the C++ core of cache manager and scheduler (cache/native.py)."""
+    import re
+    from ctypes import c_int, c_longlong
+    from vllm_lite_b200.cache import native
+    lib = native._core()
+    text = (build.CSRC / "host" / "cache_core.cpp").read_text()
+    found = 0
+    for m in re.finditer(r"^\s*([\w \*]+?)\s*\b(v[cs]_\w+)\(([^)]*)\)\s*\{", text, re.S | re.M):
+        ret, name, args = m.group(1).strip(), m.group(2), [a.strip() for a in m.group(3).replace("\n", " ").split(",") if a.strip()]
+        fn = getattr(lib, name)
+        assert fn.argtypes is not None, f"{name} is exported but not bound"
+
+        def c_kind(text_type):
+            if "*" in text_type:
+                return "pointer"
+            return "int64" if "long long" in text_type else "int"
+
+        def py_kind(t):
+            return {c_int: "int", c_longlong: "int64"}.get(t, "pointer")
+
+        assert [c_kind(" ".join(a.split()[:-1]) if "*" not in a else a) for a in args] == [py_kind(t) for t in fn.argtypes], name
+        want = "void" if ret == "void" else c_kind(ret)
+        assert want == ("void" if fn.restype is None else py_kind(fn.restype)), name
+        found += 1
+    assert found >= 19
