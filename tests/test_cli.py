@@ -58,3 +58,17 @@ def test_init_writes_a_folder_that_the_seed_determines(tmp_path):
     cj, w = P.read_model_dir(a)                                   # the plain reader takes what was written
     assert cj["hidden_size"] == H.TINY_B["hidden_size"] and "lm_head.weight" in w
     assert P.forward(cj, w, [1, 2, 3]).shape == (3, H.TINY_B["vocab_size"])
+
+
+def test_trace_run_without_a_gpu_says_so_and_exits(tmp_path):
+    """No CPU path: the replay program refuses loudly where there is no CUDA device."""
+    import subprocess
+    import sys
+    import torch
+    if torch.cuda.is_available():
+        pytest.skip("a GPU is present: the replay tests cover the program")
+    root = H.Path(__file__).resolve().parent.parent
+    proc = subprocess.run([sys.executable, str(root / "bin" / "trace_run"), "--model", str(H.model_dir("A")),
+                           "--dtype", "float32", "--out", str(tmp_path / "out"), "--max-tokens", "64"],
+                          input="", capture_output=True, text=True, timeout=300)
+    assert proc.returncode == 3 and "no CUDA device" in proc.stderr
