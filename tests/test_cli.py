@@ -72,3 +72,9 @@ def test_trace_run_without_a_gpu_says_so_and_exits(tmp_path):
                            "--dtype", "float32", "--out", str(tmp_path / "out"), "--max-tokens", "64"],
                           input="", capture_output=True, text=True, timeout=300)
     assert proc.returncode == 3 and "no CUDA device" in proc.stderr
+
+
+def test_the_engine_has_no_cpu_path():
+    from vllm_lite_b200.engine import ModelRunner, StepError
+    with pytest.raises(StepError, match="CUDA device only"):
+        ModelRunner(None, {}, device="cpu")
