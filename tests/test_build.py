@@ -22,6 +22,45 @@ def test_every_kernel_library_builds_and_exports_the_launch_switch():
         assert hasattr(handle, "vl_set_pdl"), f"{name} {defines} exports no vl_set_pdl"
 
 
+def test_the_paired_product_has_no_path_to_dependent_launch():
+    """The product on clusters of two blocks stood still on the device now and then when it was started
+    as a programmatic dependent.  Its launcher therefore builds its own launch with the cluster attribute
+    alone: it neither names the other attribute nor goes through the shared launcher that adds it."""
+    import re
+    text = (build.CSRC / "gemm_tc5_pair.cu").read_text()
+    code = re.sub(r"//[^\n]*", "", text)
+    assert "ProgrammaticStreamSerialization" not in code
+    assert "vl_launch(" not in code and "vl_pdl_enabled" not in code
+    assert re.search(r"cfg\.numAttrs\s*=\s*1\s*;", code) and code.count("numAttrs") == 1
+    assert code.count("cudaLaunchKernelEx") == 1
+    # the kernels that allocate tensor memory do so behind their wait for the kernels before them
+    for name in ("gemm_tc5_pair.cu", "gemm_tc5.cu", "flash_tc5.cu"):
+        body = re.sub(r"//[^\n]*", "", (build.CSRC / name).read_text())
+        body = body[body.index("__global__"):]
+        assert 0 < body.index("pdl_wait();") < body.index("alloc"), name
+
+
+def test_dependent_launch_is_off_until_switched_on():
+    assert ops._pdl is False or ops._pdl_libs            # the module's default; a test before may have stepped
+    for name, defines in kernel_libraries():
+        handle = build.load(name, defines)
+        if (name, build._variant(defines)) not in ops._pdl_libs:
+            assert handle.vl_get_pdl() == 0, name
+
+
+def test_digest_covers_every_header():
+    """A library is rebuilt when any header beside the sources changes, plain C headers included."""
+    import hashlib
+    before = build._digest("attention")
+    h = build.CSRC / "zz_probe_header.h"
+    try:
+        h.write_text("// probe\n")
+        assert build._digest("attention") != before
+    finally:
+        h.unlink()
+    assert build._digest("attention") == before
+
+
 def test_set_pdl_reaches_the_libraries_that_are_loaded():
     calls = []
     saved, saved_flag = dict(ops._pdl_libs), ops._pdl

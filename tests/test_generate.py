@@ -148,18 +148,21 @@ def test_steps_launched_ahead_change_nothing_but_the_timing(dtype):
 def test_long_steps_are_launched_without_dependent_launch():
     """Steps of few tokens overlap each kernel's start with the end of the one before (programmatic
     dependent launch); steps of many tokens are launched the plain way.  The switch follows the step."""
-    from vllm_lite_b200.csrc import ops
+    from vllm_lite_b200.csrc import build, ops
     from vllm_lite_b200.engine import StepEntry
     from vllm_lite_b200.engine.runner import PDL_MAX_TOKENS
     which = "B"
     runner = engine(which, dtype="bfloat16").runner
     long = H.tokens_for(which, PDL_MAX_TOKENS + 6, 300)
+    def told():                                     # what every loaded library was last told
+        return {int(build.load(lib, dict([("FA_HD", int(var[5:]))]) if var else None).vl_get_pdl())
+                for lib, var in ops._pdl_libs}
     whole = runner.step([StepEntry("a", long, [len(long) - 1])]).clone()
-    assert ops._pdl is False
+    assert ops._pdl is False and told() == {0}
     runner.step([StepEntry("a", [5], [0])])
-    assert ops._pdl is True
+    assert ops._pdl is True and told() == {1}
     runner.step([StepEntry("b", long[:10], [])])
-    assert ops._pdl is True
+    assert ops._pdl is True and told() == {1}
     cut = runner.step([StepEntry("b", long[10:], [len(long) - 11])])      # 60 tokens, with the attribute
     runner.check_device_errors()
     tol = H.TOL["bfloat16"] * float(whole.abs().max())

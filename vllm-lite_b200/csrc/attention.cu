@@ -273,6 +273,10 @@ decode_attention_split_kernel(const T* __restrict__ q, int q_stride,
     const int nvalid = min(GT, g - tile * GT);
     const int pos = positions[t];
     if (pos < 0) return;
+    if ((long long)pos >= (long long)S * chunk) {         // beyond what the scratch was sized for: flagged, and
+        if (threadIdx.x == 0 && split == 0 && err) atomicOr(err, VL_DEV_BEYOND_BOUND);   // the merge writes zeros
+        return;
+    }
     const int lo = (window > 0 && pos - window + 1 > 0) ? pos - window + 1 : 0;
     const int c0 = max(split * chunk, lo);
     const int c1 = min((split + 1) * chunk, pos + 1);
@@ -465,7 +469,9 @@ __global__ void decode_attention_merge_kernel(const float* __restrict__ part_acc
     const int tok = token_index ? token_index[t] : t;            // ... tok those of the step
     const int pos = positions[tok];
     T* op = out + ((size_t)tok * nq + h) * hd;
-    if (pos < 0) {
+    // a padded place of the batch, or a position beyond the S chunks that were computed (the split pass
+    // has flagged that): zeros, never a read outside this row's partial results
+    if (pos < 0 || (long long)pos >= (long long)S * chunk) {
         for (int e = threadIdx.x; e < hd; e += blockDim.x) op[e] = from_f32<T>(0.f);
         return;
     }

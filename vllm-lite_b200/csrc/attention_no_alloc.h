@@ -21,6 +21,11 @@
 //     later reads.
 //   * The first call on each device looks up the array's device address (with that device current)
 //     and remembers it.  Make that first call outside any stream capture.
+//   * S says how many chunks of `chunk` key positions the scratch is laid out for.  A token whose
+//     position is chunk * S or more does not fit that layout: it is not half-served, its row of
+//     `out` becomes zero and bit 0x10 is set in the error word (positions live on the device, so
+//     the host cannot refuse them beforehand).  A position of -1 marks an empty place of the batch:
+//     nothing is read for it and its row becomes zero too.
 // The entry point calls no cudaMalloc, cudaFree, or any routine of an allocating library.
 #pragma once
 

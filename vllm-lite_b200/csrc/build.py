@@ -3,7 +3,7 @@
 Each `.cu` file becomes one shared library, built the first time an operation
 from it is used and kept beside the sources under `csrc/_build/` (or, when that
 folder cannot be written, under the system's temporary folder).  The file name
-carries a hash of the source, of the shared header and of the flags, so an
+carries a hash of the source, of the headers beside it (*.cuh, *.h) and of the flags, so an
 edited source is rebuilt and a stale library is never loaded.  There is no
 fallback: when a library can be neither found nor built, loading raises.
 """
@@ -61,7 +61,7 @@ def _variant(defines) -> str:
 def _digest(name: str, defines=None) -> str:
     h = hashlib.sha256()
     h.update((CSRC / f"{name}.cu").read_bytes())
-    for header in sorted(CSRC.glob("*.cuh")):
+    for header in sorted(list(CSRC.glob("*.cuh")) + list(CSRC.glob("*.h"))):
         h.update(header.read_bytes())
     h.update(" ".join(NVCC_FLAGS + EXTRA_LIBS.get(name, [])).encode())
     h.update(_variant(defines).encode())

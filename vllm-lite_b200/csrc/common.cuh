@@ -19,6 +19,7 @@
 #define VL_DEV_BAD_SLOT 2u
 #define VL_DEV_BAD_PAGE 4u
 #define VL_DEV_WAIT_EXPIRED 8u
+#define VL_DEV_BEYOND_BOUND 0x10u   // a position at or past chunk * S, the context the launch was sized for
 // with VL_DEV_WAIT_EXPIRED: the kernel whose wait ran out ...
 #define VL_DEV_IN_DECODE_ATTENTION 0x100u
 #define VL_DEV_IN_GEMM_SMALL_M 0x200u
@@ -95,24 +96,21 @@ __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;"
 __device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 
 #include <cstdlib>
-// -1: not decided yet.  The environment's VLLM_LITE_B200_PDL=0 turns dependent launches off for good;
-// otherwise they are on until vl_set_pdl says otherwise.
-static int g_vl_pdl = -1;
+// Dependent launches are off until vl_set_pdl(1) turns them on for the launches that follow (the engine
+// does so for steps of few tokens, whose launch gaps they hide, and turns them off again for steps of
+// many tokens); the environment's VLLM_LITE_B200_PDL=0 keeps them off for good.  The product that runs as
+// clusters of two blocks (gemm_tc5_pair.cu) is launched without the attribute whatever the switch says:
+// started as a dependent while earlier kernels still ran it stood still on the device now and then (about
+// once in a few hundred of its launches at 1,588 or 4,096 rows; not once in thousands without the
+// attribute).  The kernels that allocate tensor memory do so behind their pdl_wait().
+static int g_vl_pdl = 0;
 static inline bool vl_pdl_forbidden() {
     const char* v = getenv("VLLM_LITE_B200_PDL");
     return v && v[0] == '0';
 }
-static inline bool vl_pdl_enabled() {
-    if (g_vl_pdl < 0) g_vl_pdl = vl_pdl_forbidden() ? 0 : 1;
-    return g_vl_pdl == 1;
-}
-// The engine launches the kernels of a step of few tokens with the attribute (their launch gaps are
-// what it hides) and those of a step of many tokens without it.  Steps of a thousand tokens and more
-// stopped on the device now and then with the attribute on every launch: the product that runs as
-// clusters of two blocks (gemm_tc5_pair.cu), started as a dependent while earlier kernels still ran,
-// never finished (about once in a few hundred of its launches at 1,588 or 4,096 rows; not once in
-// thousands when it alone was launched without the attribute).  Why is not known.
+static inline bool vl_pdl_enabled() { return g_vl_pdl == 1; }
 extern "C" void vl_set_pdl(int on) { g_vl_pdl = (on && !vl_pdl_forbidden()) ? 1 : 0; }
+extern "C" int vl_get_pdl() { return g_vl_pdl; }
 
 template <typename... KArgs, typename... Args>
 static inline int vl_launch(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,

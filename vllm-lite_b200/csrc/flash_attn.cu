@@ -375,8 +375,12 @@ flash_decode_kernel(const bf16* __restrict__ q, int q_stride,
     const int kvh = blockIdx.y / htiles, htile = blockIdx.y - kvh * htiles;
     const int h0 = kvh * grp + htile * DEC_ROWS;
     const int nvalid = min(DEC_ROWS, grp - htile * DEC_ROWS);
-    const int pos = positions[tok];
+    int pos = positions[tok];
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, t = lane & 3;
+    if ((long long)pos >= (long long)S * chunk) {                // beyond the S chunks the launch was sized for:
+        if (tid == 0 && split == 0 && err) atomicOr(err, VL_DEV_BEYOND_BOUND);   // flagged and served like an empty place
+        pos = -1;
+    }
     if (pos < 0) {                                               // a place of the batch that holds no request
         if (out && split == 0) {
             pdl_wait();                                          // earlier kernels may still read the rows

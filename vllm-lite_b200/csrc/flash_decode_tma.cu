@@ -134,7 +134,11 @@ flash_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_
             const int tok = token_index ? token_index[z] : z;
             const int kvh = y / htiles, htile = y - kvh * htiles;
             const int h0 = kvh * grp + htile * ROWS, nvalid = min(ROWS, grp - htile * ROWS);
-            const int pos = positions[tok];
+            int pos = positions[tok];
+            if ((long long)pos >= (long long)S * chunk) {  // beyond the S chunks the launch was sized for: flagged,
+                if (lane == 0 && split == 0 && err) atomicOr(err, VL_DEV_BEYOND_BOUND);   // served like an empty place
+                pos = -1;
+            }
             const int lo = (window > 0 && pos - window + 1 > 0) ? pos - window + 1 : 0;
             const int c0 = max(split * chunk, lo), c1 = min((split + 1) * chunk, pos + 1);
             const int ib = n & 1;

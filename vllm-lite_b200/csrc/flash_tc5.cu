@@ -142,13 +142,15 @@ flash_tc5_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constan
         mbar_fence_init();
         failed = 0;
     }
+    // Tensor memory is taken only after the kernels before this one have completed: a block started as a
+    // programmatic dependent then holds nothing of the SM that an earlier kernel may still be waiting for.
+    pdl_launch_dependents();
+    pdl_wait();                                      // q and the cache are written by the kernel before
     if (warp == 5) tc5_alloc(&tmem_base_slot, TMEM_COLS);
     tc5_fence_before();
     __syncthreads();
     tc5_fence_after();
     const unsigned tmem_base = tmem_base_slot;
-    pdl_launch_dependents();
-    pdl_wait();                                      // q and the cache are written by the kernel before
 
     // The list is in order of position and blocks start in the order of their number (x fastest): the
     // tiles with the longest rows of keys go first, for all heads, so that the longest blocks do not

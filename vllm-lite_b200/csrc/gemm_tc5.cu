@@ -67,13 +67,15 @@ gemm_tc5_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
         mbar_fence_init();
         failed = 0;
     }
+    // Tensor memory is taken only after the kernels before this one have completed: a block started as a
+    // programmatic dependent then holds nothing of the SM that an earlier kernel may still be waiting for.
+    pdl_launch_dependents();
+    pdl_wait();                                              // A is written by the kernel before
     if (warp == 1) tc5_alloc(&tmem_base_slot, 2 * BN);       // two accumulators; 2 * BN is a power of two >= 32
     tc5_fence_before();
     __syncthreads();
     tc5_fence_after();
     const unsigned tmem_base = tmem_base_slot;
-    pdl_launch_dependents();
-    pdl_wait();                                              // A is written by the kernel before
 
     if (warp == 0) {
         if (lane == 0) {                                     // ---- TMA producer ----

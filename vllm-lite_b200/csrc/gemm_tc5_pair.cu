@@ -108,14 +108,18 @@ gemm_tc5_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_con
         mbar_fence_init();
         failed = 0;
     }
+    // This kernel is never launched as a programmatic dependent (see launch_pair), so both calls below do
+    // nothing today.  They stay ahead of everything that takes a shared resource of the SM pair (tensor
+    // memory, the cluster's barrier): were the attribute ever given, nothing would be held while earlier
+    // kernels of the stream still run.
+    pdl_wait();                                              // A is written by the kernel before
+    pdl_launch_dependents();
     if (warp == 1) alloc_pair(&tmem_base_slot, TMEM_COLS);
     tc5_fence_before();
     __syncthreads();
     cluster_sync();                                          // the other block's mbarriers exist before anything arrives there
     tc5_fence_after();
     const unsigned tmem_base = tmem_base_slot;
-    pdl_launch_dependents();
-    pdl_wait();                                              // A is written by the kernel before
 
     if (warp == 0) {
         if (lane == 0) {                                     // ---- TMA producer ----
@@ -228,13 +232,15 @@ static int launch_pair(const void* A, const void* W, TO* C, int M, int N, int K,
     cfg.blockDim = dim3(NUM_THREADS);
     cfg.dynamicSmemBytes = smem;
     cfg.stream = s;
-    cudaLaunchAttribute attr[2];
+    // The cluster attribute and no other.  Started as a programmatic dependent (its clusters brought onto
+    // the SM pairs, their tensor memory allocated and their barrier passed while earlier kernels, other
+    // paired products among them, still ran) this kernel stood still on the device now and then; launched
+    // the plain way it never did.  So it is always launched the plain way, whatever vl_set_pdl says.
+    cudaLaunchAttribute attr[1];
     attr[0].id = cudaLaunchAttributeClusterDimension;
     attr[0].val.clusterDim.x = 2; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
-    attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-    attr[1].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
-    cfg.numAttrs = vl_pdl_enabled() ? 2 : 1;
+    cfg.numAttrs = 1;
     return (int)cudaLaunchKernelEx(&cfg, kern, map_a, map_w, C, M, N, K, ldc, err, tiles_m, tiles_n, swiglu);
 }
 

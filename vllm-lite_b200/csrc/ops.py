@@ -77,7 +77,8 @@ _functions = {}
 launch_count = 0          # kernels of this library launched so far (graph replays add theirs)
 
 
-_pdl = True               # whether launches carry the programmatic-dependent-launch attribute
+_pdl = False              # whether launches carry the programmatic-dependent-launch attribute: off unless the
+                          # engine turns it on for a step of few tokens (the paired tcgen05 product never has it)
 _pdl_libs = {}
 
 

@@ -37,6 +37,7 @@ class StepEntry:
 
 _DEVICE_ERRORS = {1: "a token id outside the vocabulary", 2: "a cache slot outside the pool",
                   4: "a block table entry that names no page", 8: "a wait inside a kernel ran out",
+                  0x10: "a position beyond the context that the attention launch was sized for",
                   # which kernel waited in vain (csrc/common.cuh) ...
                   0x100: "in the float32 decode attention", 0x200: "in the weight-streaming product",
                   0x400: "in the tcgen05 product", 0x800: "in the paired tcgen05 product",
@@ -204,15 +205,16 @@ class ModelRunner:
         G = len(self.cache.pools)
         i, pin = self._pinned_slot(64 + 8 * bucket + G * (bucket + bucket * fixed + 8))
         try:
-            got = self.cache.decode_step(request_ids, [0] * B, bucket, fixed, self.max_context, pin.numpy())
+            # the caller's bound is the core's limit on a request's length: a request that would pass it
+            # makes the call return before anything is appended or released
+            got = self.cache.decode_step(request_ids, [0] * B, bucket, fixed, min(int(longest), self.max_context),
+                                         pin.numpy())
         except OutOfPages:
             got = None
         if got is None or got[0] < 0:
             self._flip ^= 1
             return None
         used, off, sizes, starts = got
-        if int(starts.max()) + 1 > longest:
-            raise StepError("step_ahead: the caller's bound on the context is too small")
         dev = self._to_device(i, used, bucket)
         dev[int(off[0]):int(off[0]) + B].copy_(token_source[:B])
         self.steps += 1

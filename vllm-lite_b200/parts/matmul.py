@@ -9,6 +9,11 @@ from __future__ import annotations
 
 import torch
 
+# The library product must add in float32 whatever the shape: with this switch left on (torch's default)
+# cuBLAS may pick kernels that cut K among blocks and add the pieces in bfloat16, and a row's result
+# could then depend on how many rows share its step.
+torch.backends.cuda.matmul.allow_bf16_reduced_precision_reduction = False
+
 
 def fuses_swiglu(M, K) -> bool:
     """Whether the product for M rows runs in a kernel that can apply SwiGLU to its own tile."""
