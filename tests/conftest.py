@@ -25,3 +25,21 @@ def pytest_collection_modifyitems(config, items):
     for item in items:
         if "gpu" in item.keywords:
             item.add_marker(skip)
+
+
+def pytest_terminal_summary(terminalreporter):
+    """The worst error of every comparison with the plain implementation, so that the tolerances can be
+    read against what was seen."""
+    try:
+        import helpers
+    except Exception:
+        return
+    if not helpers.WORST:
+        return
+    terminalreporter.write_line("worst max|diff|/max|ref| against the plain implementation:")
+    by_dtype = {}
+    for (what, which, dtype), err in sorted(helpers.WORST.items()):
+        terminalreporter.write_line(f"  {dtype:9s} {which} {what:40s} {err:.3e}")
+        by_dtype[dtype] = max(by_dtype.get(dtype, 0.0), err)
+    for dtype, err in by_dtype.items():
+        terminalreporter.write_line(f"  worst of all, {dtype}: {err:.3e} (tolerance {helpers.TOL[dtype]:.1e})")

@@ -41,18 +41,33 @@ def tmp_root() -> Path:
     return Path(_tmp_root.name)
 
 
+def _store(dtype) -> str:
+    """The precision a case's folder is written in: a float32 engine is given weights with all their
+    bits (a path that dropped low bits of a weight would show), a bfloat16 engine bfloat16 ones."""
+    return "float32" if str(dtype).endswith("float32") else "bfloat16"
+
+
 @functools.lru_cache(maxsize=None)
-def model_dir(which: str) -> Path:
+def _model_dir(which: str, store: str) -> Path:
     from vllm_lite_b200.weights import write_model_dir
     spec = TINY[which]
-    d = tmp_root() / f"tiny_{which}"
-    write_model_dir(d, spec["config"], spec["seed"], std=spec["std"])
+    d = tmp_root() / f"tiny_{which}_{store}"
+    write_model_dir(d, spec["config"], spec["seed"], std=spec["std"],
+                    dtype=torch.float32 if store == "float32" else torch.bfloat16)
     return d
 
 
+def model_dir(which: str, dtype="bfloat16") -> Path:
+    return _model_dir(which, _store(dtype))
+
+
 @functools.lru_cache(maxsize=None)
-def plain_model(which: str):
-    return plain.read_model_dir(model_dir(which))
+def _plain_model(which: str, store: str):
+    return plain.read_model_dir(_model_dir(which, store))
+
+
+def plain_model(which: str, dtype="bfloat16"):
+    return _plain_model(which, _store(dtype))
 
 
 def tokens_for(which: str, length: int, seed: int):
@@ -63,17 +78,17 @@ def tokens_for(which: str, length: int, seed: int):
 _plain_cache = {}
 
 
-def plain_logits(which: str, tokens) -> torch.Tensor:
-    key = (which, tuple(tokens))
+def plain_logits(which: str, tokens, dtype="bfloat16") -> torch.Tensor:
+    key = (which, _store(dtype), tuple(tokens))
     if key not in _plain_cache:
-        cfg, w = plain_model(which)
+        cfg, w = plain_model(which, dtype)
         _plain_cache[key] = plain.forward(cfg, w, list(tokens))
     return _plain_cache[key]
 
 
 def make_runner(which: str, dtype: str, num_pages: int, page_size=None, max_requests=8, native_host=True):
     from vllm_lite_b200.engine import ModelRunner, load_model_dir
-    _, plan, weights = load_model_dir(model_dir(which), dtype, "cuda:0")
+    _, plan, weights = load_model_dir(model_dir(which, dtype), dtype, "cuda:0")
     return ModelRunner(plan, weights, dtype=torch.bfloat16 if dtype == "bfloat16" else torch.float32,
                        device="cuda:0", page_size=page_size or TINY[which]["page_size"], num_pages=num_pages,
                        max_requests=max_requests, native_host=native_host)
@@ -103,15 +118,20 @@ def run_schedule(runner, schedule):
     return rows
 
 
+WORST = {}        # (what, configuration, dtype) -> the largest error any comparison saw; printed when the run ends
+
+
 def assert_rows_match(rows, which, requests, dtype, what=""):
     """rows: {(id, position): row}; requests: {id: tokens}."""
     assert rows, "nothing was compared"
     worst = 0.0
     for (rid, pos), row in rows.items():
-        ref = plain_logits(which, requests[rid])[pos]
+        ref = plain_logits(which, requests[rid], dtype)[pos]
         scale = float(ref.abs().max())
         err = float((row - ref).abs().max()) / max(scale, 1e-12)
         worst = max(worst, err)
         assert err <= TOL[dtype], (f"{what} {which}/{dtype}: request {rid} position {pos}: "
                                    f"max|diff|/max|ref| = {err:.3e} > {TOL[dtype]:.1e}")
+    key = (what, which, dtype)
+    WORST[key] = max(WORST.get(key, 0.0), worst)
     return worst

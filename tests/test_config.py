@@ -45,7 +45,8 @@ def test_missing_size_is_an_error(key):
     assert key in str(e.value)
 
 
-@pytest.mark.parametrize("patch", [dict(num_key_value_heads=3), dict(head_dim=15), dict(hidden_size=-4),
+@pytest.mark.parametrize("patch", [dict(num_key_value_heads=3), dict(head_dim=15), dict(head_dim=24), dict(head_dim=272),
+                                   dict(hidden_size=-4),
                                    dict(vocab_size="many"), dict(attention_bias=True), dict(hidden_act="gelu"),
                                    dict(rope_scaling={"rope_type": "yarn", "factor": 4.0}),
                                    dict(use_sliding_window=True), dict(rms_norm_eps=0.0)])

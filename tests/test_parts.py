@@ -468,3 +468,185 @@ def test_toy_position_encoding_and_routed_feed_forward_register_and_step():
         POSITIONS.unregister("toy_learned_position")
         FEED_FORWARDS.unregister("toy_routed")
         unregister_architecture("ToyMixLM")
+
+
+# ---- toy ends of the model and a toy head norm, defined here ---------------------------------------
+@dataclass(frozen=True)
+class ScaledEmbeddingSpec:
+    vocab_size: int
+    hidden_size: int
+    scale: float
+    kind: str = "toy_scaled_embedding"
+
+
+class ScaledEmbedding:
+    """x[t] = scale * table[id[t]]: the gather is the framework's kernel, the scaling this part's own."""
+    graph_safe = True
+
+    @staticmethod
+    def declare(spec):
+        from vllm_lite_b200.parts.spec import TensorDecl
+        return {"weight": TensorDecl((spec.vocab_size, spec.hidden_size))}
+
+    def __init__(self, spec, weights, ctx):
+        self.spec, self.table = spec, weights["weight"]
+
+    def tied_weight(self):
+        return self.table
+
+    def __call__(self, step, x):
+        from vllm_lite_b200.csrc import ops
+        ops.embed(step.tokens, self.table, x, step.err)
+        return x.mul_(self.spec.scale)
+
+
+@dataclass(frozen=True)
+class CappedHeadSpec:
+    vocab_size: int
+    hidden_size: int
+    cap: float
+    kind: str = "toy_capped_head"
+
+
+class CappedHead:
+    """logits = cap * tanh(h W^T / cap) with a matrix of its own."""
+    graph_safe = True
+
+    @staticmethod
+    def declare(spec):
+        from vllm_lite_b200.parts.spec import TensorDecl
+        return {"weight": TensorDecl((spec.vocab_size, spec.hidden_size))}
+
+    def __init__(self, spec, weights, ctx, embedding=None):
+        from vllm_lite_b200.parts.linear import Linear
+        self.spec, self.proj = spec, Linear(weights["weight"])
+
+    def __call__(self, h, step):
+        y = self.proj(h, step, "logits", out_dtype=torch.float32)
+        return y.div_(self.spec.cap).tanh_().mul_(self.spec.cap)
+
+
+class CenteredHeadNorm:
+    """A head norm that is not an RMS norm: (x - mean) / sqrt(var + eps) * w over head_dim.  It offers
+    no fused_rms(), so the attention mixer lets it edit the heads itself."""
+
+    @staticmethod
+    def declare(spec):
+        from vllm_lite_b200.parts.spec import TensorDecl
+        return {"weight": TensorDecl((spec.size,), init="norm")}
+
+    def __init__(self, spec, weights, ctx):
+        self.spec, self.weight = spec, weights["weight"].float()
+
+    def apply_heads(self, qkv, first_head, num_heads, head_dim, step):
+        T = qkv.shape[0]
+        v = qkv[:, first_head * head_dim:(first_head + num_heads) * head_dim].view(T, num_heads, head_dim)
+        v.copy_(centered_norm(v.float(), self.weight, self.spec.eps).to(qkv.dtype))
+
+
+def centered_norm(x, w, eps):
+    c = x - x.mean(dim=-1, keepdim=True)
+    return c / torch.sqrt((c * c).mean(dim=-1, keepdim=True) + eps) * w
+
+
+def plain_toy_ends(cfg, w, ids, scale, cap):
+    """Scaled embedding; layer 0 with q/k/v biases and the centred head norm, layer 1 as in the plain
+    model; capped head with a matrix of its own although the configuration ties the embeddings."""
+    cfg = P.normalise_config(cfg)
+    n, pos = len(ids), list(range(len(ids)))
+    nq, nkv, d, eps = cfg["num_attention_heads"], cfg["num_key_value_heads"], cfg["head_dim"], cfg["rms_norm_eps"]
+    x = scale * P.embedding(ids, w["model.embed_tokens.weight"])
+    pre = "model.layers.0.self_attn."
+    h = P.rms_norm(x, w["model.layers.0.input_layernorm.weight"], eps)
+    q = (P.linear(h, w[pre + "q_proj.weight"]) + w[pre + "q_proj.bias"]).view(n, nq, d)
+    k = (P.linear(h, w[pre + "k_proj.weight"]) + w[pre + "k_proj.bias"]).view(n, nkv, d)
+    v = (P.linear(h, w[pre + "v_proj.weight"]) + w[pre + "v_proj.bias"]).view(n, nkv, d)
+    q = P.rope(centered_norm(q, w[pre + "q_norm.weight"], eps), pos, cfg["rope_theta"])
+    k = P.rope(centered_norm(k, w[pre + "k_norm.weight"], eps), pos, cfg["rope_theta"])
+    x = x + P.linear(P.causal_attention(q, k, v).reshape(n, nq * d), w[pre + "o_proj.weight"])
+    x = x + P.swiglu(P.rms_norm(x, w["model.layers.0.post_attention_layernorm.weight"], eps), w, "model.layers.0.")
+    x = P.decoder_block(x, pos, w, 1, cfg)
+    y = P.linear(P.rms_norm(x, w["model.norm.weight"], eps), w["lm_head.weight"])
+    return cap * torch.tanh(y / cap)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_toy_embedding_head_head_norm_and_biases_register_and_step(dtype):
+    """The two ends of the model are parts like the others: a scaled embedding and a capped head defined
+    here replace the plain ones; a head norm of another kind than RMS is dispatched to, not run as RMS;
+    and projections may carry a bias.  Nothing of the framework is edited."""
+    import dataclasses, json
+    from vllm_lite_b200.config import Qwen3Config, plan_from_config_json, register_architecture, unregister_architecture
+    from vllm_lite_b200.engine import ModelRunner, load_model_dir
+    from vllm_lite_b200.parts import EMBEDDINGS, HEADS, NORMS, declare_model
+    from vllm_lite_b200.parts.spec import ModelPlan, NormSpec
+    from vllm_lite_b200.weights import random_tensors, write_safetensors
+    scale, cap = 3.5, 0.4
+
+    def plan(cfg):
+        base = plan_from_config_json({**H.TINY_A, "architectures": ["Qwen3ForCausalLM"]})[1]
+        l0, l1 = base.layers
+        mixer = dataclasses.replace(l0.mixer, bias=True, qk_norm=NormSpec(cfg.head_dim, cfg.rms_norm_eps, kind="toy_centered"))
+        return ModelPlan(**{**base.__dict__, "architecture": "ToyEndsLM", "layers": (dataclasses.replace(l0, mixer=mixer), l1),
+                            "embedding": ScaledEmbeddingSpec(cfg.vocab_size, cfg.hidden_size, scale),
+                            "head": CappedHeadSpec(cfg.vocab_size, cfg.hidden_size, cap)})
+
+    EMBEDDINGS.register("toy_scaled_embedding", ScaledEmbedding)
+    HEADS.register("toy_capped_head", CappedHead)
+    NORMS.register("toy_centered", CenteredHeadNorm)
+    register_architecture("ToyEndsLM", Qwen3Config, plan)
+    try:
+        cfg_json = {**H.TINY_A, "architectures": ["ToyEndsLM"]}
+        d = H.tmp_root() / f"toy_ends_{dtype}"
+        d.mkdir(exist_ok=True)
+        (d / "config.json").write_text(json.dumps(cfg_json))
+        _, p = plan_from_config_json(cfg_json)
+        decl = declare_model(p)
+        assert "lm_head.weight" in decl and "model.layers.0.self_attn.k_proj.bias" in decl
+        assert "model.layers.1.self_attn.k_proj.bias" not in decl
+        store = torch.float32 if dtype == "float32" else torch.bfloat16
+        write_safetensors(d / "model.safetensors", random_tensors(decl, 4, std=0.06, dtype=store))
+        _, p, weights = load_model_dir(d, dtype, DEV)
+        runner = ModelRunner(p, weights, dtype=store, device=DEV, page_size=16, num_pages=8, max_requests=3)
+        a, b = H.tokens_for("A", 37, 5), H.tokens_for("A", 12, 6)
+        cfg, w = P.read_model_dir(d)
+        ref = {"a": plain_toy_ends(cfg, w, a, scale, cap), "b": plain_toy_ends(cfg, w, b, scale, cap)}
+        assert not torch.allclose(ref["a"], P.forward(cfg, w, a), atol=1e-2)
+        rows = H.run_schedule(runner, [
+            ([("a", a[:17], list(range(17)))], []),
+            ([("a", a[17:19], [0, 1]), ("b", b, list(range(12)))], ["b"]),
+            ([("a", a[19:20], [0])], []),
+            ([("a", a[20:21], [0])], []),
+            ([("a", a[21:], list(range(16)))], ["a"]),
+        ])
+        tol = 5e-5 if dtype == "float32" else H.TOL["bfloat16"]
+        for (rid, pos), row in rows.items():
+            assert float((row - ref[rid][pos]).abs().max()) <= tol * float(ref[rid].abs().max()), (rid, pos)
+    finally:
+        EMBEDDINGS.unregister("toy_scaled_embedding")
+        HEADS.unregister("toy_capped_head")
+        NORMS.unregister("toy_centered")
+        unregister_architecture("ToyEndsLM")
+
+
+def test_a_head_norm_that_offers_neither_form_is_refused_when_the_model_is_built():
+    from vllm_lite_b200.parts import MIXERS, NORMS
+    from vllm_lite_b200.parts.base import BuildContext
+    from vllm_lite_b200.parts.spec import AttentionSpec, NormSpec, RotarySpec
+
+    class Useless:
+        declare = staticmethod(lambda spec: {})
+        def __init__(self, spec, weights, ctx):
+            pass
+
+    NORMS.register("toy_useless", Useless)
+    try:
+        spec = AttentionSpec(32, 2, 1, 16, qk_norm=NormSpec(16, 1e-6, kind="toy_useless"), position=RotarySpec(16, 1e4))
+        cls = MIXERS.get("gqa_attention")
+        w = {k: torch.zeros(d.shape, device=DEV, dtype=torch.bfloat16) for k, d in cls.declare(spec).items()}
+        with pytest.raises(TypeError, match="head norm"):
+            cls(spec, w, BuildContext(torch.device(DEV), torch.bfloat16))
+        with pytest.raises(ValueError, match="head_dim"):
+            cls(AttentionSpec(32, 2, 1, 24), {}, BuildContext(torch.device(DEV), torch.bfloat16))
+    finally:
+        NORMS.unregister("toy_useless")

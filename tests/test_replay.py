@@ -201,7 +201,7 @@ def test_trace_run_program(dtype, tmp_path):
         {"step": 3, "entries": [{"id": "a", "tokens": toks[27:], "want": [12]}], "end": ["a"]},
     ]
     env = dict(os.environ)
-    proc = subprocess.run([sys.executable, str(ROOT / "bin" / "trace_run"), "--model", str(H.model_dir(which)),
+    proc = subprocess.run([sys.executable, str(ROOT / "bin" / "trace_run"), "--model", str(H.model_dir(which, dtype)),
                            "--dtype", dtype, "--out", str(tmp_path), "--max-tokens", "128"],
                           input="\n".join(json.dumps(s) for s in steps) + "\n", capture_output=True, text=True,
                           env=env, timeout=900)
@@ -209,7 +209,7 @@ def test_trace_run_program(dtype, tmp_path):
     assert [l for l in proc.stdout.splitlines() if l.startswith("done")] == [f"done {i}" for i in range(4)]
     assert not (tmp_path / "1.f32").exists()
     V = H.TINY[which]["config"]["vocab_size"]
-    ref = H.plain_logits(which, toks)
+    ref = H.plain_logits(which, toks, dtype)
     got = {0: [0, 24], 2: [25, 26], 3: [39]}
     for step, positions in got.items():
         arr = np.fromfile(tmp_path / f"{step}.f32", dtype="<f4").reshape(-1, V)

@@ -100,3 +100,51 @@ def test_container_reader_keeps_dtypes(tmp_path):
         got = f.read(k)
         assert got.dtype == t[k].dtype and torch.equal(got, t[k])
     f.close()
+
+
+def test_every_random_element_is_a_function_of_seed_name_and_index():
+    """The generator is a counter hash into a table of the normal distribution's inverse CDF: integer
+    arithmetic and single float32 roundings only, so any device gives the same bits.  Here the torch
+    code is checked against the same recipe in plain Python integers."""
+    import numpy as np
+    from vllm_lite_b200.weights import random_init as R
+    name, seed, n = "model.layers.1.self_attn.k_proj.weight", 11, 70_000
+    x = R.standard_normal(seed, name, n)
+    points, diffs = R._inverse_cdf_table()
+    key = R.tensor_key(seed, name)
+    for i in (0, 1, 2, 65_535, 65_536, n - 1):
+        z = R._mix_python((i + 1) * R._GOLDEN + key)
+        cell, frac = z >> 48, (z >> 24) & 0xFFFFFF
+        want = np.float32(points[cell]) + np.float32(np.float32(diffs[cell]) * np.float32(frac * 2.0 ** -24))
+        assert float(x[i]) == float(want), i
+    # a tensor's values do not depend on what else is generated, nor on how the work is cut into pieces
+    saved = R.CHUNK
+    try:
+        R.CHUNK = 1000
+        assert torch.equal(R.standard_normal(seed, name, n), x)
+    finally:
+        R.CHUNK = saved
+    assert not torch.equal(R.standard_normal(seed, name + "x", n), x)
+    assert not torch.equal(R.standard_normal(seed + 1, name, n), x)
+    both = random_tensors(declared("A"), 3)
+    alone = random_tensors({"model.norm.weight": declared("A")["model.norm.weight"]}, 3)
+    assert torch.equal(both["model.norm.weight"], alone["model.norm.weight"])
+    # and it is the distribution it says
+    big = R.standard_normal(1, "t", 2_000_000).double()
+    assert abs(float(big.mean())) < 3e-3 and abs(float(big.std()) - 1) < 3e-3
+    assert abs(float((big ** 4).mean()) - 3) < 0.05 and float(big.abs().max()) < 4.6
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("dtype,store", [("bfloat16", torch.bfloat16), ("float32", torch.bfloat16), ("float32", torch.float32)])
+def test_one_seed_one_model_with_or_without_a_folder(tmp_path, dtype, store):
+    """`random_model` (made on the GPU, no file) and a folder written with the same seed and read back
+    hold the same tensors bit for bit."""
+    from vllm_lite_b200.engine import load_model_dir, random_model
+    d = write_model_dir(tmp_path / "m", H.TINY_B, seed=9, std=0.05, dtype=store)
+    _, _, from_folder = load_model_dir(d, dtype, "cuda:0")
+    _, _, direct = random_model(H.TINY_B, seed=9, dtype=dtype, device="cuda:0", std=0.05, store_dtype=store)
+    assert set(from_folder) == set(direct)
+    for name in direct:
+        assert direct[name].dtype == from_folder[name].dtype, name
+        assert torch.equal(direct[name], from_folder[name]), name

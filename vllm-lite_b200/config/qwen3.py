@@ -67,8 +67,9 @@ class Qwen3Config:
         if self.num_attention_heads % self.num_key_value_heads:
             raise InvalidField("num_key_value_heads",
                                f"{self.num_key_value_heads} does not divide num_attention_heads={self.num_attention_heads}")
-        if self.head_dim % 2:
-            raise InvalidField("head_dim", f"{self.head_dim} is odd; the rotation pairs x[i] with x[i + head_dim/2]")
+        if self.head_dim % 16 or not 16 <= self.head_dim <= 256:
+            raise InvalidField("head_dim", f"{self.head_dim}: the attention kernels take multiples of 16 from 16 to 256 "
+                                           f"(the rotation pairs x[i] with x[i + head_dim/2])")
         if not (self.rms_norm_eps > 0):
             raise InvalidField("rms_norm_eps", f"must be positive, got {self.rms_norm_eps}")
         if not (self.rope_theta > 0):

@@ -133,12 +133,12 @@ static bool launch_rmsnorm_vec(float* x, const TA* delta, const int* rows, const
     return true;
 }
 
-// x += delta, for the residual that is still pending after the last block when
-// someone wants the stream itself.
+// y[r, c] += bias[c] for a linear layer with a bias vector: the product's result is widened, the float32
+// bias added and the sum rounded once.
 template <typename TA>
-__global__ void residual_add_kernel(float* __restrict__ x, const TA* __restrict__ delta, size_t n) {
+__global__ void add_bias_kernel(TA* __restrict__ y, const float* __restrict__ bias, size_t n, int cols) {
     size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
-    if (i < n) x[i] += to_f32(delta[i]);
+    if (i < n) y[i] = from_f32<TA>(to_f32(y[i]) + bias[i % (size_t)cols]);
 }
 
 template <typename TI, typename TO>
@@ -176,14 +176,15 @@ extern "C" int vl_add_rmsnorm(float* x, const void* delta, const int* rows, cons
     return vl_launch_status();
 }
 
-extern "C" int vl_residual_add(float* x, const void* delta, int act_dtype, long long n, void* stream) {
-    if (n <= 0) return VL_OK;
+extern "C" int vl_add_bias(void* y, int act_dtype, const float* bias, long long rows, int cols, void* stream) {
+    if (rows <= 0 || cols <= 0) return VL_OK;
     cudaStream_t s = (cudaStream_t)stream;
+    const size_t n = (size_t)rows * (size_t)cols;
     const unsigned blocks = (unsigned)((n + 255) / 256);
     if (act_dtype == VL_F32)
-        residual_add_kernel<float><<<blocks, 256, 0, s>>>(x, (const float*)delta, (size_t)n);
+        add_bias_kernel<float><<<blocks, 256, 0, s>>>((float*)y, bias, n, cols);
     else if (act_dtype == VL_BF16)
-        residual_add_kernel<bf16><<<blocks, 256, 0, s>>>(x, (const bf16*)delta, (size_t)n);
+        add_bias_kernel<bf16><<<blocks, 256, 0, s>>>((bf16*)y, bias, n, cols);
     else
         return VL_ERR_UNSUPPORTED;
     return vl_launch_status();

@@ -34,7 +34,7 @@ def dtype_code(dtype) -> int:
 _SIGNATURES = {
     ("embed_norm", "vl_embed"): [c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_void_p, c_void_p],
     ("embed_norm", "vl_add_rmsnorm"): [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_float, c_void_p],
-    ("embed_norm", "vl_residual_add"): [c_void_p, c_void_p, c_int, c_longlong, c_void_p],
+    ("embed_norm", "vl_add_bias"): [c_void_p, c_int, c_void_p, c_longlong, c_int, c_void_p],
     ("embed_norm", "vl_cast"): [c_void_p, c_int, c_void_p, c_int, c_longlong, c_void_p],
     ("rope_cache", "vl_qk_norm_rope_write"): [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_float, c_void_p, c_int,
                                               c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_longlong, c_int,
@@ -169,13 +169,14 @@ def add_rmsnorm(x, delta, weight, eps, out, rows=None):
     return out
 
 
-def residual_add(x, delta):
-    _need(x, torch.float32, "x"); _need(delta, None, "delta")
-    if delta.shape != x.shape:
-        raise KernelError("residual_add: shapes differ")
-    _check(_fn("embed_norm", "vl_residual_add")(_ptr(x), _ptr(delta), dtype_code(delta.dtype), x.numel(), _stream()),
-           "vl_residual_add")
-    return x
+def add_bias(y, bias):
+    """y[r, c] += bias[c] in place; y float32 or bfloat16 [rows, cols], bias float32 [cols]."""
+    _need(y, None, "y", 2); _need(bias, torch.float32, "bias", 1)
+    if bias.shape[0] != y.shape[1]:
+        raise KernelError(f"add_bias: bias has {bias.shape[0]} entries for rows of {y.shape[1]}")
+    _check(_fn("embed_norm", "vl_add_bias")(_ptr(y), dtype_code(y.dtype), _ptr(bias), y.shape[0], y.shape[1], _stream()),
+           "vl_add_bias")
+    return y
 
 
 def cast(src, out):

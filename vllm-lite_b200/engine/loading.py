@@ -31,12 +31,15 @@ def load_model_dir(model_dir, dtype, device):
     return cfg, plan, weights
 
 
-def random_model(config_json: dict, seed: int, dtype, device, std=None):
-    """The same model that `write_model_dir` would write, made on the device without a folder."""
+def random_model(config_json: dict, seed: int, dtype, device, std=None, store_dtype=torch.bfloat16):
+    """The model that `write_model_dir(folder, config_json, seed, std, dtype=store_dtype)` would write and
+    `load_model_dir(folder, dtype, device)` would read back, made on the device without a folder: every
+    element is a function of (seed, tensor name, index) alone (weights/random_init.py), so the tensors
+    are equal bit for bit."""
     dtype = parse_dtype(dtype)
     cfg, plan = plan_from_config_json(config_json)
     tensors = random_tensors(declare_model(plan), seed, plan.init_std if std is None else std,
-                             plan.norm_init_std, dtype=torch.bfloat16, device=device)
-    if dtype == torch.float32:
-        tensors = {k: v.float() for k, v in tensors.items()}
-    return cfg, plan, tensors
+                             plan.norm_init_std, dtype=store_dtype, device=device)
+    # what the loader does with a stored tensor: widened for a float32 engine, else kept as stored
+    from ..weights.loader import resident_dtype
+    return cfg, plan, {k: v.to(resident_dtype(v.dtype, dtype)) for k, v in tensors.items()}

@@ -19,6 +19,22 @@ from .registry import MIXERS, NORMS, POSITIONS
 from .spec import AttentionSpec, TensorDecl
 
 
+MAX_HEAD_DIM = 256
+
+
+def check_attention_sizes(spec: AttentionSpec):
+    """What the attention kernels take, checked when a model is planned or built instead of in its first
+    step: head sizes in steps of 16 up to 256, and kv heads that divide the query heads."""
+    if spec.num_heads <= 0 or spec.num_kv_heads <= 0 or spec.num_heads % spec.num_kv_heads:
+        raise ValueError(f"{spec.num_kv_heads} kv heads do not divide {spec.num_heads} query heads")
+    if spec.head_dim % 16 or not 16 <= spec.head_dim <= MAX_HEAD_DIM:
+        raise ValueError(f"head_dim {spec.head_dim}: the attention kernels take multiples of 16 from 16 to {MAX_HEAD_DIM}")
+    if spec.qk_norm is not None and spec.qk_norm.size != spec.head_dim:
+        raise ValueError("the head norm runs over head_dim")
+    if spec.window is not None and spec.window <= 0:
+        raise ValueError(f"window {spec.window} must be positive (None reads every earlier key)")
+
+
 @MIXERS.register("gqa_attention")
 class GqaAttention:
     graph_safe = True          # launches only stream-ordered kernels: a step can be captured in a CUDA graph
@@ -30,6 +46,9 @@ class GqaAttention:
              "k_proj.weight": TensorDecl((kvd, spec.hidden_size)),
              "v_proj.weight": TensorDecl((kvd, spec.hidden_size)),
              "o_proj.weight": TensorDecl((spec.hidden_size, qd))}
+        if spec.bias:
+            d.update({"q_proj.bias": TensorDecl((qd,)), "k_proj.bias": TensorDecl((kvd,)),
+                      "v_proj.bias": TensorDecl((kvd,))})
         if spec.qk_norm is not None:
             for side in ("q_norm.", "k_norm."):
                 for name, decl in NORMS.get(spec.qk_norm.kind).declare(spec.qk_norm).items():
@@ -44,20 +63,31 @@ class GqaAttention:
         return PagedKV(spec.num_kv_heads, spec.head_dim, spec.window)
 
     def __init__(self, spec: AttentionSpec, weights: dict, ctx):
-        if spec.num_heads % spec.num_kv_heads:
-            raise ValueError(f"{spec.num_kv_heads} kv heads do not divide {spec.num_heads} query heads")
-        if spec.qk_norm is not None and spec.qk_norm.size != spec.head_dim:
-            raise ValueError("the head norm runs over head_dim")
+        check_attention_sizes(spec)
         self.spec = spec
         self.dtype = ctx.dtype
         qkv = torch.cat([weights["q_proj.weight"], weights["k_proj.weight"], weights["v_proj.weight"]], dim=0)
-        self.qkv_proj = Linear(qkv.contiguous())
+        bias = None
+        if spec.bias:
+            bias = torch.cat([weights["q_proj.bias"].float(), weights["k_proj.bias"].float(),
+                              weights["v_proj.bias"].float()], dim=0)
+        self.qkv_proj = Linear(qkv.contiguous(), bias)
         self.o_proj = Linear(weights["o_proj.weight"])
         self.q_norm = self.k_norm = None
+        # The kernel that rotates and writes the cache also applies an RMS norm to every head.  A head norm
+        # that says it is one (`fused_rms()` -> (weight, eps)) runs there; any other kind must change the
+        # heads itself (`apply_heads`), and the kernel is then given no norm.
+        self.fused_head_norm = None
         if spec.qk_norm is not None:
             cls = NORMS.get(spec.qk_norm.kind)
             self.q_norm = cls(spec.qk_norm, sub_weights(weights, "q_norm."), ctx)
             self.k_norm = cls(spec.qk_norm, sub_weights(weights, "k_norm."), ctx)
+            if hasattr(self.q_norm, "fused_rms"):
+                (qw, eps), (kw, _) = self.q_norm.fused_rms(), self.k_norm.fused_rms()
+                self.fused_head_norm = (qw, kw, eps)
+            elif not hasattr(self.q_norm, "apply_heads"):
+                raise TypeError(f"norm kind {spec.qk_norm.kind!r} cannot serve as a head norm: it offers neither "
+                                f"fused_rms() nor apply_heads(qkv, first_head, num_heads, head_dim, step)")
         self.position = None
         if spec.position is not None:
             self.position = POSITIONS.get(spec.position.kind)(spec.position, sub_weights(weights, "rotary."), ctx)
@@ -78,11 +108,13 @@ class GqaAttention:
             # (after the projections, before the head norm's kernel writes the cache)
             self.position.apply(qkv, step.positions, s.num_heads, s.num_kv_heads, s.head_dim, step)
         inv_freq, rot = fused if fused is not None else (None, 0)
+        if self.q_norm is not None and self.fused_head_norm is None:
+            # a head norm of a kind of its own: it edits the q heads and the k heads of qkv in place
+            self.q_norm.apply_heads(qkv, 0, s.num_heads, s.head_dim, step)
+            self.k_norm.apply_heads(qkv, s.num_heads, s.num_kv_heads, s.head_dim, step)
+        qw, kw, eps = self.fused_head_norm if self.fused_head_norm is not None else (None, None, 0.0)
         ops.qk_norm_rope_write(
-            qkv, step.positions, group.slots if cache.writes else None,
-            self.q_norm.weight if self.q_norm is not None else None,
-            self.k_norm.weight if self.k_norm is not None else None,
-            s.qk_norm.eps if s.qk_norm is not None else 0.0,
+            qkv, step.positions, group.slots if cache.writes else None, qw, kw, eps,
             inv_freq, rot, cache.k, cache.v, s.num_heads, s.num_kv_heads, s.head_dim, step.err)
         out = step.workspace.get(step.tag + "attn.out", (qkv.shape[0], s.num_heads * s.head_dim), self.dtype)
         from . import attention_dispatch

@@ -1,5 +1,6 @@
-"""y = x W^T with the weight stored [out, in] and no bias
-(crates/model/src/components/attention/gqa/norm.rs:21-26 of the reference).
+"""y = x W^T (+ b) with the weight stored [out, in]; the model of this engine has no bias
+(crates/model/src/components/attention/gqa/norm.rs:21-26 of the reference), a part that
+has one passes `bias` and gives up the fusions with its neighbouring norms.
 
 The product runs in the precision of the stored weight: a bfloat16 weight on
 the tensor cores with float32 accumulation, a float32 weight through the true
@@ -13,17 +14,22 @@ from .base import ScaledRows, StreamSink
 
 
 class Linear:
-    def __init__(self, weight: torch.Tensor):
+    def __init__(self, weight: torch.Tensor, bias: torch.Tensor = None):
         if weight.dim() != 2 or not weight.is_contiguous():
             raise ValueError("a linear weight is a contiguous [out, in] matrix")
         self.weight = weight
         self.out_features, self.in_features = weight.shape
+        # a vector of out_features numbers: kept as float32 (exact from bfloat16) and added in float32
+        self.bias = None if bias is None else bias.to(device=weight.device, dtype=torch.float32).contiguous()
+        if self.bias is not None and tuple(self.bias.shape) != (self.out_features,):
+            raise ValueError(f"a linear bias has out_features={self.out_features} entries, got {tuple(bias.shape)}")
 
     def factors_norms(self, M) -> bool:
         """Whether, for M rows, this layer's kernel can take an RMS norm's output in factored form
         (`ScaledRows`) and can add its result into the stream (`into_stream`)."""
         from ..csrc import ops
-        return self.weight.dtype == torch.bfloat16 and ops.gemm_bf16_small_m_ok(M, self.in_features)
+        return (self.bias is None and self.weight.dtype == torch.bfloat16
+                and ops.gemm_bf16_small_m_ok(M, self.in_features))
 
     def into_stream(self, a, sink: StreamSink, step, tag) -> ScaledRows:
         """sink.x += a W^T; returns the next norm's output on the new stream, in factored form."""
@@ -41,6 +47,8 @@ class Linear:
         inside the product kernel when that kernel can, else in a kernel of its own."""
         from ..csrc import ops
         from . import matmul
+        if self.bias is not None and group:
+            raise ValueError("the fused gate/up layout has no bias; stack gate and up as plain halves (group 0)")
         if isinstance(a, ScaledRows):
             M = a.rows.shape[0]
             if group != ops.SWIGLU_GROUP or not self.factors_norms(M):
@@ -51,12 +59,19 @@ class Linear:
         M = a.shape[0]
         ws = step.workspace
         out = ws.get(step.tag + tag + ".act", (M, self.out_features // 2), a.dtype)
-        if (group == ops.SWIGLU_GROUP and self.weight.dtype == torch.bfloat16 and a.dtype == torch.bfloat16
-                and matmul.fuses_swiglu(M, self.in_features)):
+        if (group == ops.SWIGLU_GROUP and self.bias is None and self.weight.dtype == torch.bfloat16
+                and a.dtype == torch.bfloat16 and matmul.fuses_swiglu(M, self.in_features)):
             return matmul.gemm_bf16(a, self.weight, out, step.err, swiglu=True)
         return ops.silu_mul(self(a, step, tag), out, group)
 
     def __call__(self, a, step, tag, out_dtype=None):
+        y = self._product(a, step, tag, out_dtype)
+        if self.bias is not None:
+            from ..csrc import ops
+            ops.add_bias(y, self.bias)
+        return y
+
+    def _product(self, a, step, tag, out_dtype=None):
         from ..csrc import ops
         from . import matmul
         if isinstance(a, ScaledRows):

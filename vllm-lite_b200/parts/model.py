@@ -7,19 +7,18 @@ from __future__ import annotations
 import torch
 
 from .base import BuildContext, Residual, prefixed, sub_weights
-from .linear import Linear
-from .registry import BLOCKS, NORMS
+from .registry import BLOCKS, EMBEDDINGS, HEADS, NORMS
 from .spec import ModelPlan, TensorDecl
 
 
 def declare_model(plan: ModelPlan) -> dict:
     """Every tensor the model binds: {checkpoint name: TensorDecl}."""
-    d = {plan.embed_name: TensorDecl((plan.vocab_size, plan.hidden_size))}
+    emb, head = plan.embedding_spec, plan.head_spec
+    d = prefixed(EMBEDDINGS.get(emb.kind).declare(emb), plan.embed_prefix)
     for i, block in enumerate(plan.layers):
         d.update(prefixed(BLOCKS.get(block.kind).declare(block), plan.layer_prefix.format(i)))
     d.update(prefixed(NORMS.get(plan.final_norm.kind).declare(plan.final_norm), plan.final_norm_prefix))
-    if not plan.tie_word_embeddings:
-        d[plan.head_name] = TensorDecl((plan.vocab_size, plan.hidden_size))
+    d.update(prefixed(HEADS.get(head.kind).declare(head), plan.head_prefix))
     return d
 
 
@@ -38,21 +37,20 @@ class CausalLM:
         plan.validate()
         self.plan = plan
         self.ctx = ctx
-        self.embed_table = weights[plan.embed_name]
+        emb, head = plan.embedding_spec, plan.head_spec
+        self.embedding = EMBEDDINGS.get(emb.kind)(emb, sub_weights(weights, plan.embed_prefix), ctx)
         self.layers = [BLOCKS.get(b.kind)(b, sub_weights(weights, plan.layer_prefix.format(i)), ctx)
                        for i, b in enumerate(plan.layers)]
         self.final_norm = NORMS.get(plan.final_norm.kind)(plan.final_norm,
                                                           sub_weights(weights, plan.final_norm_prefix), ctx)
-        head = self.embed_table if plan.tie_word_embeddings else weights[plan.head_name]
-        self.head = Linear(head)
-        self.graph_safe = all(getattr(layer, "graph_safe", False) for layer in self.layers)
+        self.head = HEADS.get(head.kind)(head, sub_weights(weights, plan.head_prefix), ctx, embedding=self.embedding)
+        self.graph_safe = all(getattr(part, "graph_safe", False) for part in [self.embedding, self.head] + self.layers)
 
     def forward(self, step, caches) -> torch.Tensor:
         """Logits float32 [len(step.logit_rows), vocab]."""
-        from ..csrc import ops
         ws = step.workspace
         x = ws.get(step.tag + "residual", (step.num_tokens, self.plan.hidden_size), torch.float32)
-        ops.embed(step.tokens, self.embed_table, x, step.err)
+        self.embedding(step, x)
         residual = Residual(x)
         order = self.plan.order
         for i, (call, cache) in enumerate(zip(order, caches)):
@@ -68,4 +66,4 @@ class CausalLM:
         if R == 0:
             return ws.get(step.tag + "logits", (0, self.plan.vocab_size), torch.float32)
         h = self.final_norm(residual.x, residual.pending, step, rows=step.logit_rows, tag="final_norm")   # pending: the last block has no next norm
-        return self.head(h, step, "logits", out_dtype=torch.float32)
+        return self.head(h, step)

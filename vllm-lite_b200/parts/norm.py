@@ -23,6 +23,11 @@ class RmsNorm:
         # A vector of `size` numbers: kept as float32 on the device (exact from bfloat16).
         self.weight = weights["weight"].to(device=ctx.device, dtype=torch.float32).contiguous()
 
+    def fused_rms(self):
+        """(weight, eps): what a kernel that applies this norm itself needs (the attention mixer's
+        kernel norms every head while it rotates it)."""
+        return self.weight, self.spec.eps
+
     def __call__(self, x, delta, step, rows=None, tag="norm"):
         from ..csrc import ops
         R = x.shape[0] if rows is None else rows.shape[0]

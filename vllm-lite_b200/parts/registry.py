@@ -1,6 +1,7 @@
 """Registries from a description's `kind` to the class that implements it.
 
-Five families: mixers, feed-forwards, norms, position encodings and blocks.
+Seven families: mixers, feed-forwards, norms, position encodings, blocks, embeddings and
+output heads.
 A class of any family offers
 
     declare(spec) -> {relative tensor name: TensorDecl}      (static, CPU only)
@@ -46,3 +47,5 @@ FEED_FORWARDS = PartRegistry("feed-forward")
 NORMS = PartRegistry("norm")
 POSITIONS = PartRegistry("position encoding")
 BLOCKS = PartRegistry("block")
+EMBEDDINGS = PartRegistry("embedding")
+HEADS = PartRegistry("output head")

@@ -1,7 +1,7 @@
 """Descriptions of model parts as plain data.
 
 A model is a `ModelPlan`: an embedding, a list of layer descriptions, the order
-in which layers run, a final norm and an output head.  Every description is a
+in which layers run, a final norm and an output head (each of them a part).  Every description is a
 frozen dataclass whose `kind` names the implementation in the part registries
 (`parts.registry`); sizes and constants are fields, never code.  Layers may
 differ from one another, and `order` may name a layer twice or let a layer read
@@ -69,7 +69,26 @@ class AttentionSpec:
     position: Optional[RotarySpec] = None
     window: Optional[int] = None
     scale: Optional[float] = None
+    bias: bool = False              # q/k/v projections with a bias vector each (the output projection has none)
     kind: str = "gqa_attention"
+
+
+@dataclass(frozen=True)
+class EmbeddingSpec:
+    """Token ids to rows of the residual stream: x[t] = table[id[t]], no scaling."""
+    vocab_size: int
+    hidden_size: int
+    kind: str = "token_embedding"
+
+
+@dataclass(frozen=True)
+class HeadSpec:
+    """The output head: logits = h W^T in float32, no bias.  `tied`: W is the embedding's table
+    (the head then declares no tensor of its own)."""
+    vocab_size: int
+    hidden_size: int
+    tied: bool = False
+    kind: str = "linear_head"
 
 
 @dataclass(frozen=True)
@@ -112,12 +131,25 @@ class ModelPlan:
     tie_word_embeddings: bool
     max_position_embeddings: int
     layer_prefix: str = "model.layers.{}."
-    embed_name: str = "model.embed_tokens.weight"
+    embed_prefix: str = "model.embed_tokens."
     final_norm_prefix: str = "model.norm."
-    head_name: str = "lm_head.weight"
+    head_prefix: str = "lm_head."
     init_std: float = 0.02
     norm_init_std: float = 0.1
     extra: dict = field(default_factory=dict, compare=False, hash=False)
+    # The two ends of the model are parts like the layers' (registries EMBEDDINGS and HEADS).  Left None
+    # they are the plain ones, described by vocab_size, hidden_size and tie_word_embeddings.
+    embedding: Optional[object] = None
+    head: Optional[object] = None
+
+    @property
+    def embedding_spec(self):
+        return self.embedding if self.embedding is not None else EmbeddingSpec(self.vocab_size, self.hidden_size)
+
+    @property
+    def head_spec(self):
+        return self.head if self.head is not None else HeadSpec(self.vocab_size, self.hidden_size,
+                                                                tied=self.tie_word_embeddings)
 
     def validate(self) -> "ModelPlan":
         for i, call in enumerate(self.order):
