@@ -228,6 +228,53 @@ def continuous_run(engine, requests, vocab, prompt_range, out_len):
             "preemptions": engine.scheduler.stats["preemptions"]}
 
 
+def check_fp32(cfg, layers, tokens=1024):
+    """The whole model in true float32 at full depth: a prompt run whole, the same prompt cut into
+    portions of changing size beside another request's tokens, and its last tokens one by one must give
+    the same bits at every compared position (the float32 kernels add in an order that depends on
+    positions alone).  Prints one JSON line; exit code 0 only when every row is equal."""
+    import torch
+    from vllm_lite_b200.engine import ModelRunner, StepEntry, random_model
+    vocab = cfg["vocab_size"]
+    _, plan, weights = random_model(cfg, seed=0, dtype="float32", device="cuda:0", store_dtype=torch.float32)
+    runner = ModelRunner(plan, weights, dtype=torch.float32, device="cuda:0", page_size=16,
+                         num_pages=3 * (tokens // 16 + 2), max_requests=4, own_weights=True)
+    del weights
+    gen = torch.Generator().manual_seed(7)
+    toks = torch.randint(0, vocab, (tokens,), generator=gen).tolist()
+    other = torch.randint(0, vocab, (64,), generator=gen).tolist()
+    places = sorted({0, 1, 15, 16, 17, tokens // 3, tokens // 2} | set(range(tokens - 9, tokens)))
+    t0 = time.time()
+    whole = runner.step([StepEntry("w", toks, places)]).clone()
+    runner.release("w")
+    rows, fed, k, o = {}, 0, 0, 0
+    sizes = [299, 2, 17, 128, 1, 64, 3]
+    while fed < tokens - 8:
+        n = min(sizes[k % len(sizes)], tokens - 8 - fed)
+        k += 1
+        want = [p - fed for p in places if fed <= p < fed + n]
+        entries = [StepEntry("c", toks[fed:fed + n], want)]
+        if o < len(other):                              # another request's tokens share the step
+            m = 1 if k % 2 else 5
+            entries.insert(k % 2, StepEntry("o", other[o:o + m], []))
+            o += m
+        out = runner.step(entries)
+        for r, w in enumerate(want):
+            rows[fed + w] = out[r].clone()
+        fed += n
+    for p in range(tokens - 8, tokens):                 # the last tokens one by one (the decode path)
+        rows[p] = runner.step([StepEntry("c", [toks[p]], [0])])[0].clone()
+    runner.check_device_errors()
+    torch.cuda.synchronize()
+    unequal = [p for i, p in enumerate(places) if not torch.equal(rows[p], whole[i])]
+    worst = max(float((rows[p] - whole[i]).abs().max()) for i, p in enumerate(places))
+    print(json.dumps({"check": "float32, whole prompt against portions of changing size and single tokens",
+                      "model": f"{layers} layers, hidden {cfg['hidden_size']}, vocabulary {vocab}", "tokens": tokens,
+                      "rows_compared": len(places), "rows_equal_bit_for_bit": len(places) - len(unequal),
+                      "max_abs_difference": worst, "seconds": round(time.time() - t0, 1)}))
+    return 0 if not unequal else 1
+
+
 def main(argv=None):
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -246,6 +293,11 @@ def main(argv=None):
     ap.add_argument("--continuous", type=int, default=0, metavar="REQUESTS",
                     help="instead of the decode steps: continuous batching of this many requests through LLMEngine, prompts "
                          "uniform in [256, context/2], 512 generated tokens each (steps and warmup are not used)")
+    ap.add_argument("--kv-blocks", default=None, metavar="N|auto",
+                    help="pages of the cache: a count, or 'auto' = sized from the memory left after the weights (the "
+                         "default for --size 32b); default otherwise: what the largest batch needs at --context")
+    ap.add_argument("--check-fp32", action="store_true",
+                    help="instead of timing: the model in true float32, whole prompt against cut prompt, bit for bit")
     args = ap.parse_args(argv)
     if args.impl == "reference":
         return reference_arm()
@@ -263,6 +315,8 @@ def main(argv=None):
     cfg = dict(QWEN3_8B, num_hidden_layers=args.layers, hidden_size=hidden, num_attention_heads=heads,
                intermediate_size=inter)
     vocab = cfg["vocab_size"]
+    if args.check_fp32:
+        return check_fp32(cfg, args.layers)
     _, plan, weights = random_model(cfg, seed=0, dtype="bfloat16", device="cuda:0")
     if args.continuous:
         R, out_len, prompt_range = args.continuous, 512, (256, args.context // 2)
@@ -286,6 +340,10 @@ def main(argv=None):
         return 0
     big = args.batch if args.no_points else max(args.batch, 64)
     pages = big * (-(-args.context // 16) + 1) + PREFILL_TOKENS // 16 + 64
+    if args.kv_blocks == "auto" or (args.kv_blocks is None and args.size == "32b"):
+        pages = None                                      # the engine sizes the cache from what the weights leave
+    elif args.kv_blocks is not None:
+        pages = int(args.kv_blocks)
     engine = LLMEngine(plan=plan, weights=weights, dtype="bfloat16", kv_blocks=pages, block_size=16, max_batch_size=big,
                        max_num_batched_tokens=PREFILL_TOKENS, prefill_chunk_size=PREFILL_TOKENS,
                        max_model_len=args.context + 64)
@@ -320,7 +378,7 @@ def main(argv=None):
                    "head_dim": cfg["head_dim"], "intermediate": cfg["intermediate_size"], "vocab": vocab,
                    "global_batch": args.batch, "seq_len": args.context, "block_size": 16, "parallelism": "single GPU",
                    "kv_fill": "real prefill" if args.kv_fill == "prefill" else "random numbers", "l2": f"inputs (weights {weight_bytes / 1e9:.0f} GB) larger than L2, no flush",
-                   "peaks": pk["source"]},
+                   "peaks": pk["source"], "kv_pages": sum(p.size for p in runner.cache.pools)},
         "clocks": clocks.summary(w0, w1),
         "e2e": None if args.no_e2e else {"value": round(e2e_tps, 1), "unit": "tokens/s", "h2d_bytes_per_step": int(h2d),
                                          "d2h_bytes_per_step": d2h},

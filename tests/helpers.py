@@ -24,12 +24,20 @@ TINY_B = dict(architectures=["Qwen3ForCausalLM"], model_type="qwen3", hidden_siz
 TINY_C = dict(architectures=["Qwen3ForCausalLM"], model_type="qwen3", hidden_size=72, num_hidden_layers=2,
               num_attention_heads=6, num_key_value_heads=2, head_dim=64, intermediate_size=104, vocab_size=301,
               rope_theta=50000.0, rms_norm_eps=3e-6, tie_word_embeddings=False, max_position_embeddings=640)
-TINY = {"A": dict(config=TINY_A, seed=0, std=0.02, page_size=16),
+# a long context: decoding crosses the bounds (1,024, 2,048) that the decode graphs are recorded for
+TINY_L = dict(architectures=["Qwen3ForCausalLM"], model_type="qwen3", hidden_size=80, num_hidden_layers=2,
+              num_attention_heads=5, num_key_value_heads=1, head_dim=32, intermediate_size=112, vocab_size=199,
+              rope_theta=200000.0, rms_norm_eps=2e-6, tie_word_embeddings=True, max_position_embeddings=4096)
+TINY = {"L": dict(config=TINY_L, seed=4, std=0.05, page_size=16),
+        "A": dict(config=TINY_A, seed=0, std=0.02, page_size=16),
         "B": dict(config=TINY_B, seed=1, std=0.05, page_size=8),
         "C": dict(config=TINY_C, seed=2, std=0.04, page_size=16)}
 
-# max |engine - plain| allowed, as a fraction of max |plain| over the compared rows
-TOL = {"float32": 2e-5, "bfloat16": 4e-2}
+# max |engine - plain| allowed, as a fraction of max |plain| over the compared rows.  The run's summary
+# prints the worst error of every comparison (conftest.py); the worst ever seen were 1.4e-2 in bfloat16
+# and 7.5e-6 in float32 (both at real layer widths, sums over 12,288 products), so the bfloat16 bound
+# stands at twice that; float32 at tiny sizes stays below 1.3e-6.
+TOL = {"float32": 2e-5, "bfloat16": 2.8e-2}
 
 _tmp_root = None
 
@@ -86,12 +94,12 @@ def plain_logits(which: str, tokens, dtype="bfloat16") -> torch.Tensor:
     return _plain_cache[key]
 
 
-def make_runner(which: str, dtype: str, num_pages: int, page_size=None, max_requests=8, native_host=True):
+def make_runner(which: str, dtype: str, num_pages: int, page_size=None, max_requests=8, native_host=True, **kw):
     from vllm_lite_b200.engine import ModelRunner, load_model_dir
     _, plan, weights = load_model_dir(model_dir(which, dtype), dtype, "cuda:0")
     return ModelRunner(plan, weights, dtype=torch.bfloat16 if dtype == "bfloat16" else torch.float32,
                        device="cuda:0", page_size=page_size or TINY[which]["page_size"], num_pages=num_pages,
-                       max_requests=max_requests, native_host=native_host)
+                       max_requests=max_requests, native_host=native_host, **kw)
 
 
 def run_schedule(runner, schedule):

@@ -13,7 +13,9 @@ def test_flags_carry_the_reference_names_defaults_and_environment(monkeypatch):
     for name in ("VLLM_MODEL", "VLLM_KV_BLOCKS", "VLLM_MAX_BATCH_SIZE", "VLLM_MAX_MODEL_LEN"):
         monkeypatch.delenv(name, raising=False)
     args = cli.build_parser().parse_args(["-m", "/x"])
-    assert (args.model, args.kv_blocks, args.max_batch_size, args.max_model_len) == ("/x", 1024, 256, None)
+    # no --kv-blocks: the cache is sized from the GPU (the reference's default of 1,024 pages is not kept)
+    assert (args.model, args.kv_blocks, args.max_batch_size, args.max_model_len) == ("/x", None, 256, None)
+    assert args.gpu_memory_fraction == 0.9
     assert (args.tensor_parallel_size, args.kv_quantization, args.temperature, args.max_tokens) == (1, False, 0.0, 16)
     monkeypatch.setenv("VLLM_MODEL", "/from/env")
     monkeypatch.setenv("VLLM_KV_BLOCKS", "77")

@@ -180,3 +180,19 @@ def test_command_line(tmp_path):
     bad = subprocess.run([sys.executable, "-m", "vllm_lite_b200", "--prompt-ids", "1,2"], capture_output=True, text=True,
                          cwd=ROOT, env={k: v for k, v in __import__("os").environ.items() if k != "VLLM_MODEL"})
     assert bad.returncode == 2 and "--model" in bad.stderr
+
+
+def test_stats_report_step_counts_and_times_by_kind():
+    which = "B"
+    eng = engine(which, dtype="bfloat16", max_num_batched_tokens=32, prefill_chunk_size=16)
+    eng.generate([H.tokens_for(which, 40, 400), H.tokens_for(which, 9, 401)], max_tokens=40)
+    times = eng.stats()["step_times"]
+    assert set(times) == {"prompt", "mixed", "decode"}
+    assert times["prompt"]["steps"] >= 1 and times["decode"]["steps"] >= 30
+    assert times["prompt"]["steps"] + times["mixed"]["steps"] + times["decode"]["steps"] >= 40
+    d = times["decode"]
+    assert d["host_ms_p50"] is not None and 0 < d["host_ms_p50"] <= d["host_ms_p90"]
+    torch.cuda.synchronize()
+    sampled = sum(t["device_samples"] for t in eng.stats()["step_times"].values())
+    assert sampled >= 2                                     # every 16th step is timed on the device
+    assert all(t["device_ms_p50"] is None or t["device_ms_p50"] > 0 for t in eng.stats()["step_times"].values())

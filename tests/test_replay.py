@@ -219,34 +219,134 @@ def test_trace_run_program(dtype, tmp_path):
             assert err <= H.TOL[dtype], (step, pos, err)
 
 
-def test_real_layer_sizes_bfloat16_against_float32_engine():
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_real_layer_sizes_against_the_plain_implementation(dtype):
     """Two layers of Qwen3-8B width (hidden 4096, 32/8 heads of 128, intermediate 12288) with a small
-    vocabulary: a prompt long enough for the tcgen05 GEMM and the tensor-core attention, then decoded
-    tokens through the CUDA-graph path.  The float32 engine (bit-identical across cuts, checked against
-    the plain implementation at tiny sizes) is the reference for the bfloat16 engine here."""
+    vocabulary, against the plain implementation on the CPU: a prompt of 1,100 tokens whole (the tcgen05
+    products, one SM and paired, and the tcgen05 attention at head size 128 in bfloat16), the same prompt
+    cut 700 + 400, then 30 tokens one by one (the weight-streaming products with the norms folded in,
+    through the graph).  The float32 engine holds weights with all their bits."""
+    import plain_qwen3 as P
     from vllm_lite_b200.engine import ModelRunner, StepEntry, random_model
     cfg = dict(architectures=["Qwen3ForCausalLM"], model_type="qwen3", hidden_size=4096, num_hidden_layers=2,
                num_attention_heads=32, num_key_value_heads=8, head_dim=128, intermediate_size=12288, vocab_size=2048,
                rope_theta=1000000.0, rms_norm_eps=1e-6, tie_word_embeddings=False, max_position_embeddings=4096)
     toks = [int(t) for t in np.random.default_rng(5).integers(0, 2048, size=1130)]
-    rows = {}
-    for dtype in ("float32", "bfloat16"):
-        _, plan, weights = random_model(cfg, seed=3, dtype=dtype, device="cuda:0")
-        runner = ModelRunner(plan, weights, dtype=torch.float32 if dtype == "float32" else torch.bfloat16,
-                             device="cuda:0", page_size=16, num_pages=160, max_requests=2)
-        del weights
-        out = [runner.step([StepEntry("r", toks[:1100], [0, 63, 64, 1023, 1099])]).float().cpu()]
-        if dtype == "float32":                          # the same prompt cut in two gives the same bits
-            again = runner.step([StepEntry("s", toks[:700], [0, 63, 64])]).float().cpu()
-            again2 = runner.step([StepEntry("s", toks[700:1100], [323, 399])]).float().cpu()
-            assert torch.equal(torch.cat([again, again2]), out[0])
-            runner.release("s")
-        for p in range(1100, 1130):
-            out.append(runner.step([StepEntry("r", [toks[p]], [0])]).float().cpu())
-        runner.check_device_errors()
-        rows[dtype] = torch.cat(out)
-        del runner
-        torch.cuda.empty_cache()
-    ref, got = rows["float32"], rows["bfloat16"]
-    err = (got - ref).abs().amax(dim=1) / ref.abs().amax(dim=1)
-    assert float(err.max()) <= H.TOL["bfloat16"], err
+    store = torch.float32 if dtype == "float32" else torch.bfloat16
+    # the tensors a folder written with this seed would hold (tests/test_weights.py checks that they are)
+    _, plan, weights = random_model(cfg, seed=3, dtype=dtype, device="cuda:0", store_dtype=store)
+    ref = P.forward(cfg, {k: v.float().cpu() for k, v in weights.items()}, toks)
+    runner = ModelRunner(plan, weights, dtype=store, device="cuda:0", page_size=16, num_pages=160, max_requests=2)
+    del weights
+    whole_places = [0, 63, 64, 700, 1023, 1099]
+    whole = runner.step([StepEntry("r", toks[:1100], whole_places)]).float().cpu()
+    first = runner.step([StepEntry("s", toks[:700], [0, 63, 64])]).float().cpu()
+    second = runner.step([StepEntry("s", toks[700:1100], [0, 323, 399])]).float().cpu()
+    runner.release("s")
+    cut = torch.cat([first, second])
+    if dtype == "float32":                              # the same prompt cut in two gives the same bits
+        assert torch.equal(cut, whole)
+    decoded = [runner.step([StepEntry("r", [toks[p]], [0])]).float().cpu() for p in range(1100, 1130)]
+    runner.check_device_errors()
+    assert runner.graph_replays >= 28
+    got = torch.cat([whole, cut] + decoded)
+    want = ref[whole_places + whole_places + list(range(1100, 1130))]
+    err = (got - want).abs().amax(dim=1) / want.abs().amax(dim=1)
+    key = ("real layer sizes", "8B x 2 layers", dtype)
+    H.WORST[key] = max(H.WORST.get(key, 0.0), float(err.max()))
+    assert float(err.max()) <= H.TOL[dtype], err
+    del runner
+    torch.cuda.empty_cache()
+
+
+@pytest.mark.parametrize("live", [12, 33, 70])
+@pytest.mark.parametrize("which,dtype", [(w, d) for w in ("B", "C") for d in ("float32", "bfloat16")])
+def test_many_requests_decode_in_one_step(which, dtype, live):
+    """Decode steps of more than 8 requests: the batch is padded to 16, 64 or 128 places and replayed
+    from a graph, the bfloat16 products of that many rows run in the library, and the decode attention
+    picks other chunk sizes.  The requests' prompts are of unequal length and arrive several to a step,
+    on pages that earlier requests held; then every request decodes, all in one step, six times."""
+    ps = H.TINY[which]["page_size"]
+    lens = [3 + (7 * i) % 41 for i in range(live)]
+    decoded = 6
+    reqs = {i: H.tokens_for(which, lens[i] + decoded, 500 + i) for i in range(live)}
+    need = sum(-(-(n + decoded) // ps) for n in lens)
+    runner = H.make_runner(which, dtype, num_pages=need, max_requests=live)
+    # earlier requests take every page once and give it back, so that the pages are used again
+    fill, taken = [], 0
+    while taken + 5 <= need:
+        fill.append((f"x{len(fill)}", H.tokens_for(which, 5 * ps, 900 + len(fill)), []))
+        taken += 5
+    schedule = [(fill[k:k + 4], [f[0] for f in fill[k:k + 4]]) for k in range(0, len(fill), 4)]
+    # prompts, seven to a step
+    fed = {}
+    for k in range(0, live, 7):
+        entries = [(i, reqs[i][:lens[i]], [lens[i] - 1]) for i in range(k, min(k + 7, live))]
+        schedule.append((entries, []))
+    for i in range(live):
+        fed[i] = lens[i]
+    for _ in range(decoded):
+        schedule.append(([(i, [reqs[i][fed[i]]], [0]) for i in range(live)], []))
+        for i in range(live):
+            fed[i] += 1
+    schedule[-1] = (schedule[-1][0], list(range(live)))
+    before = runner.graph_replays
+    rows = H.run_schedule(runner, schedule)
+    assert len(rows) == live * (decoded + 1)
+    assert runner.graph_replays - before >= decoded - 1          # the decode steps ran from the graph of their bucket
+    assert any(k[0] == (16 if live == 12 else 64 if live == 33 else 128) for k in runner._graphs)
+    H.assert_rows_match(rows, which, reqs, dtype, f"{live} requests decoding")
+    assert runner.cache.free_pages() == [need]
+
+
+@pytest.mark.parametrize("ahead", [False, True])
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_decoding_across_the_context_bounds_of_the_graphs(dtype, ahead):
+    """Decode graphs are recorded for a bound on the context (1,024, 2,048, ... up to the longest the
+    runner takes).  A request decodes across 1,024 and across 2,048 beside a short one: the step picks
+    the graph of the next bound when a request passes one, and a step launched ahead (its tokens still on
+    the device) is refused while no graph for the new bound exists, and taken afterwards."""
+    from vllm_lite_b200.engine import StepEntry
+    which = "L"
+    toks = H.tokens_for(which, 2075, 61)
+    short = H.tokens_for(which, 70, 62)
+    runner = H.make_runner(which, dtype, num_pages=-(-2075 // 16) + 6, max_requests=4, max_context=4096)
+    rows, refused, taken = {}, 0, 0
+
+    def keep(out, places):
+        out = out.float().cpu()
+        for r, (rid, pos) in enumerate(places):
+            rows[(rid, pos)] = out[r].clone()
+
+    def decode(lo, hi, s_at):
+        """tokens lo..hi-1 of the long request one by one, the short request's beside them"""
+        nonlocal refused, taken
+        for k, p in enumerate(range(lo, hi)):
+            ids, places = ["r", "s"], [("r", p), ("s", s_at + k)]
+            feed = [toks[p], short[s_at + k]]
+            out = None
+            if ahead and k > 0:
+                src = torch.tensor(feed, dtype=torch.int32, device="cuda:0")
+                out = runner.step_ahead(ids, src, p + 1)
+                refused += out is None
+                taken += out is not None
+            if out is None:
+                out = runner.step([StepEntry(i, [t], [0]) for i, t in zip(ids, feed)])
+            keep(out, places)
+            runner.check_device_errors()
+        return s_at + (hi - lo)
+
+    keep(runner.step([StepEntry("r", toks[:1015], [1014]), StepEntry("s", short[:5], [4])]), [("r", 1014), ("s", 4)])
+    s_at = decode(1015, 1040, 5)                       # passes 1,024
+    keep(runner.step([StepEntry("r", toks[1040:2040], [999])]), [("r", 2039)])
+    s_at = decode(2040, 2075, s_at)                    # passes 2,048
+    bounds = sorted(k[1] for k in runner._graphs if k[0] == 2)
+    assert bounds == [1024, 2048, 4096], bounds
+    if ahead:
+        assert refused == 2 and taken == 25 + 35 - 2 - 2      # refused once at each bound passed
+    H.assert_rows_match(rows, which, {"r": toks, "s": short}, dtype, "across context bounds" + (", ahead" if ahead else ""))
+    # a step launched ahead with too small a bound changes nothing
+    before = runner.cached_tokens("r")
+    assert runner.step_ahead(["r", "s"], torch.zeros(2, dtype=torch.int32, device="cuda:0"), before) is None
+    assert runner.cached_tokens("r") == before
+    runner.cache.check_invariants()

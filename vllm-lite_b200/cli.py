@@ -5,8 +5,9 @@
 
 Flags that the reference's server has keep its names, defaults and environment
 variables (crates/server/src/cli/args.rs:144-186): `--model/-m` is required
-(VLLM_MODEL) and is a local folder that is never downloaded, `--kv-blocks` (1024,
-VLLM_KV_BLOCKS), `--max-batch-size` (256, VLLM_MAX_BATCH_SIZE), `--max-model-len`
+(VLLM_MODEL) and is a local folder that is never downloaded, `--kv-blocks` (VLLM_KV_BLOCKS; the
+reference's default is 1024, here the cache is sized from the GPU's free memory when the flag
+is absent, under `--gpu-memory-fraction`), `--max-batch-size` (256, VLLM_MAX_BATCH_SIZE), `--max-model-len`
 (VLLM_MAX_MODEL_LEN), `--tensor-parallel-size` (1) and `--kv-quantization`
 (false), which are accepted only at those values because the engine runs on one
 GPU with an unquantized cache, and `--log-level`.  The server's network and
@@ -47,7 +48,11 @@ def build_parser() -> argparse.ArgumentParser:
     init.add_argument("--std", type=float, default=None, help="standard deviation of the matrices (default 0.02)")
 
     ap.add_argument("--model", "-m", default=_env("VLLM_MODEL"), help="model folder (config.json + safetensors)")
-    ap.add_argument("--kv-blocks", type=_bounded(1, 1 << 24, "--kv-blocks"), default=int(_env("VLLM_KV_BLOCKS", 1024)))
+    ap.add_argument("--kv-blocks", type=_bounded(1, 1 << 24, "--kv-blocks"),
+                    default=(int(_env("VLLM_KV_BLOCKS")) if _env("VLLM_KV_BLOCKS") else None),
+                    help="pages of the cache; without it the cache is sized from the GPU's free memory")
+    ap.add_argument("--gpu-memory-fraction", type=float, default=0.9,
+                    help="share of the memory free after loading that cache and activations may take (no --kv-blocks)")
     ap.add_argument("--max-batch-size", type=_bounded(1, 4096, "--max-batch-size"),
                     default=int(_env("VLLM_MAX_BATCH_SIZE", 256)))
     ap.add_argument("--max-model-len", type=_bounded(1, 4_000_000, "--max-model-len"),
@@ -109,7 +114,8 @@ def main(argv=None) -> int:
     t0 = time.time()
     engine = LLMEngine(args.model, dtype=args.dtype, kv_blocks=args.kv_blocks, block_size=args.block_size,
                        max_batch_size=args.max_batch_size, max_num_batched_tokens=args.max_num_batched_tokens,
-                       prefill_chunk_size=args.prefill_chunk_size, max_model_len=args.max_model_len)
+                       prefill_chunk_size=args.prefill_chunk_size, max_model_len=args.max_model_len,
+                       gpu_memory_fraction=args.gpu_memory_fraction)
     if verbose:
         print(f"[vllm-lite_b200] model loaded in {time.time() - t0:.1f} s", file=sys.stderr)
     params = SamplingParams(temperature=args.temperature, top_k=args.top_k, top_p=args.top_p,

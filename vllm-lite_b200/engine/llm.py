@@ -10,6 +10,8 @@ integers on both sides; the engine has no tokenizer.
 """
 from __future__ import annotations
 
+import time
+from contextlib import contextmanager
 from dataclasses import dataclass
 from typing import Dict, List, Optional, Sequence as Seq
 
@@ -21,10 +23,80 @@ from .runner import ModelRunner, StepEntry
 from .scheduler import Scheduler, SchedulerConfig, Sequence
 
 
+@contextmanager
+def _span(name: str):
+    """A named range on the profiler's timeline (NVTX), as the reference wraps the phases of a step in
+    tracing spans (crates/core/src/scheduler/engine/state/batch.rs:23-28).  Costs nothing when no
+    profiler listens."""
+    torch.cuda.nvtx.range_push(name)
+    try:
+        yield
+    finally:
+        torch.cuda.nvtx.range_pop()
+
+
+class StepTimes:
+    """Host time of every `step()` by kind, and device time of every N-th step (events on the stream;
+    read only once they have completed, so that steps launched ahead are never waited for)."""
+    KINDS = ("prompt", "mixed", "decode")
+
+    def __init__(self, device_every: int = 16, keep: int = 4096):
+        self.device_every, self.keep = int(device_every), int(keep)
+        self.host_ms = {k: [] for k in self.KINDS}
+        self.device_ms = {k: [] for k in self.KINDS}
+        self.count = {k: 0 for k in self.KINDS}
+        self._pending = []
+
+    @staticmethod
+    def kind_of(plan) -> str:
+        prompt = any(e.count > 1 or not e.samples for e in plan.entries)
+        single = any(e.count == 1 and e.samples for e in plan.entries)
+        return "mixed" if prompt and single else "prompt" if prompt else "decode"
+
+    def host(self, kind: str, ms: float):
+        self.count[kind] += 1
+        self._add(self.host_ms[kind], ms)
+
+    def _add(self, where, ms):
+        where.append(ms)
+        if len(where) > self.keep:
+            del where[:len(where) - self.keep]
+
+    def wants_device_time(self) -> bool:
+        return self.device_every > 0 and sum(self.count.values()) % self.device_every == 0
+
+    def device(self, kind, start, end):
+        self._pending.append((kind, start, end))
+
+    def harvest(self):
+        still = []
+        for kind, start, end in self._pending:
+            if end.query():
+                self._add(self.device_ms[kind], start.elapsed_time(end))
+            else:
+                still.append((kind, start, end))
+        self._pending = still
+
+    @staticmethod
+    def _quantile(values, q):
+        v = sorted(values)
+        return round(v[min(len(v) - 1, int(q * len(v)))], 4) if v else None
+
+    def summary(self) -> dict:
+        self.harvest()
+        out = {}
+        for k in self.KINDS:
+            out[k] = {"steps": self.count[k],
+                      "host_ms_p50": self._quantile(self.host_ms[k], 0.5), "host_ms_p90": self._quantile(self.host_ms[k], 0.9),
+                      "device_ms_p50": self._quantile(self.device_ms[k], 0.5),
+                      "device_ms_p90": self._quantile(self.device_ms[k], 0.9), "device_samples": len(self.device_ms[k])}
+        return out
+
+
 class _InFlight:
     """A launched step whose tokens the host has not read yet."""
     def __init__(self, plan, sampling):
-        self.plan, self.sampling = plan, sampling
+        self.plan, self.sampling, self.kind = plan, sampling, "decode"
         self.event = self.tokens_device = self.host_tokens = self.host_logprobs = None
 
 
@@ -38,15 +110,18 @@ class StepOutput:
 
 
 class LLMEngine:
-    def __init__(self, model=None, *, dtype="bfloat16", device="cuda:0", kv_blocks: int = 1024, block_size: int = 16,
-                 max_batch_size: int = 256, max_num_batched_tokens: int = 4096, prefill_chunk_size: int = 512,
-                 max_model_len: Optional[int] = None, plan=None, weights=None, logprobs: bool = False,
-                 lookahead: bool = True):
+    def __init__(self, model=None, *, dtype="bfloat16", device="cuda:0", kv_blocks: Optional[int] = None,
+                 block_size: int = 16, max_batch_size: int = 256, max_num_batched_tokens: int = 4096,
+                 prefill_chunk_size: int = 512, max_model_len: Optional[int] = None, plan=None, weights=None,
+                 logprobs: bool = False, lookahead: bool = True, gpu_memory_fraction: float = 0.9):
         """`model`: a folder with config.json and safetensors (never downloaded).  `kv_blocks`
-        and `max_batch_size` carry the reference's names and defaults
-        (crates/server/src/cli/args.rs:155-186); `block_size` is its BLOCK_SIZE constant
-        (crates/traits/src/types.rs:13) made an option.  Alternatively pass `plan` and
-        `weights` of a model that is already on the device.  `lookahead`: see `step`."""
+        and `max_batch_size` carry the reference's names (crates/server/src/cli/args.rs:155-186);
+        `block_size` is its BLOCK_SIZE constant (crates/traits/src/types.rs:13) made an option.
+        `kv_blocks=None` (the default here; the reference's is 1,024) sizes the cache from the GPU:
+        `gpu_memory_fraction` of the memory that is free once the weights are resident, less a
+        reserve for activations (cache/sizing.py).  Alternatively pass `plan` and `weights` of a
+        model that is already on the device; the engine takes the dict over and empties it.
+        `lookahead`: see `step`."""
         self.dtype = parse_dtype(dtype)
         if plan is None:
             if model is None:
@@ -55,7 +130,10 @@ class LLMEngine:
         if max_model_len is None:
             max_model_len = plan.max_position_embeddings
         self.runner = ModelRunner(plan, weights, dtype=self.dtype, device=device, page_size=block_size,
-                                  num_pages=kv_blocks, max_requests=max_batch_size, max_context=max_model_len)
+                                  num_pages=kv_blocks, max_requests=max_batch_size, max_context=max_model_len,
+                                  memory_fraction=gpu_memory_fraction, max_step_tokens=max_num_batched_tokens,
+                                  own_weights=True)
+        del weights
         self.scheduler = Scheduler(self.runner.cache, SchedulerConfig(
             max_num_seqs=max_batch_size, max_num_batched_tokens=max_num_batched_tokens,
             prefill_chunk_size=prefill_chunk_size, max_model_len=max_model_len))
@@ -67,6 +145,7 @@ class LLMEngine:
         self._slot = 0
         self._host_tok = [None, None]           # pinned read-back buffers of the two steps that can be in flight
         self._host_lp = [None, None]
+        self.times = StepTimes()
 
     # ---- requests -----------------------------------------------------------
     def add_request(self, prompt: Seq[int], max_tokens: int, sampling_params: SamplingParams = None) -> int:
@@ -98,22 +177,41 @@ class LLMEngine:
         option needs the token on the host (penalties, biases).  Its input tokens then stay on the
         device.  A request that turns out to have ended (stop sequence, cancel) has cost one token
         of work that is thrown away."""
+        t0 = time.perf_counter()
         if self._ahead is None:
-            plan = self.scheduler.schedule()
+            with _span("schedule"):
+                plan = self.scheduler.schedule()
             if not plan.entries:
                 return []
             self._ahead = self._launch(plan)
         current, self._ahead = self._ahead, None
         if self.lookahead:
-            self._ahead = self._launch_following(current)
-        return self._collect(current)
+            with _span("launch ahead"):
+                self._ahead = self._launch_following(current)
+        with _span("collect"):
+            out = self._collect(current)
+        self.times.host(current.kind, (time.perf_counter() - t0) * 1e3)
+        return out
 
     def _launch(self, plan) -> "_InFlight":
         entries = [StepEntry(e.seq.seq_id, e.seq.tokens[e.start:e.start + e.count],
                              [e.count - 1] if e.samples else []) for e in plan.entries]
-        logits = self.runner.step(entries)
+        kind = StepTimes.kind_of(plan)
+        timed = self.times.wants_device_time()
+        if timed:
+            start = torch.cuda.Event(enable_timing=True)
+            start.record()
+        with _span("pack and launch " + kind):
+            logits = self.runner.step(entries)
         sampling = [e for e in plan.entries if e.samples]
-        return self._sample(plan, sampling, logits, [len(e.seq.generated) for e in sampling])
+        with _span("sample"):
+            flight = self._sample(plan, sampling, logits, [len(e.seq.generated) for e in sampling])
+        flight.kind = kind
+        if timed:
+            end = torch.cuda.Event(enable_timing=True)
+            end.record()
+            self.times.device(kind, start, end)
+        return flight
 
     def _sample(self, plan, sampling, logits, steps) -> "_InFlight":
         """Queues sampling and the copy of the tokens to pinned host memory; nothing waits here."""
@@ -150,13 +248,22 @@ class LLMEngine:
                 return None
             steps.append(produced)
         longest = max(e.start + e.count for e in entries) + 1
+        timed = self.times.wants_device_time()
+        if timed:
+            start = torch.cuda.Event(enable_timing=True)
+            start.record()
         logits = self.runner.step_ahead([e.seq.seq_id for e in entries], current.tokens_device, longest)
         if logits is None:
             return None
         from .scheduler import Scheduled, StepPlan
         plan = StepPlan()
         plan.entries = [Scheduled(e.seq, e.start + e.count, 1, True) for e in entries]
-        return self._sample(plan, plan.entries, logits, steps)
+        flight = self._sample(plan, plan.entries, logits, steps)
+        if timed:
+            end = torch.cuda.Event(enable_timing=True)
+            end.record()
+            self.times.device("decode", start, end)
+        return flight
 
     def _collect(self, flight: "_InFlight") -> List[StepOutput]:
         plan = flight.plan
@@ -195,8 +302,12 @@ class LLMEngine:
         return [list(seq.generated) for seq in seqs]
 
     def stats(self) -> dict:
+        """Counters of the scheduler, the state of the pools and queues, and step times by kind of step
+        (`prompt`: portions only, `decode`: single tokens only, `mixed`): how many, the median and the
+        90th percentile of the host time of `step()` and, for every 16th step, of the time on the device."""
         s = dict(self.scheduler.stats)
         s["free_pages"] = self.runner.cache.free_pages()
         s["running"] = len(self.scheduler.running)
         s["waiting"] = len(self.scheduler.waiting)
+        s["step_times"] = self.times.summary()
         return s

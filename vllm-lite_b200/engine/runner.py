@@ -67,7 +67,14 @@ def _pow2_at_least(n: int, floor: int = 1) -> int:
 class ModelRunner:
     def __init__(self, plan, weights: dict, *, dtype=torch.bfloat16, device="cuda:0", page_size: int = 16,
                  num_pages=1024, max_requests: int = 256, decode_graphs: bool = True,
-                 max_context: Optional[int] = None, native_host: bool = True):
+                 max_context: Optional[int] = None, native_host: bool = True, memory_fraction: float = 0.9,
+                 max_step_tokens: int = 4096, own_weights: bool = False, free_memory_bytes: Optional[int] = None):
+        """`num_pages`: pages of every paged group (an int, or one count per group), or None: the pools are
+        then sized from the device memory that is free once the model is built (`memory_fraction` of it,
+        less a reserve for the activations of steps of up to `max_step_tokens` tokens; cache/sizing.py).
+        `own_weights`: the dict is emptied once the model holds its tensors, so that what the model stacked
+        into new matrices (q/k/v, gate/up) is freed before memory is measured.  `free_memory_bytes` stands
+        in for the measurement (tests)."""
         self.device = torch.device(device)
         if self.device.type != "cuda":
             raise StepError("the engine runs on a CUDA device only; there is no CPU path")
@@ -79,6 +86,21 @@ class ModelRunner:
         torch.cuda.set_device(self.device)
         self.model = CausalLM(plan, weights, BuildContext(self.device, dtype))
         self.layout = CacheLayout.from_needs(cache_needs(plan), [c.cache_of for c in plan.order])
+        self.max_context = int(max_context or plan.max_position_embeddings)
+        if own_weights:
+            weights.clear()
+        self.sized_from_memory = None
+        if num_pages is None:
+            from ..cache.sizing import activation_reserve, pages_from_memory
+            itemsize = 2 if dtype == torch.bfloat16 else 4
+            if free_memory_bytes is None:
+                torch.cuda.empty_cache()
+                free_memory_bytes = torch.cuda.mem_get_info(self.device)[0]
+            reserve = activation_reserve(plan, max_step_tokens, max_requests, self.max_context, itemsize)
+            num_pages = pages_from_memory(self.layout, self.page_size, itemsize, free_memory_bytes, memory_fraction,
+                                          reserve, max_requests, self.max_context, max_step_tokens)
+            self.sized_from_memory = dict(free_bytes=int(free_memory_bytes), fraction=memory_fraction,
+                                          reserve_bytes=reserve, pages=list(num_pages))
         # bookkeeping and batch packing in C++ (csrc/host/cache_core.cpp); the Python manager is the reference
         self.native_host = bool(native_host)
         self.cache = make_cache_manager(self.layout, self.page_size, num_pages, max_requests, native=self.native_host)
@@ -93,7 +115,6 @@ class ModelRunner:
         # Decode-only steps (one token per request) are replayed from CUDA graphs, one per
         # batch-size bucket, when every part of the model launches only stream-ordered kernels.
         self.decode_graphs = bool(decode_graphs) and getattr(self.model, "graph_safe", False)
-        self.max_context = int(max_context or plan.max_position_embeddings)
         self._graphs = {}
         self._graph_meta = {}
         self.graph_replays = 0
