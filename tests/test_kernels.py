@@ -432,8 +432,7 @@ def run_attention(kernel, qkv, out, kc, vc, table, req, pos, nq, nkv, hd, scale,
         stream = kernel.endswith("tma")         # "...tma": the persistent TMA kernel, else a block per chunk;
         own = kernel.endswith("own")            # "...own": the chunks are merged by the kernel's last block
         kernel = kernel[:-3] if stream or own else kernel
-        if stream and not ops().flash_tc5_supported(qkv.dtype, hd, kc.shape[2]):
-            pytest.skip("the TMA kernel does not take this head or page size")
+        assert not stream or ops().flash_tc5_supported(qkv.dtype, hd, kc.shape[2]), "a case the TMA kernel does not take"
         chunk = int(kernel[len("flash_decode"):] or 256)
         S, n_acc, n_ml = ops().decode_attention_scratch(qkv.shape[0], nq, hd, ctx, chunk)
         pa = torch.full((n_acc,), float("nan"), device=DEV)
@@ -458,11 +457,24 @@ def attention_cases():
             ("flash_prefill", torch.bfloat16)]
 
 
-@pytest.mark.parametrize("kernel,dtype", [c for c in attention_cases() if c[0] != "paged"])
-@pytest.mark.parametrize("nq,nkv,hd,page,window", [(6, 2, 48, 4, 0), (5, 5, 16, 16, 0), (32, 8, 128, 16, 0),
-                                                   (3, 1, 80, 8, 300), (16, 2, 256, 32, 0), (7, 1, 64, 16, 0),
-                                                   (40, 2, 32, 16, 0), (20, 1, 128, 64, 500), (4, 2, 64, 8, 0),
-                                                   (6, 3, 128, 128, 0)])
+def decode_split_cases():
+    """Every decode kernel at every shape it takes: the persistent TMA kernel is listed only with the
+    head and page sizes it is built for (head size 64 or 128, pages of 8, 16, 32 or a multiple of 64)."""
+    from vllm_lite_b200.csrc.ops import flash_tc5_supported
+    shapes = [(6, 2, 48, 4, 0), (5, 5, 16, 16, 0), (32, 8, 128, 16, 0), (3, 1, 80, 8, 300), (16, 2, 256, 32, 0),
+              (7, 1, 64, 16, 0), (40, 2, 32, 16, 0), (20, 1, 128, 64, 500), (4, 2, 64, 8, 0), (6, 3, 128, 128, 0)]
+    cases = []
+    for kernel, dtype in attention_cases():
+        if kernel == "paged":
+            continue
+        for nq, nkv, hd, page, window in shapes:
+            if kernel.endswith("tma") and not flash_tc5_supported(dtype, hd, page):
+                continue
+            cases.append((kernel, dtype, nq, nkv, hd, page, window))
+    return cases
+
+
+@pytest.mark.parametrize("kernel,dtype,nq,nkv,hd,page,window", decode_split_cases())
 def test_decode_attention_split(kernel, dtype, nq, nkv, hd, page, window):
     """Single tokens of requests of very different lengths (one token, a chunk's edge, several
     chunks), pages shuffled; a padded token at position -1 yields zeros."""
