@@ -8,7 +8,9 @@ given batch, timed on the device with CUDA events (weights, 16 GB, are far large
 L2, so every step reads them from HBM).  `e2e` is the same metric through the Python
 entry point (`LLMEngine.step`): host token ids in through pinned memory, sampled ids
 back to the host, every step.  `prefill` is one 2,048-token prompt, `points` are decode
-at batch 1 and 64, `roofline` relates the decode step to the bytes it must read.
+at batch 1 and 64 and `prefill_default`, the same prompt through `LLMEngine` with the scheduler's default
+limits (tokens per second to the first token, wall clock); `roofline` relates the decode step to the bytes
+it must read.
 Weights are random (seeded), prompts are seeded uniform token ids.
 """
 from __future__ import annotations
@@ -163,6 +165,35 @@ def prefill_run(runner, vocab, repeats=3):
             times.append(t0.elapsed_time(t1))
     times.sort()
     return times[len(times) // 2]
+
+
+def prefill_default_run(engine, vocab, repeats=3):
+    """What a user gets for one 2,048-token prompt: through LLMEngine with the scheduler's default limits
+    (4,096 tokens a step, portions of 512 beside decoding requests), host ids in, the first token out.
+    Returns tokens per second (median of `repeats` after one warm-up run)."""
+    import torch
+    cfg = engine.scheduler.config
+    saved = (cfg.max_num_batched_tokens, cfg.prefill_chunk_size)
+    cfg.max_num_batched_tokens, cfg.prefill_chunk_size = 4096, 512
+    gen = torch.Generator().manual_seed(77)
+    times = []
+    try:
+        for r in range(repeats + 1):
+            prompt = torch.randint(0, vocab, (PREFILL_TOKENS,), generator=gen).tolist()
+            torch.cuda.synchronize()
+            t0 = time.perf_counter()
+            engine.add_request(prompt, max_tokens=1)
+            out = []
+            while engine.has_unfinished():
+                out += engine.step()
+            dt = time.perf_counter() - t0
+            assert len(out) == 1 and out[0].finished
+            if r:
+                times.append(dt)
+    finally:
+        cfg.max_num_batched_tokens, cfg.prefill_chunk_size = saved
+    times.sort()
+    return PREFILL_TOKENS / times[len(times) // 2]
 
 
 def e2e_run(engine, batch, context, warmup, steps, vocab):
@@ -395,7 +426,8 @@ def main(argv=None):
                           "frac_of_sustained": round(prefill_flops / (pms * 1e-3) / (pk["bf16_tflops_sustained"] * 1e12), 4)}
         ms1, _, _ = decode_run(runner, sampler, 1, args.context, warmup, args.steps, "prefill", vocab, "s")
         ms64, _, _ = decode_run(runner, sampler, 64, args.context, warmup, args.steps, args.kv_fill, vocab, "l")
-        out["points"] = {"decode_b1": round(1000.0 / ms1, 1), "decode_b64": round(64 * 1000.0 / ms64, 1)}
+        out["points"] = {"decode_b1": round(1000.0 / ms1, 1), "decode_b64": round(64 * 1000.0 / ms64, 1),
+                         "prefill_default": round(prefill_default_run(engine, vocab), 1)}
     print(json.dumps(out))
     return 0
 

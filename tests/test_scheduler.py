@@ -48,18 +48,38 @@ def test_first_come_first_served_under_a_token_budget():
     a = s.add_request(range(9), 3)
     b = s.add_request(range(4), 2)
     plan, _ = run_step(cache, s)
-    assert [(e.seq.seq_id, e.start, e.count, e.samples) for e in plan.entries] == [(a.seq_id, 0, 6, False), (b.seq_id, 0, 4, True)]
+    # nobody decodes yet: prefill_chunk_size does not bound the portions, the token budget does
+    assert [(e.seq.seq_id, e.start, e.count, e.samples) for e in plan.entries] == [(a.seq_id, 0, 9, True), (b.seq_id, 0, 1, False)]
     assert plan.num_tokens <= 10
     plan, _ = run_step(cache, s)
-    # b decodes (one token, first), a finishes its prompt beside it
-    assert [(e.seq.seq_id, e.start, e.count, e.samples) for e in plan.entries] == [(b.seq_id, 4, 1, True), (a.seq_id, 6, 3, True)]
-    assert b.status == "finished" and b.finish_reason == "length" and b.generated == [7, 7]
+    # a decodes (one token, first), b finishes its prompt beside it
+    assert [(e.seq.seq_id, e.start, e.count, e.samples) for e in plan.entries] == [(a.seq_id, 9, 1, True), (b.seq_id, 1, 3, True)]
     plan, _ = run_step(cache, s)
-    assert [(e.seq.seq_id, e.count) for e in plan.entries] == [(a.seq_id, 1)]
-    run_step(cache, s)
+    assert [(e.seq.seq_id, e.count) for e in plan.entries] == [(a.seq_id, 1), (b.seq_id, 1)]
+    assert b.status == "finished" and b.finish_reason == "length" and b.generated == [7, 7]
     assert a.status == "finished" and len(a.generated) == 3
     assert cache.free_pages() == [64] and not s.has_work()
     assert s.stats["prefill_tokens"] == 13 and s.stats["decode_tokens"] == 3 and s.stats["finished"] == 2
+
+
+def test_prefill_chunk_size_bounds_portions_only_beside_decoding_requests():
+    cache, s = make(max_num_batched_tokens=32, prefill_chunk_size=6)
+    a = s.add_request(range(5), 8)
+    run_step(cache, s)                                   # a's prompt; from now on a decodes
+    b = s.add_request(range(20), 2)
+    plan, _ = run_step(cache, s)
+    assert [(e.seq.seq_id, e.count) for e in plan.entries] == [(a.seq_id, 1), (b.seq_id, 6)]   # a's token must not wait long
+    plan, _ = run_step(cache, s)
+    assert [(e.seq.seq_id, e.count) for e in plan.entries] == [(a.seq_id, 1), (b.seq_id, 6)]
+    s.cancel(a.seq_id)
+    plan, _ = run_step(cache, s)
+    assert [(e.seq.seq_id, e.start, e.count) for e in plan.entries] == [(b.seq_id, 12, 8)]     # alone again: all that is left
+    c = s.add_request(range(40), 2)                      # and a prompt beyond the budget is cut by the budget
+    plan, _ = run_step(cache, s)
+    assert [(e.seq.seq_id, e.count) for e in plan.entries] == [(b.seq_id, 1), (c.seq_id, 6)]
+    assert b.status == "finished"
+    plan, _ = run_step(cache, s)
+    assert [(e.seq.seq_id, e.start, e.count) for e in plan.entries] == [(c.seq_id, 6, 32)]     # 34 left, 32 fit the budget
 
 
 def test_n_tokens_take_one_prompt_step_and_n_minus_one_decode_steps():

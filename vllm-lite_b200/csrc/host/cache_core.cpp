@@ -458,7 +458,7 @@ long long vc_decode_step(void* h, int B, const long long* keys, const int* token
 //   arrival[i] = its arrival number.
 //   A step holds the next token of every decoding request, then portions of running prompts, then
 //   admissions from the head of the queue, under max_num_batched_tokens / max_num_seqs /
-//   prefill_chunk_size; a running sequence that cannot get its pages makes the most recently arrived
+//   prefill_chunk_size (the last bounds a prompt's portion only in a step that also decodes); a running sequence that cannot get its pages makes the most recently arrived
 //   running sequence a victim (its pages count as free, it goes back to the head of the queue with
 //   all its tokens to compute) and the step is composed again.
 //   Out: entries (sequence number, tokens) in step order, victims in the order they were chosen, and
@@ -490,12 +490,15 @@ int vs_schedule(void* h, int max_num_seqs, long long max_num_batched_tokens, lon
         const long long held = holds[i] ? comp[i] : 0;
         return (int)((held + count + ps - 1) / ps - (held + ps - 1) / ps);
     };
+    bool capped = true;                              // prefill_chunk_size bounds portions only beside decoding requests
     auto chunk = [&](int i, long long room) {
         long long k = rem[i] < room ? rem[i] : room;
-        if (rem[i] > 1 && k > prefill_chunk_size) k = prefill_chunk_size;
+        if (rem[i] > 1 && capped && k > prefill_chunk_size) k = prefill_chunk_size;
         return k;
     };
     for (;;) {
+        capped = false;
+        for (int i : running) capped = capped || rem[i] == 1;
         std::vector<int> free(G);
         for (int g = 0; g < G; ++g) free[g] = c->pools[g].free_count() + extra_free[g];
         int free_slots = c->slots.free_count() + extra_slots;

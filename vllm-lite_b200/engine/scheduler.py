@@ -115,7 +115,8 @@ class Scheduler:
                                  f"{self.config.max_model_len}")
         ps = self.cache.page_size
         for need, pool in zip(self.cache.layout.paged_groups, self.cache.pools):
-            most = total if need.window is None else min(total, need.window + 2 * ps + self.config.prefill_chunk_size)
+            longest_step = max(self.config.prefill_chunk_size, self.config.max_num_batched_tokens)
+            most = total if need.window is None else min(total, need.window + 2 * ps + longest_step)
             if -(-most // ps) > pool.size:
                 raise AdmissionError(f"the request needs {-(-most // ps)} pages alone; the pool has {pool.size}")
         seq = Sequence(self._next_id, prompt, len(prompt), int(max_tokens), (params or SamplingParams()).validate(),
@@ -173,9 +174,12 @@ class Scheduler:
                         for i, n in entries]
         return plan
 
-    def _chunk(self, seq: Sequence, room: int) -> int:
+    def _chunk(self, seq: Sequence, room: int, capped: bool = True) -> int:
+        """Tokens of `seq` in this step.  `prefill_chunk_size` bounds a prompt's portion only in a step that
+        also holds decoding requests (whose next tokens would wait behind a long portion); a step of prompts
+        alone gives a prompt all the room the token budget leaves."""
         n = min(seq.remaining, room)
-        if seq.remaining > 1:
+        if seq.remaining > 1 and capped:
             n = min(n, self.config.prefill_chunk_size)
         return n
 
@@ -188,8 +192,9 @@ class Scheduler:
         entries: List[Scheduled] = []
         # decoding requests first, then running prompts, both in order of arrival
         order = [s for s in self.running if s.remaining == 1] + [s for s in self.running if s.remaining > 1]
+        capped = any(s.remaining == 1 for s in self.running)     # someone decodes in this step
         for seq in order:
-            n = self._chunk(seq, room)
+            n = self._chunk(seq, room, capped)
             if n <= 0:
                 continue
             need = self._pages_needed(seq, n)
@@ -203,7 +208,7 @@ class Scheduler:
         # admit from the head of the queue while slots, pages and budget last
         while self.waiting and room > 0 and len(self.running) < cfg.max_num_seqs:
             seq = self.waiting[0]
-            n = self._chunk(seq, room)
+            n = self._chunk(seq, room, capped)
             need = self._pages_needed(seq, n)
             if any(a > b for a, b in zip(need, free)) or (seq.seq_id not in self.cache.requests and free_slots < 1):
                 break                                         # head-of-line: never admit what cannot get pages
