@@ -256,7 +256,9 @@ def continuous_run(engine, requests, vocab, prompt_range, out_len):
             "all_tokens_per_s": round((prompt_tokens + produced) / dt, 1),
             "steps": {k: v[0] for k, v in kinds.items()},
             "ms_per_step": {k: round(v[1] / v[0] * 1e3, 3) if v[0] else None for k, v in kinds.items()},
-            "preemptions": engine.scheduler.stats["preemptions"]}
+            "preemptions": engine.scheduler.stats["preemptions"],
+            # host time of LLMEngine.step() and device time of every 16th step, by kind (median, 90th percentile)
+            "step_times": engine.stats()["step_times"]}
 
 
 def check_fp32(cfg, layers, tokens=1024):

@@ -305,10 +305,19 @@ def paged_reference(q, keys, values, pos, scale, window):
     return out
 
 
-def build_paged(seqs_kv, nkv, hd, page, dtype, shuffle_seed=0):
-    """Scatter each sequence's keys/values into shuffled pages; returns caches and block table."""
+def build_paged(seqs_kv, nkv, hd, page, dtype, shuffle_seed=0, order="shuffled"):
+    """Scatter each sequence's keys/values into pages; returns caches and block table.  `order`: the pages
+    a sequence gets are "shuffled", "in a row" (neighbours in the pool, as a fresh pool hands them out) or
+    in "runs" (neighbours but for a swap every few pages)."""
     total_pages = sum(-(-k.shape[0] // page) for k, _ in seqs_kv) + 3
-    perm = np.random.default_rng(shuffle_seed).permutation(total_pages).tolist()
+    if order == "shuffled":
+        perm = np.random.default_rng(shuffle_seed).permutation(total_pages).tolist()
+    else:
+        perm = list(range(total_pages))
+        if order == "runs":
+            for i in range(5, total_pages - 1, 7):
+                perm[i], perm[i + 1] = perm[i + 1], perm[i]
+        perm.reverse()                            # pop() hands out the front first
     kc = torch.full((total_pages, nkv, page, hd), float("nan"), dtype=dtype)
     vc = torch.full((total_pages, nkv, page, hd), float("nan"), dtype=dtype)
     max_blocks = max(-(-k.shape[0] // page) for k, _ in seqs_kv)
@@ -379,7 +388,8 @@ def test_paged_attention_ragged(kernel, dtype, nq, nkv, hd, page, window):
 @pytest.mark.parametrize("nq,nkv,hd,page,window", [(2, 1, 64, 16, 0), (6, 2, 64, 8, 37), (5, 5, 64, 64, 0),
                                                    (4, 2, 128, 16, 0), (8, 1, 128, 32, 150), (3, 3, 128, 128, 0),
                                                    (32, 8, 128, 16, 0)])
-def test_flash_tc5_prefill(nq, nkv, hd, page, window):
+@pytest.mark.parametrize("order", ["shuffled", "in a row", "runs"])
+def test_flash_tc5_prefill(nq, nkv, hd, page, window, order):
     """The tcgen05 kernel on a ragged batch: a whole prompt of several tiles, a continuation that
     starts inside a page, a short portion, a single token; pages shuffled; every cache slot that no
     query may read holds NaN, which would show in the output."""
@@ -388,7 +398,7 @@ def test_flash_tc5_prefill(nq, nkv, hd, page, window):
     lens = [300, 471, 130, 77]                    # keys present per request
     new = [300, 200, 3, 1]                        # query tokens of this step per request (the last `new` positions)
     seqs = [(torch.randn(n, nkv, hd), torch.randn(n, nkv, hd)) for n in lens]
-    kc, vc, table = build_paged(seqs, nkv, hd, page, dtype)
+    kc, vc, table = build_paged(seqs, nkv, hd, page, dtype, order=order)     # neighbouring pages come in one box
     req, pos, tiles, t0 = [], [], [], 0
     for b, (n, c) in enumerate(zip(lens, new)):
         for p_ in range(n - c, n):
@@ -481,7 +491,13 @@ def test_decode_attention_split(kernel, dtype, nq, nkv, hd, page, window):
     torch.manual_seed(nq * 10 + hd)
     lens = [1, 255, 256, 257, 700, 1030]
     seqs = [(torch.randn(n, nkv, hd), torch.randn(n, nkv, hd)) for n in lens]
-    kc, vc, table = build_paged(seqs, nkv, hd, page, dtype)
+    # pages shuffled, and in a row as a fresh pool hands them out
+    for order in ("shuffled", "in a row"):
+        _decode_attention_split(kernel, dtype, nq, nkv, hd, page, window, lens, seqs, order)
+
+
+def _decode_attention_split(kernel, dtype, nq, nkv, hd, page, window, lens, seqs, order):
+    kc, vc, table = build_paged(seqs, nkv, hd, page, dtype, order=order)
     T = len(lens) + 1
     req = torch.tensor(list(range(len(lens))) + [0], dtype=torch.int32, device=DEV)
     pos = torch.tensor([n - 1 for n in lens] + [-1], dtype=torch.int32, device=DEV)
@@ -497,7 +513,7 @@ def test_decode_attention_split(kernel, dtype, nq, nkv, hd, page, window):
     for t, n in enumerate(lens):
         k, v = seqs[t]
         ref = paged_reference(qd[t], k.to(dtype).float(), v.to(dtype).float(), n - 1, scale, window)
-        assert torch.allclose(out[t].float().cpu().view(nq, hd), ref, **tol(dtype)), (t, n)
+        assert torch.allclose(out[t].float().cpu().view(nq, hd), ref, **tol(dtype)), (t, n, order)
     if kernel != "flash_prefill":
         assert bool((out[T - 1] == 0).all())
 

@@ -14,9 +14,10 @@
 //        P = exp2(S - m) as bfloat16 into shared memory (128-byte swizzled rows, the layout the
 //        tensor core reads) and, when a row's maximum has grown by more than 2^8, rescale the
 //        output accumulator in TMEM (tcgen05.ld / tcgen05.st);
-//   warp 4               TMA producer: the K and V rows of a key tile, one box per page and 64
-//        columns (cp.async.bulk.tensor.2d, 128-byte swizzle), into two stages each; a lane owns a
-//        box and looks its page up one tile ahead; a page that no query of the tile may read, or
+//   warp 4               TMA producer: the K and V rows of a key tile into two stages each: ONE box
+//        (cp.async.bulk.tensor.5d over pages x blocks of columns, 128-byte swizzle) when the tile's
+//        pages are neighbours in the pool, else one box per page and 64 columns
+//        (cp.async.bulk.tensor.2d); a lane owns a page and looks it up one tile ahead; a page that no query of the tile may read, or
 //        that the block table does not hold, is fetched from beyond the end of the tensor, which
 //        the TMA unit fills with zeros; the rows of V behind the tile's last key (another request's
 //        leftovers, possibly NaN) are zeroed in shared memory once the last key tile has landed;
@@ -107,6 +108,7 @@ __device__ __forceinline__ unsigned swizzled(int row, int chunk) {
 // position of the first}
 extern "C" __global__ void __launch_bounds__(NTHREADS, 2)
 flash_tc5_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v,
+                 const __grid_constant__ CUtensorMap pages_k, const __grid_constant__ CUtensorMap pages_v, int use_pages,
                  const bf16* __restrict__ q, int q_stride, bf16* __restrict__ out,
                  const int* __restrict__ block_table, int max_blocks, const int4* __restrict__ tiles, int num_tiles,
                  int nq, int nkv, int page_size, int num_pages, float scale_log2, int window, unsigned* err) {
@@ -206,10 +208,20 @@ flash_tc5_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constan
                     else mbar_arrive_expect_tx(full, KV_STAGE);
                 }
                 ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
-                if (ok && lane < nbox) {
+                // The pages of the tile are neighbours in the pool (the usual case: the pool hands pages out in
+                // a row) and all of them are read: one box brings them all.  Else a box per page and block of
+                // columns.
+                const int row = kv ? row_v : row_k;
+                const int row0 = __shfl_sync(0xffffffffu, row, 0);
+                const bool in_a_row = use_pages && __all_sync(0xffffffffu, lane >= nbox || (row != beyond && row == row0 + lane * nkv * page_size));
+                if (ok && in_a_row) {
+                    if (lane == 0)
+                        tma_load_5d((kv ? Vs : Ks) + (unsigned)s * KV_STAGE, kv ? &pages_v : &pages_k, 0, 0,
+                                    row0 / (nkv * page_size), 0, kvh, full);
+                } else if (ok && lane < nbox) {
                     unsigned char* st = (kv ? Vs : Ks) + (unsigned)s * KV_STAGE + (unsigned)(lane * box_rows) * ROW_BYTES;
                     for (int cb = 0; cb < CB; ++cb)
-                        tma_load_2d(st + (unsigned)cb * (BN * ROW_BYTES), kv ? &map_v : &map_k, cb * 64, kv ? row_v : row_k, full);
+                        tma_load_2d(st + (unsigned)cb * (BN * ROW_BYTES), kv ? &map_v : &map_k, cb * 64, row, full);
                 }
             }
             row_v = row_k;
@@ -409,9 +421,18 @@ extern "C" int vl_flash_prefill_tc5(const void* q, int q_stride, void* out, cons
     if (rc) return rc;
     rc = tc5_make_map(&map_v, vcache, (int)rows, HD, HD, box_rows);
     if (rc) return rc;
+    // pages smaller than a key tile: a second pair of maps whose box spans the tile's pages when they are neighbours
+    CUtensorMap pages_k = map_k, pages_v = map_v;
+    const int use_pages = page_size < BN ? 1 : 0;
+    if (use_pages) {
+        rc = tc5_make_map_pages(&pages_k, kcache, num_pages, nkv, page_size, HD, BN / page_size);
+        if (rc) return rc;
+        rc = tc5_make_map_pages(&pages_v, vcache, num_pages, nkv, page_size, HD, BN / page_size);
+        if (rc) return rc;
+    }
     cudaError_t e = cudaFuncSetAttribute(flash_tc5_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM_BYTES);
     if (e != cudaSuccess) return (int)e;
     return vl_launch(flash_tc5_kernel, dim3(nq, num_tiles), dim3(NTHREADS), SMEM_BYTES, (cudaStream_t)stream,
-                     map_k, map_v, (const bf16*)q, q_stride, (bf16*)out, block_table, max_blocks, (const int4*)tiles,
+                     map_k, map_v, pages_k, pages_v, use_pages, (const bf16*)q, q_stride, (bf16*)out, block_table, max_blocks, (const int4*)tiles,
                      num_tiles, nq, nkv, page_size, num_pages, scale * 1.4426950408889634f, window, err);
 }

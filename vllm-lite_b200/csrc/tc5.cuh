@@ -47,6 +47,13 @@ __device__ __forceinline__ void tma_load_3d(void* dst, const CUtensorMap* map, i
         "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4}], [%5];"
         ::"r"(smem_u32(dst)), "l"(map), "r"(x), "r"(y), "r"(z), "r"(smem_u32(bar)) : "memory");
 }
+// five coordinates: (x, row in page, page, block of 64 columns, KV head) of tc5_make_map_pages
+__device__ __forceinline__ void tma_load_5d(void* dst, const CUtensorMap* map, int c0, int c1, int c2, int c3, int c4,
+                                            unsigned long long* bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.5d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4, %5, %6}], [%7];"
+        ::"r"(smem_u32(dst)), "l"(map), "r"(c0), "r"(c1), "r"(c2), "r"(c3), "r"(c4), "r"(smem_u32(bar)) : "memory");
+}
 __device__ __forceinline__ void tc5_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void tc5_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void tc5_alloc(unsigned* smem_result, unsigned ncols) {          // whole warp
@@ -247,6 +254,33 @@ static inline int tc5_make_map_blocks(CUtensorMap* map, const void* base, int ro
     cuuint32_t box[3] = {(cuuint32_t)tc5::SWIZZLE_COLS, (cuuint32_t)box_rows, (cuuint32_t)(cols / tc5::SWIZZLE_COLS)};
     cuuint32_t estr[3] = {1, 1, 1};
     CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(base), dims, strides, box, estr,
+                     CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                     CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    return r == CUDA_SUCCESS ? 0 : VL_ERR_ARGUMENT;
+}
+
+
+// A paged cache [pages, kv heads, page_size, cols] of bfloat16 (cols a multiple of 64) seen as
+// (64 columns, rows of a page, pages, blocks of 64 columns, kv heads): one box brings, for one kv head, the
+// rows of `box_pages` NEIGHBOURING pages and lays them down block of columns after block of columns, each
+// block as box_pages * page_size rows of 128 bytes (page after page, i.e. in the order of the keys when a
+// request holds neighbouring pages) with the 128-byte swizzle.  A request's pages are neighbours whenever
+// the pool handed them out in a row, so a tile of 64 keys on pages of 16 is then ONE request of 16 KB to
+// the TMA unit instead of four (or eight) small ones.
+static inline int tc5_make_map_pages(CUtensorMap* map, const void* base, int num_pages, int nkv, int page_size, int cols,
+                                     int box_pages) {
+    EncodeTiledFn enc = encode_tiled_fn();
+    if (!enc) return VL_ERR_UNSUPPORTED;
+    if (cols % tc5::SWIZZLE_COLS || box_pages <= 0 || box_pages * page_size > 256) return VL_ERR_UNSUPPORTED;
+    const cuuint64_t row_bytes = (cuuint64_t)cols * 2;
+    cuuint64_t dims[5] = {(cuuint64_t)tc5::SWIZZLE_COLS, (cuuint64_t)page_size, (cuuint64_t)num_pages,
+                          (cuuint64_t)(cols / tc5::SWIZZLE_COLS), (cuuint64_t)nkv};
+    cuuint64_t strides[4] = {row_bytes, (cuuint64_t)nkv * page_size * row_bytes, (cuuint64_t)tc5::SWIZZLE_COLS * 2,
+                             (cuuint64_t)page_size * row_bytes};
+    cuuint32_t box[5] = {(cuuint32_t)tc5::SWIZZLE_COLS, (cuuint32_t)page_size, (cuuint32_t)box_pages,
+                         (cuuint32_t)(cols / tc5::SWIZZLE_COLS), 1};
+    cuuint32_t estr[5] = {1, 1, 1, 1, 1};
+    CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 5, const_cast<void*>(base), dims, strides, box, estr,
                      CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                      CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     return r == CUDA_SUCCESS ? 0 : VL_ERR_ARGUMENT;
