@@ -650,3 +650,43 @@ def test_a_head_norm_that_offers_neither_form_is_refused_when_the_model_is_built
             cls(AttentionSpec(32, 2, 1, 24), {}, BuildContext(torch.device(DEV), torch.bfloat16))
     finally:
         NORMS.unregister("toy_useless")
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("tied", [False, True])
+def test_embedding_and_output_head_alone(dtype, tied):
+    """The two ends of a model as parts of their own, at sizes of no model: the gather into the float32
+    stream (an id outside the table is flagged, never read, and its row is zero) and the float32 logits of chosen
+    rows, with a matrix of the head's own or the embedding's table."""
+    from vllm_lite_b200.parts import EMBEDDINGS, HEADS
+    from vllm_lite_b200.parts.base import BuildContext
+    from vllm_lite_b200.parts.spec import EmbeddingSpec, HeadSpec
+    torch.manual_seed(3)
+    V, Hd, T = 211, 88, 9
+    ctx = BuildContext(torch.device(DEV), dtype)
+    es, hs = EmbeddingSpec(V, Hd), HeadSpec(V, Hd, tied=tied)
+    assert EMBEDDINGS.get(es.kind).declare(es)["weight"].shape == (V, Hd)
+    assert ("weight" in HEADS.get(hs.kind).declare(hs)) == (not tied)
+    table = (torch.randn(V, Hd) * 0.3).to(dtype)
+    own = (torch.randn(V, Hd) * 0.3).to(dtype)
+    emb = EMBEDDINGS.get(es.kind)(es, {"weight": table.to(DEV)}, ctx)
+    head = HEADS.get(hs.kind)(hs, {} if tied else {"weight": own.to(DEV)}, ctx, embedding=emb)
+    step = make_step(None, T)
+    ids = torch.tensor([0, 5, V - 1, 17, 17, 3, 99, 210, 1], dtype=torch.int32)
+    step.tokens = ids.to(DEV)
+    x = torch.full((T, Hd), 7.0, device=DEV)
+    emb(step, x)
+    assert torch.equal(x.cpu(), table.float()[ids.long()])
+    assert int(step.err.item()) == 0
+    step.tokens = torch.tensor([2, V, 4] + [0] * (T - 3), dtype=torch.int32, device=DEV)      # V lies outside the table
+    y = torch.full((T, Hd), 7.0, device=DEV)
+    emb(step, y)
+    assert int(step.err.item()) & 1 and bool((y[1] == 0.0).all()) and torch.equal(y[0].cpu(), table.float()[2])
+    h = (torch.randn(4, Hd, device=DEV) * 0.5).to(dtype)
+    logits = head(h, step)
+    assert logits.dtype == torch.float32 and logits.shape == (4, V)
+    ref = h.float().cpu() @ (table if tied else own).float().T
+    tol = dict(atol=1e-5, rtol=1e-5) if dtype == torch.float32 else dict(atol=2e-2, rtol=2e-2)
+    assert torch.allclose(logits.cpu(), ref, **tol)
+    with pytest.raises(ValueError, match="tied"):
+        HEADS.get(hs.kind)(HeadSpec(V, Hd, tied=True), {}, ctx, embedding=None)
