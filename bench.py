@@ -308,6 +308,108 @@ def check_fp32(cfg, layers, tokens=1024):
     return 0 if not unequal else 1
 
 
+def read_ceiling(cfg, batch, context):
+    """What ONE launch that must read a given number of bytes can reach, at the sizes of a decode step's
+    kernels: a kernel that only reads (csrc/memprobe.cu) beside the engine's own kernel for each of them.
+    Every launch reads memory that L2 does not hold (8 copies of the operands in turn), launches follow one
+    another inside a CUDA graph with programmatic dependent launch on, as in a decode step.  One JSON line."""
+    import torch
+    from vllm_lite_b200.csrc import ops
+    dev = "cuda:0"
+    H, I, V = cfg["hidden_size"], cfg["intermediate_size"], cfg["vocab_size"]
+    nq, nkv, hd = cfg["num_attention_heads"], cfg["num_key_value_heads"], cfg["head_dim"]
+    M, L = batch, 8
+    ops.set_pdl(True)
+    err = torch.zeros(1, dtype=torch.int32, device=dev)
+
+    def in_graph(fn):                                   # microseconds per launch, L launches a replay
+        fn(); torch.cuda.synchronize()
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g):
+            fn()
+        for _ in range(3):
+            g.replay()
+        torch.cuda.synchronize()
+        t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        t0.record()
+        for _ in range(10):
+            g.replay()
+        t1.record(); torch.cuda.synchronize()
+        return t0.elapsed_time(t1) / 10 / L * 1e3
+
+    def weights(n, k):
+        return [torch.randn(n, k, device=dev, dtype=torch.bfloat16) for _ in range(L)]
+
+    nw = torch.ones(H, device=dev)
+    x = torch.randn(M, H, device=dev)
+    part = torch.zeros(ops.NORM_PARTIALS, 16, device=dev)
+    rows = torch.empty(M, H, device=dev, dtype=torch.bfloat16)
+    out = {}
+
+    def product(name, n, k, **kw):
+        ws = weights(n, k)
+        a = torch.randn(M, k, device=dev, dtype=torch.bfloat16)
+        width = n // 2 if kw.get("swiglu") else n
+        c = torch.empty(M, width, device=dev, dtype=kw.pop("out_dtype", torch.bfloat16))
+        sink = kw.pop("sink", False)
+        gu = torch.empty(M, n, device=dev, dtype=torch.bfloat16) if M > ops.SMALL_M else None
+        def ours():
+            for w in ws:
+                if M > ops.SMALL_M:                   # more rows than the weight-streaming product takes: the library
+                    if kw.get("swiglu"):
+                        torch.mm(a, w.t(), out=gu)
+                    else:
+                        torch.mm(a, w.t(), out=c)
+                elif sink:
+                    ops.gemm_bf16_small_m(a, w, rows, err, sink=(x, nw, part))
+                else:
+                    ops.gemm_bf16_small_m(a, w, c, err, **kw)
+        nbytes = n * k * 2
+        def plain():
+            for w in ws:
+                ops.read_only(w, nbytes)
+        out[name] = {"MB": round(nbytes / 1e6, 1), "engine_us": round(in_graph(ours), 1), "read_only_us": round(in_graph(plain), 1)}
+        del ws
+
+    product("qkv", (nq + 2 * nkv) * hd, H, scaled=(part, 1, 1e-6, H))
+    product("o", H, nq * hd, sink=True)
+    product("gate_up", 2 * I, H, swiglu=True, scaled=(part, 1, 1e-6, H))
+    product("down", H, I, sink=True)
+    if M <= ops.SMALL_M:
+        product("head", V, H, out_dtype=torch.float32)
+    # decode attention: `batch` requests of `context` keys, pages of 16 in a row
+    page, nblk = 16, context // 16 + 1
+    caches = [(torch.randn(batch * nblk, nkv, page, hd, device=dev, dtype=torch.bfloat16),
+               torch.randn(batch * nblk, nkv, page, hd, device=dev, dtype=torch.bfloat16)) for _ in range(L)]
+    table = torch.arange(batch * nblk, device=dev, dtype=torch.int32).view(batch, nblk)
+    qkv = torch.randn(batch, (nq + 2 * nkv) * hd, device=dev, dtype=torch.bfloat16)
+    o = torch.empty(batch, nq * hd, device=dev, dtype=torch.bfloat16)
+    req = torch.arange(batch, dtype=torch.int32, device=dev)
+    pos = torch.full((batch,), context - 1, dtype=torch.int32, device=dev)
+    chunk = ops.decode_chunk_for(batch, nkv, context)
+    S, na, nm = ops.decode_attention_scratch(batch, nq, hd, context, chunk)
+    pa, pm = torch.empty(na, device=dev), torch.empty(nm, device=dev)
+    arr = torch.zeros(ops.flash_decode_arrivals(batch, nq, nkv), dtype=torch.int32, device=dev)
+    def attention():
+        for kc, vc in caches:
+            ops.flash_decode(qkv, o, kc, vc, table, req, pos, nq, nkv, hd, hd ** -0.5, 0, context, pa, pm, err,
+                             chunk=chunk, arrivals=arr)
+    kv_bytes = batch * context * nkv * hd * 2 * 2
+    def attention_plain():
+        for kc, vc in caches:
+            ops.read_only(kc, kv_bytes // 2 // 16 * 16)
+            ops.read_only(vc, kv_bytes // 2 // 16 * 16)
+    out["attention"] = {"MB": round(kv_bytes / 1e6, 1), "engine_us": round(in_graph(attention), 1),
+                        "read_only_us": round(in_graph(attention_plain), 1), "read_only_launches": 2}
+    assert int(err.item()) == 0
+    pk = peaks()
+    for v in out.values():
+        v["at_copy_peak_us"] = round(v["MB"] * 1e6 / (pk["hbm_gbs"] * 1e9) * 1e6, 1)
+    print(json.dumps({"read_ceiling": out, "batch": batch, "context": context, "copy_peak_gbs": pk["hbm_gbs"],
+                      "how": "microseconds a launch, 8 launches over memory L2 does not hold, in a CUDA graph, dependent launches on"}))
+    return 0
+
+
 def main(argv=None):
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -329,6 +431,8 @@ def main(argv=None):
     ap.add_argument("--kv-blocks", default=None, metavar="N|auto",
                     help="pages of the cache: a count, or 'auto' = sized from the memory left after the weights (the "
                          "default for --size 32b); default otherwise: what the largest batch needs at --context")
+    ap.add_argument("--read-ceiling", action="store_true",
+                    help="instead of timing steps: every kernel of a decode step alone beside a kernel that only reads as many bytes")
     ap.add_argument("--check-fp32", action="store_true",
                     help="instead of timing: the model in true float32, whole prompt against cut prompt, bit for bit")
     args = ap.parse_args(argv)
@@ -350,6 +454,8 @@ def main(argv=None):
     vocab = cfg["vocab_size"]
     if args.check_fp32:
         return check_fp32(cfg, args.layers)
+    if args.read_ceiling:
+        return read_ceiling(cfg, args.batch, args.context)
     _, plan, weights = random_model(cfg, seed=0, dtype="bfloat16", device="cuda:0")
     if args.continuous:
         R, out_len, prompt_range = args.continuous, 512, (256, args.context // 2)

@@ -68,6 +68,7 @@ _SIGNATURES = {
                                        c_void_p, c_int, c_void_p],
     ("gemm_tc5_pair", "vl_gemm_bf16_tc5_pair"): [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
                                                  c_void_p, c_int, c_void_p],
+    ("memprobe", "vl_read_only"): [c_void_p, c_longlong, c_void_p, c_void_p],
     ("sampling", "vl_apply_penalties"): [c_void_p, c_longlong, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p,
                                          c_void_p, c_void_p, c_void_p, c_void_p],
     ("sampling", "vl_sample"): [c_void_p, c_longlong, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p,
@@ -537,6 +538,18 @@ def gemm_bf16_tc5_pair(a, w, out, err=None, swiglu=False):
                                                          K, K, width, _ptr(err), int(swiglu), _stream()),
            "vl_gemm_bf16_tc5_pair")
     return out
+
+
+# ---------------------------------------------------------------- measurement
+def read_only(buf, nbytes=None, sink=None):
+    """Streams the first `nbytes` bytes of `buf` from memory once and does nothing with them: the time of
+    this launch is what any kernel that must read as many bytes is measured against (bench.py --read-ceiling)."""
+    _need(buf, None, "buf")
+    total = buf.numel() * buf.element_size()
+    nbytes = total if nbytes is None else int(nbytes)
+    if not 0 < nbytes <= total or nbytes % 16:
+        raise KernelError(f"read_only: {nbytes} bytes of a buffer of {total} (a multiple of 16 is wanted)")
+    _check(_fn("memprobe", "vl_read_only")(_ptr(buf), nbytes, _ptr(sink), _stream()), "vl_read_only")
 
 
 # ---------------------------------------------------------------- sampling
