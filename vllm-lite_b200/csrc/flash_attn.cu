@@ -415,40 +415,56 @@ flash_decode_kernel(const bf16* __restrict__ q, int q_stride,
         const bf16* src = valid ? q + (size_t)tok * q_stride + (size_t)(h0 + r) * HD + c * 8 : q;
         cp_async16(Qs + (size_t)r * LDS + c * 8, src, valid);
     }
+    cp_async_commit();                                           // the query rows: this thread's oldest group
     __syncthreads();                                             // s_rows
-    auto load_stage = [&](int st, int buf) {
-        bf16* kt = ring + (size_t)buf * 2 * BN * LDS;
-        load_kv_tiles(kt, kt + BN * LDS, kcache, vcache, s_rows + (st - st0) * BN, BN);
+    // Every warp runs a pipeline of its own: of each 64 keys it takes 16 (warp w the keys 16 w .. 16 w + 15),
+    // copies their K and V rows itself into a ring of DEC_NST tiles that belongs to it, and waits for
+    // nobody but its own copies.  No barrier of the block stands in the loop, and of a warp's ring all
+    // tiles but the one being multiplied are in flight (64 requests of 4,096 keys: 197 -> 190 us; one
+    // request: 11.0 -> 10.2 us).  The keys a warp sees, and so every sum, are those of the shared ring before.
+    bf16* wring = ring + (size_t)warp * DEC_NST * 2 * 16 * LDS;  // [DEC_NST][K | V][16][LDS]
+    auto load_tile = [&](int st, int buf) {
+        bf16* kt = wring + (size_t)buf * 2 * 16 * LDS;
+        const int* rows16 = s_rows + (st - st0) * BN + warp * 16;
+#pragma unroll
+        for (int i = 0; i < 16 * CPR / 32; ++i) {
+            const int idx = lane + 32 * i;
+            const int r = idx / CPR, c = idx - r * CPR;
+            const int row = rows16[r];
+            const size_t off = row < 0 ? 0 : (size_t)row * HD + c * 8;
+            cp_async16(kt + (size_t)r * LDS + c * 8, kcache + off, row >= 0);
+            cp_async16(kt + (size_t)(16 + r) * LDS + c * 8, vcache + off, row >= 0);
+        }
     };
 #pragma unroll
     for (int i = 0; i < DEC_NST - 1; ++i) {
-        if (st0 + i <= st1) load_stage(st0 + i, i);
+        if (st0 + i <= st1) load_tile(st0 + i, i);
         cp_async_commit();
     }
     float o[DTILES][4], m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};
 #pragma unroll
     for (int d = 0; d < DTILES; ++d) { o[d][0] = o[d][1] = o[d][2] = o[d][3] = 0.f; }
     unsigned qf[KSTEPS][4];
+    cp_async_wait<DEC_NST - 1>();                                // this thread's share of the query rows has landed ...
+    __syncthreads();                                             // ... and so has everybody's
+#pragma unroll
+    for (int ks = 0; ks < KSTEPS; ++ks)
+        ldmatrix_x4(qf[ks], Qs + (size_t)((lane & 7) + 8 * ((lane >> 3) & 1)) * LDS + ks * 16 + 8 * (lane >> 4));
 
     for (int st = st0; st <= st1; ++st) {
         const int it = st - st0;
         cp_async_wait<DEC_NST - 2>();
-        __syncthreads();
-        if (st + DEC_NST - 1 <= st1) load_stage(st + DEC_NST - 1, (it + DEC_NST - 1) % DEC_NST);
+        __syncwarp();                                            // the tile has landed for every lane; the tile before is read
+        if (st + DEC_NST - 1 <= st1) load_tile(st + DEC_NST - 1, (it + DEC_NST - 1) % DEC_NST);
         cp_async_commit();
-        if (it == 0) {
-#pragma unroll
-            for (int ks = 0; ks < KSTEPS; ++ks)
-                ldmatrix_x4(qf[ks], Qs + (size_t)((lane & 7) + 8 * ((lane >> 3) & 1)) * LDS + ks * 16 + 8 * (lane >> 4));
-        }
-        const bf16* Kt = ring + (size_t)(it % DEC_NST) * 2 * BN * LDS;
-        const bf16* Vt = Kt + BN * LDS;
-        const int kr0 = warp * 16;                               // this warp's 16 keys of the tile
+        const bf16* Kt = wring + (size_t)(it % DEC_NST) * 2 * 16 * LDS;
+        const bf16* Vt = Kt + 16 * LDS;
+        const int kr0 = warp * 16;                               // this warp's 16 keys of every 64
         float s[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
 #pragma unroll
         for (int ks = 0; ks < KSTEPS; ++ks) {
             unsigned kb[4];
-            ldmatrix_x4(kb, Kt + (size_t)(kr0 + (lane & 7) + 8 * (lane >> 4)) * LDS + ks * 16 + 8 * ((lane >> 3) & 1));
+            ldmatrix_x4(kb, Kt + (size_t)((lane & 7) + 8 * (lane >> 4)) * LDS + ks * 16 + 8 * ((lane >> 3) & 1));
             mma16816(s[0], qf[ks], kb[0], kb[1]);
             mma16816(s[1], qf[ks], kb[2], kb[3]);
         }
@@ -487,7 +503,7 @@ flash_decode_kernel(const bf16* __restrict__ q, int q_stride,
 #pragma unroll
         for (int dp = 0; dp < DTILES / 2; ++dp) {
             unsigned vb[4];
-            ldmatrix_x4_trans(vb, Vt + (size_t)(kr0 + (lane & 7) + 8 * ((lane >> 3) & 1)) * LDS + dp * 16 + 8 * (lane >> 4));
+            ldmatrix_x4_trans(vb, Vt + (size_t)((lane & 7) + 8 * ((lane >> 3) & 1)) * LDS + dp * 16 + 8 * (lane >> 4));
             o[2 * dp][0] *= corr[0]; o[2 * dp][1] *= corr[0]; o[2 * dp][2] *= corr[1]; o[2 * dp][3] *= corr[1];
             o[2 * dp + 1][0] *= corr[0]; o[2 * dp + 1][1] *= corr[0]; o[2 * dp + 1][2] *= corr[1]; o[2 * dp + 1][3] *= corr[1];
             mma16816(o[2 * dp], pf, vb[0], vb[1]);
