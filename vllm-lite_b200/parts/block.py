@@ -13,19 +13,16 @@ from .base import StreamSink, prefixed, sub_weights
 from .registry import BLOCKS, FEED_FORWARDS, MIXERS, NORMS
 from .spec import BlockSpec
 
-# tensor-name prefixes of the block's four parts
-NORM1, MIXER, NORM2, FFN = "input_layernorm.", "self_attn.", "post_attention_layernorm.", "mlp."
-
-
 @BLOCKS.register("pre_norm")
 class PreNormBlock:
     @staticmethod
     def declare(spec: BlockSpec) -> dict:
+        norm1, mixer, norm2, ffn = spec.names
         d = {}
-        d.update(prefixed(NORMS.get(spec.norm1.kind).declare(spec.norm1), NORM1))
-        d.update(prefixed(MIXERS.get(spec.mixer.kind).declare(spec.mixer), MIXER))
-        d.update(prefixed(NORMS.get(spec.norm2.kind).declare(spec.norm2), NORM2))
-        d.update(prefixed(FEED_FORWARDS.get(spec.ffn.kind).declare(spec.ffn), FFN))
+        d.update(prefixed(NORMS.get(spec.norm1.kind).declare(spec.norm1), norm1))
+        d.update(prefixed(MIXERS.get(spec.mixer.kind).declare(spec.mixer), mixer))
+        d.update(prefixed(NORMS.get(spec.norm2.kind).declare(spec.norm2), norm2))
+        d.update(prefixed(FEED_FORWARDS.get(spec.ffn.kind).declare(spec.ffn), ffn))
         return d
 
     @staticmethod
@@ -34,10 +31,11 @@ class PreNormBlock:
 
     def __init__(self, spec: BlockSpec, weights: dict, ctx):
         self.spec = spec
-        self.norm1 = NORMS.get(spec.norm1.kind)(spec.norm1, sub_weights(weights, NORM1), ctx)
-        self.mixer = MIXERS.get(spec.mixer.kind)(spec.mixer, sub_weights(weights, MIXER), ctx)
-        self.norm2 = NORMS.get(spec.norm2.kind)(spec.norm2, sub_weights(weights, NORM2), ctx)
-        self.ffn = FEED_FORWARDS.get(spec.ffn.kind)(spec.ffn, sub_weights(weights, FFN), ctx)
+        norm1, mixer, norm2, ffn = spec.names
+        self.norm1 = NORMS.get(spec.norm1.kind)(spec.norm1, sub_weights(weights, norm1), ctx)
+        self.mixer = MIXERS.get(spec.mixer.kind)(spec.mixer, sub_weights(weights, mixer), ctx)
+        self.norm2 = NORMS.get(spec.norm2.kind)(spec.norm2, sub_weights(weights, norm2), ctx)
+        self.ffn = FEED_FORWARDS.get(spec.ffn.kind)(spec.ffn, sub_weights(weights, ffn), ctx)
         self.graph_safe = bool(getattr(self.mixer, "graph_safe", False) and getattr(self.ffn, "graph_safe", False))
 
     chains_norms = True        # __call__ takes `next_norm`

@@ -106,6 +106,8 @@ class BlockSpec:
     norm1: NormSpec
     norm2: NormSpec
     kind: str = "pre_norm"
+    # tensor-name prefixes of the four parts inside a layer (norm1, mixer, norm2, feed-forward)
+    names: Tuple[str, str, str, str] = ("input_layernorm.", "self_attn.", "post_attention_layernorm.", "mlp.")
 
 
 @dataclass(frozen=True)
