@@ -181,7 +181,8 @@ def test_gemm_small_m_with_fused_norms(M, H, K, N2, swiglu):
     assert float((out.double() - y).abs().max()) <= 2e-2 * float(y.abs().max()) + 1e-3
 
 
-@pytest.mark.parametrize("kernel,M", [("small_m", 1), ("small_m", 8), ("small_m", 13), ("tc5", 128), ("tc5", 300), ("tc5", 2048)])
+@pytest.mark.parametrize("kernel,M", [("small_m", 1), ("small_m", 8), ("small_m", 13), ("tc5", 128), ("tc5", 300), ("tc5", 2048),
+                                      ("tc5_pair", 300), ("tc5_pair", 2048)])
 @pytest.mark.parametrize("I,K", [(160, 96), (12288, 4096), (24, 64)])
 def test_gemm_with_fused_swiglu(kernel, M, I, K):
     """W interleaves 8 gate rows with their 8 up rows; the kernel writes silu(gate) * up."""
