@@ -222,35 +222,36 @@ def test_trace_run_program(dtype, tmp_path):
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 def test_real_layer_sizes_against_the_plain_implementation(dtype):
     """Two layers of Qwen3-8B width (hidden 4096, 32/8 heads of 128, intermediate 12288) with a small
-    vocabulary, against the plain implementation on the CPU: a prompt of 1,100 tokens whole (the tcgen05
-    products, one SM and paired, and the tcgen05 attention at head size 128 in bfloat16), the same prompt
-    cut 700 + 400, then 30 tokens one by one (the weight-streaming products with the norms folded in,
-    through the graph).  The float32 engine holds weights with all their bits."""
+    vocabulary, against the plain implementation on the CPU: a prompt of 2,100 tokens whole (in bfloat16 the
+    paired tcgen05 products with and without the fused activation and the tcgen05 attention at head size
+    128), the same prompt cut 1,300 + 800 (the library's products beside the fused tcgen05 one), then 30
+    tokens one by one (the weight-streaming products with the norms folded in, through the graph).  The
+    float32 engine holds weights with all their bits."""
     import plain_qwen3 as P
     from vllm_lite_b200.engine import ModelRunner, StepEntry, random_model
     cfg = dict(architectures=["Qwen3ForCausalLM"], model_type="qwen3", hidden_size=4096, num_hidden_layers=2,
                num_attention_heads=32, num_key_value_heads=8, head_dim=128, intermediate_size=12288, vocab_size=2048,
                rope_theta=1000000.0, rms_norm_eps=1e-6, tie_word_embeddings=False, max_position_embeddings=4096)
-    toks = [int(t) for t in np.random.default_rng(5).integers(0, 2048, size=1130)]
+    toks = [int(t) for t in np.random.default_rng(5).integers(0, 2048, size=2130)]
     store = torch.float32 if dtype == "float32" else torch.bfloat16
     # the tensors a folder written with this seed would hold (tests/test_weights.py checks that they are)
     _, plan, weights = random_model(cfg, seed=3, dtype=dtype, device="cuda:0", store_dtype=store)
     ref = P.forward(cfg, {k: v.float().cpu() for k, v in weights.items()}, toks)
-    runner = ModelRunner(plan, weights, dtype=store, device="cuda:0", page_size=16, num_pages=160, max_requests=2)
+    runner = ModelRunner(plan, weights, dtype=store, device="cuda:0", page_size=16, num_pages=290, max_requests=2)
     del weights
-    whole_places = [0, 63, 64, 700, 1023, 1099]
-    whole = runner.step([StepEntry("r", toks[:1100], whole_places)]).float().cpu()
-    first = runner.step([StepEntry("s", toks[:700], [0, 63, 64])]).float().cpu()
-    second = runner.step([StepEntry("s", toks[700:1100], [0, 323, 399])]).float().cpu()
+    whole_places = [0, 63, 64, 700, 1023, 1299, 1300, 2047, 2099]
+    whole = runner.step([StepEntry("r", toks[:2100], whole_places)]).float().cpu()
+    first = runner.step([StepEntry("s", toks[:1300], [0, 63, 64, 700, 1023, 1299])]).float().cpu()
+    second = runner.step([StepEntry("s", toks[1300:2100], [0, 747, 799])]).float().cpu()
     runner.release("s")
     cut = torch.cat([first, second])
     if dtype == "float32":                              # the same prompt cut in two gives the same bits
         assert torch.equal(cut, whole)
-    decoded = [runner.step([StepEntry("r", [toks[p]], [0])]).float().cpu() for p in range(1100, 1130)]
+    decoded = [runner.step([StepEntry("r", [toks[p]], [0])]).float().cpu() for p in range(2100, 2130)]
     runner.check_device_errors()
     assert runner.graph_replays >= 28
     got = torch.cat([whole, cut] + decoded)
-    want = ref[whole_places + whole_places + list(range(1100, 1130))]
+    want = ref[whole_places + whole_places + list(range(2100, 2130))]
     err = (got - want).abs().amax(dim=1) / want.abs().amax(dim=1)
     key = ("real layer sizes", "8B x 2 layers", dtype)
     H.WORST[key] = max(H.WORST.get(key, 0.0), float(err.max()))

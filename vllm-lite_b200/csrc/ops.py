@@ -502,11 +502,16 @@ def gemm_bf16_small_m(a, w, out, err=None, swiglu=False, scaled=None, sink=None)
     return out
 
 
-TC5_MIN_M = 1024          # from this many rows on the tcgen05 kernel is used
+# From this many rows on the tcgen05 kernels are used: 1,024 where the activation is fused into the product
+# (the library would need a kernel of its own for it: level at 1,024 rows, ahead beyond), 2,048 for a plain
+# product (measured at 1,024 rows, q/k/v and down of Qwen3-8B: 58 and 82 us against the library's 41 and 73;
+# at 2,048 rows 81 and 156 against 72 and 137; at 4,096 rows 158 and 358 against 165 and 314).
+TC5_MIN_M = 1024
+TC5_MIN_M_PLAIN = 2048
 
 
-def gemm_bf16_tc5_ok(M, K) -> bool:
-    return M >= TC5_MIN_M and K % 8 == 0
+def gemm_bf16_tc5_ok(M, K, fused=False) -> bool:
+    return M >= (TC5_MIN_M if fused else TC5_MIN_M_PLAIN) and K % 8 == 0
 
 
 def gemm_bf16_tc5(a, w, out, err=None, swiglu=False):
