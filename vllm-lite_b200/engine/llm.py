@@ -67,6 +67,9 @@ class StepTimes:
 
     def device(self, kind, start, end):
         self._pending.append((kind, start, end))
+        if len(self._pending) > 8:                       # read those that have completed; none is waited for
+            self.harvest()
+            del self._pending[:-64]                      # (a stream that never completes must not grow the list)
 
     def harvest(self):
         still = []
