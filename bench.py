@@ -219,6 +219,8 @@ def e2e_run(engine, batch, context, warmup, steps, vocab):
     for seq in list(engine.scheduler.running):
         engine.cancel_request(seq.seq_id)
     assert produced == batch * steps, (produced, batch, steps)
+    if os.environ.get("VLLM_LITE_B200_BENCH_STEP_TIMES"):
+        print("step times of the end-to-end run:", json.dumps(engine.stats()["step_times"]["decode"]), file=sys.stderr)
     return produced / dt, h2d, 4 * batch
 
 
