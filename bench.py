@@ -480,14 +480,17 @@ def main(argv=None):
         print(json.dumps(out))
         return 0
     big = args.batch if args.no_points else max(args.batch, 64)
-    pages = big * (-(-args.context // 16) + 1) + PREFILL_TOKENS // 16 + 64
+    # In the end-to-end run the requests' prompts are computed one after the other while the earlier requests
+    # already decode: every request needs room for the tokens it generates meanwhile.
+    slack = 64 + args.batch * (args.context // PREFILL_TOKENS + 2)
+    pages = big * (-(-(args.context + slack) // 16) + 1) + PREFILL_TOKENS // 16 + 64
     if args.kv_blocks == "auto" or (args.kv_blocks is None and args.size == "32b"):
         pages = None                                      # the engine sizes the cache from what the weights leave
     elif args.kv_blocks is not None:
         pages = int(args.kv_blocks)
     engine = LLMEngine(plan=plan, weights=weights, dtype="bfloat16", kv_blocks=pages, block_size=16, max_batch_size=big,
                        max_num_batched_tokens=PREFILL_TOKENS, prefill_chunk_size=PREFILL_TOKENS,
-                       max_model_len=args.context + 64)
+                       max_model_len=args.context + slack)
     del weights
     runner, sampler = engine.runner, engine.sampler
     for t in runner.storage.paged:                        # pages that no prompt wrote hold random numbers
