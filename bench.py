@@ -200,8 +200,12 @@ def e2e_run(engine, batch, context, warmup, steps, vocab):
     """The same decode steps through LLMEngine.step: host ids in, sampled ids out, every step."""
     import torch
     gen = torch.Generator().manual_seed(4321)
-    prompt_len = context - (warmup + steps) - 2 * batch - 2
-    for _ in range(batch):
+    # A request decodes while the prompts of the later ones are computed (a prompt takes `fill` steps): the
+    # earlier a request comes, the shorter its prompt, so that all of them end the timed steps just below
+    # `context` (and none crosses the context bound its decode graph was recorded for in mid-measurement).
+    fill = -(-context // PREFILL_TOKENS) + 1
+    for i in range(batch):
+        prompt_len = max(16, context - (warmup + steps) - (batch - 1 - i) * fill - 4)
         engine.add_request(torch.randint(0, vocab, (prompt_len,), generator=gen).tolist(),
                            max_tokens=engine.scheduler.config.max_model_len - prompt_len)
         while any(s.remaining > 1 for s in engine.scheduler.running) or engine.scheduler.waiting:
@@ -422,6 +426,7 @@ def main(argv=None):
     ap.add_argument("--context", type=int, default=4096)
     ap.add_argument("--size", default="8b", choices=sorted(SIZES), help="layer sizes of Qwen3-8B (default), 14B or 32B")
     ap.add_argument("--layers", type=int, default=None, help="fewer layers than the size has (both numbers are reported)")
+    ap.add_argument("--block-size", type=int, default=64, help="positions per page of the cache")
     ap.add_argument("--no-points", action="store_true", help="skip the batch 1 / 64 points and the prefill")
     ap.add_argument("--only-prefill", action="store_true", help="time the 2,048-token prefill alone (for profiling)")
     ap.add_argument("--no-e2e", action="store_true", help="skip the run through the Python entry point (for profiling)")
@@ -461,8 +466,8 @@ def main(argv=None):
     _, plan, weights = random_model(cfg, seed=0, dtype="bfloat16", device="cuda:0")
     if args.continuous:
         R, out_len, prompt_range = args.continuous, 512, (256, args.context // 2)
-        pages = R * (-(-(prompt_range[1] + out_len) // 16) + 1) + 64
-        engine = LLMEngine(plan=plan, weights=weights, dtype="bfloat16", kv_blocks=pages, block_size=16, max_batch_size=R,
+        pages = R * (-(-(prompt_range[1] + out_len) // args.block_size) + 1) + 64
+        engine = LLMEngine(plan=plan, weights=weights, dtype="bfloat16", kv_blocks=pages, block_size=args.block_size, max_batch_size=R,
                            max_num_batched_tokens=4096, prefill_chunk_size=512, max_model_len=args.context)
         del weights
         continuous_run(engine, min(R, 4), vocab, (256, 512), 16)          # warm-up: builds, graphs of the small buckets
@@ -474,7 +479,7 @@ def main(argv=None):
                "dtype": "bf16", "data": "synthetic (random weights N(0,0.02), uniform token ids)",
                "config": {"model": f"Qwen3-{args.size.upper()} layer sizes", "layers": args.layers, "layers_full": full_layers,
                           "context": args.context, "prompt_lengths": f"uniform in [{prompt_range[0]}, {prompt_range[1]}]",
-                          "generated_each": out_len, "block_size": 16, "max_num_batched_tokens": 4096,
+                          "generated_each": out_len, "block_size": args.block_size, "max_num_batched_tokens": 4096,
                           "prefill_chunk_size": 512, "timing": "wall clock around the whole run, host ids in and out"},
                "clocks": clocks.summary(w0, time.time())}
         print(json.dumps(out))
@@ -483,12 +488,12 @@ def main(argv=None):
     # In the end-to-end run the requests' prompts are computed one after the other while the earlier requests
     # already decode: every request needs room for the tokens it generates meanwhile.
     slack = 64 + args.batch * (args.context // PREFILL_TOKENS + 2)
-    pages = big * (-(-(args.context + slack) // 16) + 1) + PREFILL_TOKENS // 16 + 64
+    pages = big * (-(-(args.context + slack) // args.block_size) + 1) + PREFILL_TOKENS // args.block_size + 64
     if args.kv_blocks == "auto" or (args.kv_blocks is None and args.size == "32b"):
         pages = None                                      # the engine sizes the cache from what the weights leave
     elif args.kv_blocks is not None:
         pages = int(args.kv_blocks)
-    engine = LLMEngine(plan=plan, weights=weights, dtype="bfloat16", kv_blocks=pages, block_size=16, max_batch_size=big,
+    engine = LLMEngine(plan=plan, weights=weights, dtype="bfloat16", kv_blocks=pages, block_size=args.block_size, max_batch_size=big,
                        max_num_batched_tokens=PREFILL_TOKENS, prefill_chunk_size=PREFILL_TOKENS,
                        max_model_len=args.context + slack)
     del weights
@@ -520,7 +525,7 @@ def main(argv=None):
         "config": {"model": f"Qwen3-{args.size.upper()} layer sizes", "layers": args.layers, "layers_full": full_layers,
                    "hidden": cfg["hidden_size"], "heads": cfg["num_attention_heads"], "kv_heads": cfg["num_key_value_heads"],
                    "head_dim": cfg["head_dim"], "intermediate": cfg["intermediate_size"], "vocab": vocab,
-                   "global_batch": args.batch, "seq_len": args.context, "block_size": 16, "parallelism": "single GPU",
+                   "global_batch": args.batch, "seq_len": args.context, "block_size": args.block_size, "parallelism": "single GPU",
                    "kv_fill": "real prefill" if args.kv_fill == "prefill" else "random numbers", "l2": f"inputs (weights {weight_bytes / 1e9:.0f} GB) larger than L2, no flush",
                    "peaks": pk["source"], "kv_pages": sum(p.size for p in runner.cache.pools)},
         "clocks": clocks.summary(w0, w1),

@@ -120,11 +120,15 @@ def test_mixed_with_page_reuse(which, dtype):
 
 @pytest.mark.parametrize("page_size", [16, 64])
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-def test_long_portions_and_head_size_64(dtype, page_size):
+def test_long_portions_and_head_size_64(dtype, page_size, monkeypatch):
     """A configuration with 64-wide heads and prompts of several hundred tokens: in bfloat16 the
     portions of more than 64 tokens run on the tcgen05 attention kernel and, with pages of 64
-    positions, decoding on the persistent TMA kernel.  Whole prompt; two long portions and 32 tokens
-    one by one; and steps that hold a long portion of one request beside decoded tokens of two others."""
+    positions, decoding on the persistent TMA kernel (which the engine picks for steps that read many
+    keys: the bound is lowered here so that this small model's steps take it).  Whole prompt; two long
+    portions and 32 tokens one by one; and steps that hold a long portion of one request beside decoded
+    tokens of two others."""
+    from vllm_lite_b200.csrc import ops
+    monkeypatch.setattr(ops, "STREAM_DECODE_MIN_KEYS", 0)
     which = "C"
     toks = H.tokens_for(which, 332, 41)
     pages = -(-400 // page_size) + 2

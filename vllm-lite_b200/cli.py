@@ -62,7 +62,8 @@ def build_parser() -> argparse.ArgumentParser:
                     default=_env("VLLM_KV_QUANTIZATION", "false").lower() in ("1", "true"))
     ap.add_argument("--log-level", default=_env("VLLM_LOG_LEVEL", "info"))
     ap.add_argument("--dtype", choices=["bfloat16", "float32"], default="bfloat16")
-    ap.add_argument("--block-size", type=_bounded(1, 256, "--block-size"), default=16)
+    ap.add_argument("--block-size", type=_bounded(1, 256, "--block-size"), default=64,
+                    help="positions per page of the cache (the reference's constant is 16; 64 suits the TMA copies)")
     ap.add_argument("--max-num-batched-tokens", type=int, default=4096)
     ap.add_argument("--prefill-chunk-size", type=int, default=512)
     ap.add_argument("--prompt-ids", action="append", default=[],

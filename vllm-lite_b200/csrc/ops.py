@@ -68,6 +68,9 @@ _SIGNATURES = {
                                        c_void_p, c_int, c_void_p],
     ("gemm_tc5_pair", "vl_gemm_bf16_tc5_pair"): [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
                                                  c_void_p, c_int, c_void_p],
+    ("gemm_tc5_stream", "vl_gemm_bf16_stream_tc5"): [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
+                                                     c_void_p, c_int, c_void_p, c_int, c_float, c_int, c_void_p, c_int,
+                                                     c_void_p, c_void_p, c_void_p, c_void_p],
     ("memprobe", "vl_read_only"): [c_void_p, c_longlong, c_void_p, c_void_p],
     ("sampling", "vl_apply_penalties"): [c_void_p, c_longlong, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p,
                                          c_void_p, c_void_p, c_void_p, c_void_p],
@@ -370,6 +373,9 @@ def flash_decode_arrivals(num_tokens, num_heads, num_kv_heads) -> int:
     return num_tokens * num_kv_heads * -(-(num_heads // num_kv_heads) // 16)
 
 
+STREAM_DECODE_MIN_KEYS = 8 * 49152      # tokens x KV heads x context bound from which the persistent TMA kernel is used
+
+
 def flash_decode(qkv, out, k_cache, v_cache, block_table, req_index, positions, num_heads, num_kv_heads,
                  head_dim, scale, window, max_context, part_acc, part_ml, err, chunk=DECODE_CHUNK, token_index=None,
                  stream_kernel=None, arrivals=None):
@@ -377,9 +383,9 @@ def flash_decode(qkv, out, k_cache, v_cache, block_table, req_index, positions, 
     keys; the chunks are merged by the block that finishes last (`arrivals`: int32 counters,
     `flash_decode_arrivals` of them, zero before the first call and left zero) or, without
     `arrivals`, by a second kernel.
-    The split pass is the persistent TMA kernel where it takes the head size and pages hold at
-    least 64 positions (`stream_kernel`: None = that rule, True / False to force; it always merges
-    with the second kernel), else a block per chunk.
+    The split pass is the persistent TMA kernel where it takes the head size, pages hold at
+    least 64 positions and the step reads STREAM_DECODE_MIN_KEYS keys or more (`stream_kernel`: None =
+    that rule, True / False to force; it always merges with the second kernel), else a block per chunk.
     `token_index` (int32) restricts the launch to some tokens of the step (the others' rows of `out`
     are left alone); the scratch is then sized for that many tokens."""
     _flash_checks(qkv, k_cache, v_cache, block_table, num_heads, num_kv_heads, head_dim)
@@ -395,8 +401,13 @@ def flash_decode(qkv, out, k_cache, v_cache, block_table, req_index, positions, 
     S, need_acc, need_ml = decode_attention_scratch(T, num_heads, head_dim, max_context, chunk)
     if part_acc.numel() < need_acc or part_ml.numel() < need_ml:
         raise KernelError(f"flash_decode: scratch too small ({part_acc.numel()} < {need_acc})")
-    if stream_kernel is None:           # measured: it wins from 64-position pages on (TMA boxes of 8 KB, not 2 KB)
-        stream_kernel = flash_tc5_supported(qkv.dtype, head_dim, k_cache.shape[2]) and k_cache.shape[2] >= 64
+    if stream_kernel is None:
+        # measured (Qwen3-8B heads, pages of 64): it wins from 64-position pages on (TMA boxes of 8 KB, not 2 KB)
+        # when the step streams enough keys to keep every SM's block busy: 16 tokens x 4,096 keys 55.8 us
+        # against 60.0 for a block per chunk, 64 x 4,096: 170 against 188, 8 x 16,384: 96 against 108; at
+        # 8 x 4,096 and below the block per chunk, which merges in the same launch, is level or ahead
+        stream_kernel = (flash_tc5_supported(qkv.dtype, head_dim, k_cache.shape[2]) and k_cache.shape[2] >= 64
+                         and T * num_kv_heads * int(max_context) >= STREAM_DECODE_MIN_KEYS)
     args = (_ptr(qkv), qkv.shape[1], _ptr(k_cache), _ptr(v_cache), _ptr(block_table), block_table.shape[1],
             _ptr(req_index), _ptr(positions), T, num_heads, num_kv_heads, head_dim, k_cache.shape[2], k_cache.shape[0],
             float(scale), int(window or 0), chunk, S, _ptr(part_acc), _ptr(part_ml), _ptr(err), _ptr(token_index))
@@ -499,6 +510,47 @@ def gemm_bf16_small_m(a, w, out, err=None, swiglu=False, scaled=None, sink=None)
         if not 0 < grid.value <= NORM_PARTIALS:
             raise KernelError(f"gemm_bf16_small_m: {grid.value} blocks do not fit the partial sums")
         return grid.value
+    return out
+
+
+STREAM_MAX_M = 64         # most rows of the tcgen05 weight-streaming product (csrc/gemm_tc5_stream.cu)
+STREAM_SS_STRIDE = 64     # floats between two vectors of its partial sums of squares
+
+
+def gemm_bf16_stream_ok(M, K) -> bool:
+    """Steps of 9 to 64 rows: the weight stream on tcgen05 (128 rows of the weight by all rows of the step a tile)."""
+    return SMALL_M < M <= STREAM_MAX_M and K % 8 == 0
+
+
+def gemm_bf16_stream(a, w, out, err=None, swiglu=False, scaled=None, sink=None):
+    """out[M, N] = a[M, K] @ w[N, K]^T for M <= 64 on the tcgen05 tensor cores, bound by one read of w;
+    `swiglu`, `scaled` and `sink` as in `gemm_bf16_small_m`, the vectors of partial sums being
+    STREAM_SS_STRIDE floats apart."""
+    M, N, K, width = _gemm_shapes(a, w, out, swiglu)
+    if M > STREAM_MAX_M:
+        raise KernelError(f"gemm_bf16_stream: {M} rows, at most {STREAM_MAX_M}")
+    ss_in, count, eps, size = (None, 0, 0.0, 0) if scaled is None else scaled
+    x, next_w, ss_out = (None, None, None) if sink is None else sink
+    if scaled is not None:
+        _need(ss_in, torch.float32, "partial", 2)
+        if ss_in.shape[1] != STREAM_SS_STRIDE or not 0 < count <= ss_in.shape[0] or size != K:
+            raise KernelError("gemm_bf16_stream: partial sums do not match the product")
+    vectors = ctypes.c_int(0)
+    if sink is not None:
+        _need(x, torch.float32, "x", 2); _need(next_w, torch.float32, "next_weight", 1)
+        _need(ss_out, torch.float32, "partial_out", 2)
+        if x.shape != (M, N) or next_w.shape[0] != N or ss_out.shape != (NORM_PARTIALS, STREAM_SS_STRIDE) or swiglu:
+            raise KernelError("gemm_bf16_stream: the stream, the next weight or the partial sums do not match")
+        if -(-N // 128) * 8 > NORM_PARTIALS:
+            raise KernelError(f"gemm_bf16_stream: {N} columns leave more partial sums than {NORM_PARTIALS} vectors hold")
+    _check(_fn("gemm_tc5_stream", "vl_gemm_bf16_stream_tc5")(
+        _ptr(a), _ptr(w), _ptr(out), dtype_code(out.dtype), M, N, K, K, K, width, _ptr(err), int(swiglu),
+        _ptr(ss_in), int(count), float(eps), int(size), _ptr(x), N, _ptr(next_w), _ptr(ss_out),
+        ctypes.addressof(vectors), _stream()), "vl_gemm_bf16_stream_tc5")
+    if sink is not None:
+        if not 0 < vectors.value <= NORM_PARTIALS:
+            raise KernelError(f"gemm_bf16_stream: {vectors.value} vectors do not fit the partial sums")
+        return vectors.value
     return out
 
 

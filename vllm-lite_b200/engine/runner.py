@@ -65,7 +65,7 @@ def _pow2_at_least(n: int, floor: int = 1) -> int:
 
 
 class ModelRunner:
-    def __init__(self, plan, weights: dict, *, dtype=torch.bfloat16, device="cuda:0", page_size: int = 16,
+    def __init__(self, plan, weights: dict, *, dtype=torch.bfloat16, device="cuda:0", page_size: int = 64,
                  num_pages=1024, max_requests: int = 256, decode_graphs: bool = True,
                  max_context: Optional[int] = None, native_host: bool = True, memory_fraction: float = 0.9,
                  max_step_tokens: int = 4096, own_weights: bool = False, free_memory_bytes: Optional[int] = None):
