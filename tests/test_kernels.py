@@ -181,77 +181,7 @@ def test_gemm_small_m_with_fused_norms(M, H, K, N2, swiglu):
     assert float((out.double() - y).abs().max()) <= 2e-2 * float(y.abs().max()) + 1e-3
 
 
-@pytest.mark.parametrize("out_dtype", [torch.bfloat16, torch.float32])
-@pytest.mark.parametrize("M,N,K", [(9, 333, 96), (16, 6144, 4096), (17, 50, 200), (33, 1000, 264), (64, 160, 4096),
-                                   (12, 17, 8), (64, 4096, 12288), (40, 24576, 4096), (64, 20000, 520), (1, 128, 64),
-                                   (24, 4096, 4096), (64, 700, 2056)])
-def test_gemm_bf16_stream(M, N, K, out_dtype):
-    """The weight stream on tcgen05 for up to 64 rows: tiles of 128 rows of w, K cut among the blocks of a
-    cluster where the tiles are few (their sums added in rank order), several tiles a block where they
-    are many; ragged M, N and K."""
-    torch.manual_seed(M * N + K)
-    a = torch.randn(M, K, device=DEV).to(torch.bfloat16)
-    w = (torch.randn(N, K, device=DEV) * 0.05).to(torch.bfloat16)
-    out = torch.full((M, N), float("nan"), device=DEV, dtype=out_dtype)
-    e = err_word()
-    ops().gemm_bf16_stream(a, w, out, e)
-    assert int(e.item()) == 0
-    ref = a.double() @ w.double().T
-    scale = float(ref.abs().max())
-    if out_dtype == torch.float32:
-        assert float((out.double() - ref).abs().max()) <= 1e-5 * scale * (K ** 0.5)
-    else:
-        assert float((out.double() - ref).abs().max()) <= 2 ** -8 * scale + 1e-6
-    # a row's result does not depend on the other rows of the launch, bit for bit, whatever their number
-    # (16, 32 and 64 rows a tile cut K and add alike)
-    for m2 in (1, 17, 64):
-        other = torch.randn(m2, K, device=DEV).to(torch.bfloat16)
-        other[m2 - 1] = a[M - 1]
-        again = torch.empty(m2, N, device=DEV, dtype=out_dtype)
-        ops().gemm_bf16_stream(other, w, again, e)
-        assert torch.equal(again[m2 - 1], out[M - 1])
-    assert int(e.item()) == 0
-
-
-@pytest.mark.parametrize("M,H,K,N2,swiglu", [(9, 96, 64, 80, False), (64, 4096, 4096, 6144, False), (21, 200, 520, 48, True),
-                                               (33, 1000, 264, 64, True), (64, 4096, 12288, 24576, True),
-                                               (16, 5120, 1024, 256, False), (48, 2048, 6144, 12288, True)])
-def test_gemm_stream_with_fused_norms(M, H, K, N2, swiglu):
-    """As `test_gemm_small_m_with_fused_norms`, for the 9 to 64 rows of the tcgen05 stream: the first product
-    adds into the float32 stream and leaves the norm's input times its weight and the sums of squares,
-    the second scales its rows (and applies SwiGLU)."""
-    torch.manual_seed(M + H)
-    eps = 1e-5
-    x = torch.randn(M, H, device=DEV) * 3
-    a = torch.randn(M, K, device=DEV).to(torch.bfloat16)
-    w1 = (torch.randn(H, K, device=DEV) * 0.05).to(torch.bfloat16)
-    nw = 1 + 0.1 * torch.randn(H, device=DEV)
-    w2 = (torch.randn(N2, H, device=DEV) * 0.05).to(torch.bfloat16)
-    x_new = x.double() + a.double() @ w1.double().T
-    h = x_new / torch.sqrt((x_new * x_new).mean(dim=1, keepdim=True) + eps) * nw.double()
-    y = h @ w2.double().T
-    if swiglu:
-        y = y.view(M, N2 // 16, 2, 8)
-        y = (torch.nn.functional.silu(y[:, :, 0]) * y[:, :, 1]).reshape(M, N2 // 2)
-    stream = x.clone()
-    rows = torch.empty(M, H, device=DEV, dtype=torch.bfloat16)
-    stride = ops().STREAM_SS_STRIDE
-    partial = torch.full((ops().NORM_PARTIALS, stride), float("nan"), device=DEV)
-    e = err_word()
-    count = ops().gemm_bf16_stream(a, w1, rows, e, sink=(stream, nw, partial))
-    assert 0 < count <= ops().NORM_PARTIALS
-    assert float((stream.double() - x_new).abs().max()) <= 1e-5 * float(x_new.abs().max()) * K ** 0.5
-    assert torch.allclose(rows.double(), x_new * nw.double(), atol=2 ** -7 * float(x_new.abs().max()), rtol=0)
-    assert not torch.isnan(partial[:count, :M]).any()                  # every entry written by some group
-    ss = partial[:count, :M].double().sum(dim=0)
-    assert torch.allclose(ss, (x_new * x_new).sum(dim=1), rtol=1e-5)
-    out = torch.empty(M, N2 // 2 if swiglu else N2, device=DEV, dtype=torch.bfloat16)
-    ops().gemm_bf16_stream(rows, w2, out, e, swiglu=swiglu, scaled=(partial, count, eps, H))
-    assert int(e.item()) == 0
-    assert float((out.double() - y).abs().max()) <= 2e-2 * float(y.abs().max()) + 1e-3
-
-
-@pytest.mark.parametrize("kernel,M", [("small_m", 1), ("small_m", 8), ("small_m", 13), ("stream", 9), ("stream", 64), ("tc5", 128), ("tc5", 300), ("tc5", 2048),
+@pytest.mark.parametrize("kernel,M", [("small_m", 1), ("small_m", 8), ("small_m", 13), ("tc5", 128), ("tc5", 300), ("tc5", 2048),
                                       ("tc5_pair", 300), ("tc5_pair", 2048)])
 @pytest.mark.parametrize("I,K", [(160, 96), (12288, 4096), (24, 64)])
 def test_gemm_with_fused_swiglu(kernel, M, I, K):
@@ -263,8 +193,7 @@ def test_gemm_with_fused_swiglu(kernel, M, I, K):
     w = torch.stack([gate.view(I // 8, 8, K), up.view(I // 8, 8, K)], dim=1).reshape(2 * I, K).contiguous()
     out = torch.full((M, I), float("nan"), device=DEV, dtype=torch.bfloat16)
     e = err_word()
-    fn = {"small_m": ops().gemm_bf16_small_m, "stream": ops().gemm_bf16_stream, "tc5": ops().gemm_bf16_tc5,
-          "tc5_pair": ops().gemm_bf16_tc5_pair}[kernel]
+    fn = {"small_m": ops().gemm_bf16_small_m, "tc5": ops().gemm_bf16_tc5, "tc5_pair": ops().gemm_bf16_tc5_pair}[kernel]
     fn(a, w, out, e, swiglu=True)
     assert int(e.item()) == 0
     g, u = a.double() @ gate.double().T, a.double() @ up.double().T

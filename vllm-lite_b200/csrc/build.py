@@ -23,7 +23,7 @@ from pathlib import Path
 CSRC = Path(__file__).resolve().parent
 ARCH_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a"]
 NVCC_FLAGS = ARCH_FLAGS + ["-O3", "-lineinfo", "-std=c++17", "--shared", "-Xcompiler", "-fPIC"]
-SOURCES = ("embed_norm", "rope_cache", "attention", "activation", "gemm_f32", "gemm_bf16", "gemm_tc5", "gemm_tc5_pair", "gemm_tc5_stream", "sampling",
+SOURCES = ("embed_norm", "rope_cache", "attention", "activation", "gemm_f32", "gemm_bf16", "gemm_tc5", "gemm_tc5_pair", "sampling",
            "memprobe")
 # sources compiled once per value of a constant; the values here are what build_all() prepares,
 # any other allowed value is compiled when a model first needs it

@@ -68,9 +68,6 @@ _SIGNATURES = {
                                        c_void_p, c_int, c_void_p],
     ("gemm_tc5_pair", "vl_gemm_bf16_tc5_pair"): [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
                                                  c_void_p, c_int, c_void_p],
-    ("gemm_tc5_stream", "vl_gemm_bf16_stream_tc5"): [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
-                                                     c_void_p, c_int, c_void_p, c_int, c_float, c_int, c_void_p, c_int,
-                                                     c_void_p, c_void_p, c_void_p, c_void_p],
     ("memprobe", "vl_read_only"): [c_void_p, c_longlong, c_void_p, c_void_p],
     ("sampling", "vl_apply_penalties"): [c_void_p, c_longlong, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p,
                                          c_void_p, c_void_p, c_void_p, c_void_p],
@@ -510,47 +507,6 @@ def gemm_bf16_small_m(a, w, out, err=None, swiglu=False, scaled=None, sink=None)
         if not 0 < grid.value <= NORM_PARTIALS:
             raise KernelError(f"gemm_bf16_small_m: {grid.value} blocks do not fit the partial sums")
         return grid.value
-    return out
-
-
-STREAM_MAX_M = 64         # most rows of the tcgen05 weight-streaming product (csrc/gemm_tc5_stream.cu)
-STREAM_SS_STRIDE = 64     # floats between two vectors of its partial sums of squares
-
-
-def gemm_bf16_stream_ok(M, K) -> bool:
-    """Steps of 9 to 64 rows: the weight stream on tcgen05 (128 rows of the weight by all rows of the step a tile)."""
-    return SMALL_M < M <= STREAM_MAX_M and K % 8 == 0
-
-
-def gemm_bf16_stream(a, w, out, err=None, swiglu=False, scaled=None, sink=None):
-    """out[M, N] = a[M, K] @ w[N, K]^T for M <= 64 on the tcgen05 tensor cores, bound by one read of w;
-    `swiglu`, `scaled` and `sink` as in `gemm_bf16_small_m`, the vectors of partial sums being
-    STREAM_SS_STRIDE floats apart."""
-    M, N, K, width = _gemm_shapes(a, w, out, swiglu)
-    if M > STREAM_MAX_M:
-        raise KernelError(f"gemm_bf16_stream: {M} rows, at most {STREAM_MAX_M}")
-    ss_in, count, eps, size = (None, 0, 0.0, 0) if scaled is None else scaled
-    x, next_w, ss_out = (None, None, None) if sink is None else sink
-    if scaled is not None:
-        _need(ss_in, torch.float32, "partial", 2)
-        if ss_in.shape[1] != STREAM_SS_STRIDE or not 0 < count <= ss_in.shape[0] or size != K:
-            raise KernelError("gemm_bf16_stream: partial sums do not match the product")
-    vectors = ctypes.c_int(0)
-    if sink is not None:
-        _need(x, torch.float32, "x", 2); _need(next_w, torch.float32, "next_weight", 1)
-        _need(ss_out, torch.float32, "partial_out", 2)
-        if x.shape != (M, N) or next_w.shape[0] != N or ss_out.shape != (NORM_PARTIALS, STREAM_SS_STRIDE) or swiglu:
-            raise KernelError("gemm_bf16_stream: the stream, the next weight or the partial sums do not match")
-        if -(-N // 128) * 8 > NORM_PARTIALS:
-            raise KernelError(f"gemm_bf16_stream: {N} columns leave more partial sums than {NORM_PARTIALS} vectors hold")
-    _check(_fn("gemm_tc5_stream", "vl_gemm_bf16_stream_tc5")(
-        _ptr(a), _ptr(w), _ptr(out), dtype_code(out.dtype), M, N, K, K, K, width, _ptr(err), int(swiglu),
-        _ptr(ss_in), int(count), float(eps), int(size), _ptr(x), N, _ptr(next_w), _ptr(ss_out),
-        ctypes.addressof(vectors), _stream()), "vl_gemm_bf16_stream_tc5")
-    if sink is not None:
-        if not 0 < vectors.value <= NORM_PARTIALS:
-            raise KernelError(f"gemm_bf16_stream: {vectors.value} vectors do not fit the partial sums")
-        return vectors.value
     return out
 
 
