@@ -319,14 +319,13 @@ static int launch_small_m(const bf16* A, const bf16* W, TO* C, int M, int N, int
     // Measured on the shapes of decode steps (Qwen3-8B, 8 rows, microseconds inside a step): with tiles for
     // two blocks per SM or more, four stages of 512 columns, three blocks per SM (q/k/v 10.0, gate/up 31.6,
     // vocabulary head 185.4; with three stages of 768: 10.6, 34.0, 188.5); with fewer tiles every block is
-    // resident and larger stages keep more bytes in flight: three of 768 (o: 8.8 against 9.0), and, when K
-    // is long, three of 1,024, two blocks per SM (down: 18.2 against 19.5).  Less than about 200 KB in flight
-    // per SM loses outright (two blocks of 50 KB: 16.2 / 48.2 / 24.8 for q/k/v, gate/up, down).  More rows
-    // need the registers and keep four stages of 512 columns.
+    // resident at once and larger stages keep more bytes in flight: three of 1,024, two blocks per SM (o: 8.0
+    // against 8.8 with three of 768 and 9.0 with four of 512; down: 18.2 against 19.5).  Less than about
+    // 200 KB in flight per SM loses outright (two blocks of 50 KB: 16.2 / 48.2 / 24.8 for q/k/v, gate/up,
+    // down).  More rows need the registers and keep four stages of 512 columns.
     if (M <= 8) {
         const int tiles16 = (N + GS_ROWS - 1) / GS_ROWS;
-        if (tiles16 <= 2 * num_sms && K >= 8192) GS_LAUNCH(1, 1024, 3)
-        if (tiles16 < 2 * num_sms) GS_LAUNCH(1, 768, 3)
+        if (tiles16 <= 2 * num_sms) GS_LAUNCH(1, 1024, 3)
         GS_LAUNCH(1, 512, 4)
     }
     GS_LAUNCH(2, 512, 4)
