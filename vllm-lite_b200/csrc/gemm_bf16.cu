@@ -287,6 +287,42 @@ gemm_bf16_small_m_kernel(const bf16* __restrict__ A, const bf16* __restrict__ W,
     }
 }
 
+// One shape of the ring (columns a stage, stages) of the kernel for MT * 8 rows: its shared memory, how
+// many of its blocks share an SM, and the grid for a product of `tiles` tiles of 16 rows.
+// A block per tile, or, when that gives more blocks than fit on the device at once, the fewest blocks that
+// need no more tiles each than that many would (1,536 tiles for 444 places: 384 blocks of 4 tiles, not
+// 444 blocks of 3 or 4), each with an even share of the rows (for the fused activation: of the 16-row
+// groups): all blocks end together, and the stream is bound by memory, not by the blocks' number (a decode
+// step at batch 8: 3.99 -> 3.92 ms).
+template <int MT, typename TO, int KC, int STAGES>
+struct RingShape {
+    static constexpr size_t smem = (size_t)STAGES * GS_ROWS * (KC * 2 + 16);
+    static constexpr long long in_flight = (long long)STAGES * GS_ROWS * KC * 2;     // bytes of W a block keeps on their way
+    static int per_sm() {
+        static int v = 0;
+        if (!v) {
+            auto kern = gemm_bf16_small_m_kernel<MT, TO, KC, STAGES>;
+            if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess ||
+                cudaOccupancyMaxActiveBlocksPerMultiprocessor(&v, kern, 160, smem) != cudaSuccess || v < 1)
+                v = 1;
+        }
+        return v;
+    }
+    static int blocks(int tiles, int num_sms) {
+        const int fit = num_sms * per_sm();
+        const int rounds = (tiles + fit - 1) / fit;               // tiles of the busiest block
+        return tiles < fit ? tiles : (tiles + rounds - 1) / rounds;
+    }
+    static int launch(const bf16* A, const bf16* W, TO* C, int M, int N, int K, int lda, int ldw, int ldc, unsigned* err,
+                      int swiglu, NormFusion nf, int* grid_out, int num_sms, cudaStream_t s) {
+        auto kern = gemm_bf16_small_m_kernel<MT, TO, KC, STAGES>;
+        const int grid = blocks((N + GS_ROWS - 1) / GS_ROWS, num_sms);
+        if (grid_out) *grid_out = grid;
+        return vl_launch(kern, dim3(grid), dim3(160), smem, s, A, W, C, M, N, K, lda, ldw, ldc, err, swiglu,
+                         swiglu ? GS_ROWS : 1, nf);
+    }
+};
+
 template <typename TO>
 static int launch_small_m(const bf16* A, const bf16* W, TO* C, int M, int N, int K, int lda, int ldw, int ldc,
                           unsigned* err, int swiglu, NormFusion nf, int* grid_out, cudaStream_t s) {
@@ -296,40 +332,40 @@ static int launch_small_m(const bf16* A, const bf16* W, TO* C, int M, int N, int
         cudaGetDevice(&dev);
         if (cudaDeviceGetAttribute(&num_sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || num_sms <= 0) num_sms = 148;
     }
-    // A block per tile of 16 rows, or, when that gives more blocks than fit on the device at once, the
-    // fewest blocks that need no more tiles each than that many would (1,536 tiles for 444 places: 384
-    // blocks of 4 tiles, not 444 blocks of 3 or 4), each with an even share of the rows (for the fused
-    // activation: of the 16-row groups): all blocks end together, and the stream is bound by memory, not
-    // by the blocks' number (a decode step at batch 8: 3.99 -> 3.92 ms).
-#define GS_LAUNCH(MT, KC, STAGES)                                                                          \
-    {                                                                                                      \
-        const size_t smem = (size_t)STAGES * GS_ROWS * (KC * 2 + 16);                                      \
-        auto kern = gemm_bf16_small_m_kernel<MT, TO, KC, STAGES>;                                          \
-        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
-        if (e != cudaSuccess) return (int)e;                                                               \
-        static int per_sm = 0;                                                                             \
-        if (!per_sm && (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kern, 160, smem) != cudaSuccess || per_sm < 1)) per_sm = 1; \
-        const int tiles = (N + GS_ROWS - 1) / GS_ROWS, fit = num_sms * per_sm;                             \
-        const int gran = swiglu ? GS_ROWS : 1;                                                             \
-        const int rounds = (tiles + fit - 1) / fit;              /* tiles of the busiest block */          \
-        dim3 grid(tiles < fit ? tiles : (tiles + rounds - 1) / rounds);                                    \
-        if (grid_out) *grid_out = (int)grid.x;                                                             \
-        return vl_launch(kern, grid, dim3(160), smem, s, A, W, C, M, N, K, lda, ldw, ldc, err, swiglu, gran, nf); \
+#define GS_ARGS A, W, C, M, N, K, lda, ldw, ldc, err, swiglu, nf, grid_out, num_sms, s
+    if (M > 8) return RingShape<2, TO, 512, 4>::launch(GS_ARGS);   // more rows need the registers
+    // Up to 8 rows.  What decides is how many bytes of W the launch keeps on their way: memory answers after
+    // 3 to 5 us under load, so about 23 MB must be in flight for its full bandwidth (measured inside a decode
+    // step's graph, 8 rows, over the layer shapes of Qwen3-8B, 14B and 32B).  The shapes, finest stages first:
+    // 4 x 512 columns (three blocks per SM), 3 x 768 (three), 2 x 1,024 (three), 3 x 1,024 (two per SM).  The
+    // first whose blocks, all resident, hold 22.5 MB is taken, else the one that holds most.  For instance
+    // (us): q/k/v of 8B, 384 tiles: 9.8 with 4 x 512 against 10.1 and 11.1 with 3 x 768 and 3 x 1,024; o of 8B,
+    // 256 tiles: 7.7 with 3 x 1,024 against 8.5; q/k/v of 14B, 448 tiles (one more than 444 places: 224 blocks of
+    // two tiles): 13.7 with 3 x 1,024 against 18.7 with 4 x 512; down of 32B, 320 tiles, K = 25,600: 42.6 with
+    // 3 x 768 against 46.6 and 50.3.  Less than about 200 KB in flight per SM loses outright (two blocks of
+    // 50 KB: 16.2 / 48.2 / 24.8 us for q/k/v, gate/up, down of 8B against 10.6 / 34.0 / 18.2).
+    using S0 = RingShape<1, TO, 512, 4>;
+    using S1 = RingShape<1, TO, 768, 3>;
+    using S2 = RingShape<1, TO, 1024, 2>;
+    using S3 = RingShape<1, TO, 1024, 3>;
+    const int tiles = (N + GS_ROWS - 1) / GS_ROWS;
+    const long long held[4] = {S0::blocks(tiles, num_sms) * S0::in_flight, S1::blocks(tiles, num_sms) * S1::in_flight,
+                               S2::blocks(tiles, num_sms) * S2::in_flight, S3::blocks(tiles, num_sms) * S3::in_flight};
+    int pick = -1;
+    for (int i = 0; i < 4 && pick < 0; ++i)
+        if (held[i] >= 22500000ll) pick = i;
+    if (pick < 0) {
+        pick = 0;
+        for (int i = 1; i < 4; ++i)
+            if (held[i] > held[pick]) pick = i;
     }
-    // Measured on the shapes of decode steps (Qwen3-8B, 8 rows, microseconds inside a step): with tiles for
-    // two blocks per SM or more, four stages of 512 columns, three blocks per SM (q/k/v 10.0, gate/up 31.6,
-    // vocabulary head 185.4; with three stages of 768: 10.6, 34.0, 188.5); with fewer tiles every block is
-    // resident at once and larger stages keep more bytes in flight: three of 1,024, two blocks per SM (o: 8.0
-    // against 8.8 with three of 768 and 9.0 with four of 512; down: 18.2 against 19.5).  Less than about
-    // 200 KB in flight per SM loses outright (two blocks of 50 KB: 16.2 / 48.2 / 24.8 for q/k/v, gate/up,
-    // down).  More rows need the registers and keep four stages of 512 columns.
-    if (M <= 8) {
-        const int tiles16 = (N + GS_ROWS - 1) / GS_ROWS;
-        if (tiles16 <= 2 * num_sms) GS_LAUNCH(1, 1024, 3)
-        GS_LAUNCH(1, 512, 4)
+    switch (pick) {
+        case 0: return S0::launch(GS_ARGS);
+        case 1: return S1::launch(GS_ARGS);
+        case 2: return S2::launch(GS_ARGS);
+        default: return S3::launch(GS_ARGS);
     }
-    GS_LAUNCH(2, 512, 4)
-#undef GS_LAUNCH
+#undef GS_ARGS
 }
 
 // The product with an RMS norm fused on its input side (ss_in != null), on its output side
