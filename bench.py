@@ -392,7 +392,7 @@ def read_ceiling(cfg, batch, context):
     o = torch.empty(batch, nq * hd, device=dev, dtype=torch.bfloat16)
     req = torch.arange(batch, dtype=torch.int32, device=dev)
     pos = torch.full((batch,), context - 1, dtype=torch.int32, device=dev)
-    chunk = ops.decode_chunk_for(batch, nkv, context)
+    chunk = ops.decode_chunk_for(batch, nkv, context, head_dim=hd)
     S, na, nm = ops.decode_attention_scratch(batch, nq, hd, context, chunk)
     pa, pm = torch.empty(na, device=dev), torch.empty(nm, device=dev)
     arr = torch.zeros(ops.flash_decode_arrivals(batch, nq, nkv), dtype=torch.int32, device=dev)

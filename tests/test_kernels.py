@@ -519,6 +519,20 @@ def _decode_attention_split(kernel, dtype, nq, nkv, hd, page, window, lens, seqs
         assert bool((out[T - 1] == 0).all())
 
 
+@pytest.mark.parametrize("nq,nkv,hd,page", [(8, 2, 128, 64), (6, 3, 64, 16), (4, 1, 32, 8)])
+def test_decode_attention_merges_up_to_16_chunks_in_a_cluster(nq, nkv, hd, page):
+    """Few tokens with 9 to 16 chunks each: the chunks of a token are the blocks of one cluster (beyond the
+    portable 8 where the device takes it, else the last block to arrive merges); requests of other lengths
+    beside them leave some blocks of a cluster without keys."""
+    most = ops().flash_decode_max_cluster(hd)
+    assert most in (8, 16)
+    torch.manual_seed(nq + hd)
+    lens = [1000, 577, 3]
+    seqs = [(torch.randn(n, nkv, hd), torch.randn(n, nkv, hd)) for n in lens]
+    _decode_attention_split("flash_decode64own", torch.bfloat16, nq, nkv, hd, page, 0, lens, seqs, "shuffled")
+    _decode_attention_split("flash_decode64own", torch.bfloat16, nq, nkv, hd, page, 400, lens, seqs, "in a row")
+
+
 @pytest.mark.parametrize("kernel,dtype", attention_cases())
 @pytest.mark.parametrize("far,window", [(3, 0), (640, 0), (15, 0), (16, 0), (63, 0), (64, 0), (255, 0), (256, 0),
                                         (700, 300), (699, 300)])

@@ -303,7 +303,8 @@ __device__ __forceinline__ float dec_ld_cluster(unsigned cluster_addr) {
 __device__ __forceinline__ void dec_cluster_sync() {
     asm volatile("barrier.cluster.arrive.release.aligned;\n barrier.cluster.wait.acquire.aligned;" ::: "memory");
 }
-constexpr int DEC_MAX_CLUSTER = 8;                   // most chunks of a token that a cluster merges (portable cluster size)
+constexpr int DEC_MAX_CLUSTER = 16;                  // most chunks of a token that a cluster merges (8 is the portable cluster
+                                                     // size; 16 where the device takes it: vl_flash_decode_max_cluster)
 
 // The chunks of a token and its heads are the blocks of one cluster.  Every block has left its partial
 // result in its shared memory (bO [rows][HD], bM maxima in units of log2, bL sums); block `rank` of
@@ -618,6 +619,36 @@ flash_decode_kernel(const bf16* __restrict__ q, int q_stride,
     }
 }
 
+// The largest cluster the decode kernel may be launched as on this device: 16 where clusters beyond the
+// portable size are allowed and one fits, else 8.
+static int decode_max_cluster() {
+    static int v = 0;
+    if (!v) {
+        v = 8;
+        if (cudaFuncSetAttribute(flash_decode_kernel, cudaFuncAttributeNonPortableClusterSizeAllowed, 1) == cudaSuccess) {
+            const size_t ring = (size_t)DEC_NST * 2 * BN * LDS * sizeof(bf16);
+            const size_t merge = (size_t)(4 * DEC_ROWS * (HD + 4) + DEC_ROWS * HD) * sizeof(float);
+            const size_t smem = (size_t)DEC_ROWS * LDS * sizeof(bf16) + (ring > merge ? ring : merge);
+            cudaLaunchConfig_t cfg = {};
+            cfg.gridDim = dim3(16, 1, 1);
+            cfg.blockDim = dim3(NTHREADS);
+            cfg.dynamicSmemBytes = smem;
+            cudaLaunchAttribute attr[1];
+            attr[0].id = cudaLaunchAttributeClusterDimension;
+            attr[0].val.clusterDim.x = 16; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
+            cfg.attrs = attr;
+            cfg.numAttrs = 1;
+            int clusters = 0;
+            if (cudaFuncSetAttribute(flash_decode_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) == cudaSuccess &&
+                cudaOccupancyMaxActiveClusters(&clusters, flash_decode_kernel, &cfg) == cudaSuccess && clusters >= 8)
+                v = 16;
+        }
+        cudaGetLastError();                                      // a refusal above is an answer, not an error of the step
+    }
+    return v;
+}
+extern "C" int vl_flash_decode_max_cluster() { return decode_max_cluster(); }
+
 // Most chunks per token that vl_flash_decode merges itself when they are too many for a cluster:
 // their weights, for 16 rows, have to fit the shared memory that held the keys.
 extern "C" int vl_flash_decode_own_merge_cap() {
@@ -663,7 +694,7 @@ extern "C" int vl_flash_decode(const void* q, int q_stride, const void* kcache, 
             per_sm = 1;
         resident = sms * per_sm;
     }
-    const int in_cluster = out != nullptr && S >= 2 && S <= DEC_MAX_CLUSTER && (long long)S * nkv * htiles * T <= resident;
+    const int in_cluster = out != nullptr && S >= 2 && S <= decode_max_cluster() && (long long)S * nkv * htiles * T <= resident;
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(S, nkv * htiles, T);
     cfg.blockDim = dim3(NTHREADS);

@@ -285,16 +285,39 @@ def decode_attention(qkv, out, k_cache, v_cache, block_table, req_index, positio
     return out
 
 
-def decode_chunk_for(num_tokens, num_kv_heads, max_context, target_blocks=256) -> int:
+_max_clusters = {}
+
+
+def flash_decode_max_cluster(head_dim) -> int:
+    """Most chunks of a token that `vl_flash_decode` merges as the blocks of one cluster: 16 where the device
+    takes clusters beyond the portable 8, else 8."""
+    v = _max_clusters.get(head_dim)
+    if v is None:
+        fn = build.load("flash_attn", {"FA_HD": head_dim}).vl_flash_decode_max_cluster
+        fn.restype = c_int
+        v = _max_clusters[head_dim] = int(fn())
+    return v
+
+
+def decode_chunk_for(num_tokens, num_kv_heads, max_context, target_blocks=256, head_dim=None) -> int:
     """Key positions per block of the split decode kernels: the largest of 256..1024 that still
     gives most of the 148 SMs two blocks (a block's start-up is paid once per chunk; measured at
     batch 8, context 4,096: 4.80 / 4.55 / 4.38 ms a step with chunks of 256 / 512 / 1,024)."""
+    ctx = int(max_context)
     for chunk in (1024, 512):
-        if num_tokens * num_kv_heads * -(-int(max_context) // chunk) >= target_blocks:
+        if num_tokens * num_kv_heads * -(-ctx // chunk) >= target_blocks:
             return chunk
-    # too few blocks either way: up to 8 chunks merge within a cluster (batch 1 at 4,096 keys: 10.8 us
-    # with 8 chunks of 512, 12.9 us with 16 of 256)
-    return 512 if -(-int(max_context) // 512) <= 8 else 256
+    # Too few blocks either way.  What bounds so few blocks is a warp's own pace (2,200 cycles for its 16
+    # keys of every 64), so the shortest chunks win whose blocks still merge as one cluster per token (8
+    # blocks, 16 where the device takes it) and have an SM each: one request at 4,096 keys, 16 chunks of 256
+    # against 8 of 512: 3.24 -> 3.08 ms a step; two requests (256 blocks, two to an SM): 3.26 -> 3.43, so not there
+    if head_dim is not None and flash_supported(torch.bfloat16, head_dim):
+        most = flash_decode_max_cluster(head_dim)
+        for chunk in (128, 256, 512, 1024):
+            chunks = -(-ctx // chunk)
+            if chunks <= most and num_tokens * num_kv_heads * chunks <= 2 * sm_pairs():
+                return chunk
+    return 512 if -(-ctx // 512) <= 8 else 256
 
 
 def flash_supported(dtype, head_dim) -> bool:

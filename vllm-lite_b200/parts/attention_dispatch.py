@@ -19,7 +19,7 @@ from .base import QUERY_TILE
 
 
 def _decode(ops, args, step, spec, group, num_tokens, max_context, token_index=None):
-    chunk = ops.decode_chunk_for(num_tokens, spec.num_kv_heads, max_context)
+    chunk = ops.decode_chunk_for(num_tokens, spec.num_kv_heads, max_context, head_dim=spec.head_dim)
     S, n_acc, n_ml = ops.decode_attention_scratch(num_tokens, spec.num_heads, spec.head_dim, max_context, chunk)
     part_acc = step.workspace.get(step.tag + "attn.part_acc", (n_acc,), torch.float32)
     part_ml = step.workspace.get(step.tag + "attn.part_ml", (n_ml,), torch.float32)
