@@ -349,7 +349,12 @@ __device__ __forceinline__ void decode_cluster_merge(const float* bO, const floa
 }
 }  // namespace
 
-extern "C" __global__ void __launch_bounds__(NTHREADS)
+// TR: the products are taken the other way round, S^T = K Q^T and O^T = V^T P^T: the 16 keys of a warp's tile are
+// the 16 rows of the tensor-core tile and the query heads of the KV head its 8 columns (for groups of up
+// to 8 heads; with heads as rows, 16 of them, a group of 4 wastes three quarters of every product): half the
+// products, half the accumulators and half the exponentials per key.
+template <bool TR>
+__global__ void __launch_bounds__(NTHREADS)
 flash_decode_kernel(const bf16* __restrict__ q, int q_stride,
                     const bf16* __restrict__ kcache, const bf16* __restrict__ vcache,
                     const int* __restrict__ block_table, int max_blocks,
@@ -442,93 +447,175 @@ flash_decode_kernel(const bf16* __restrict__ q, int q_stride,
         if (st0 + i <= st1) load_tile(st0 + i, i);
         cp_async_commit();
     }
-    float o[DTILES][4], m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};
+    float* sO = reinterpret_cast<float*>(ring);                  // [4][16][HD + 4]: the warps' outputs, once the ring is free
+    constexpr int OLD = HD + 4;
+    if constexpr (TR) {
+        // ---- keys as rows: lane (g, t) holds keys g and g + 8 of the tile and heads 2t, 2t + 1 ----
+        constexpr int MT = HD / 16;                              // tiles of 16 features of the output
+        float oT[MT][4], m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};
 #pragma unroll
-    for (int d = 0; d < DTILES; ++d) { o[d][0] = o[d][1] = o[d][2] = o[d][3] = 0.f; }
-    unsigned qf[KSTEPS][4];
-    cp_async_wait<DEC_NST - 1>();                                // this thread's share of the query rows has landed ...
-    __syncthreads();                                             // ... and so has everybody's
-#pragma unroll
-    for (int ks = 0; ks < KSTEPS; ++ks)
-        ldmatrix_x4(qf[ks], Qs + (size_t)((lane & 7) + 8 * ((lane >> 3) & 1)) * LDS + ks * 16 + 8 * (lane >> 4));
-
-    for (int st = st0; st <= st1; ++st) {
-        const int it = st - st0;
-        cp_async_wait<DEC_NST - 2>();
-        __syncwarp();                                            // the tile has landed for every lane; the tile before is read
-        if (st + DEC_NST - 1 <= st1) load_tile(st + DEC_NST - 1, (it + DEC_NST - 1) % DEC_NST);
-        cp_async_commit();
-        const bf16* Kt = wring + (size_t)(it % DEC_NST) * 2 * 16 * LDS;
-        const bf16* Vt = Kt + 16 * LDS;
-        const int kr0 = warp * 16;                               // this warp's 16 keys of every 64
-        float s[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
+        for (int d = 0; d < MT; ++d) { oT[d][0] = oT[d][1] = oT[d][2] = oT[d][3] = 0.f; }
+        unsigned qb[KSTEPS][2];                                  // Q^T as the 16 x 8 operand: features 2t.., 2t + 8.. of head g
+        cp_async_wait<DEC_NST - 1>();                            // this thread's share of the query rows has landed ...
+        __syncthreads();                                         // ... and so has everybody's
 #pragma unroll
         for (int ks = 0; ks < KSTEPS; ++ks) {
-            unsigned kb[4];
-            ldmatrix_x4(kb, Kt + (size_t)((lane & 7) + 8 * (lane >> 4)) * LDS + ks * 16 + 8 * ((lane >> 3) & 1));
-            mma16816(s[0], qf[ks], kb[0], kb[1]);
-            mma16816(s[1], qf[ks], kb[2], kb[3]);
+            qb[ks][0] = *reinterpret_cast<const unsigned*>(Qs + (size_t)g * LDS + ks * 16 + 2 * t);
+            qb[ks][1] = *reinterpret_cast<const unsigned*>(Qs + (size_t)g * LDS + ks * 16 + 2 * t + 8);
         }
-        float mx[2] = {-INFINITY, -INFINITY};
+        for (int st = st0; st <= st1; ++st) {
+            const int it = st - st0;
+            cp_async_wait<DEC_NST - 2>();
+            __syncwarp();                                        // the tile has landed for every lane; the tile before is read
+            if (st + DEC_NST - 1 <= st1) load_tile(st + DEC_NST - 1, (it + DEC_NST - 1) % DEC_NST);
+            cp_async_commit();
+            const bf16* Kt = wring + (size_t)(it % DEC_NST) * 2 * 16 * LDS;
+            const bf16* Vt = Kt + 16 * LDS;
+            float sT[4] = {0.f, 0.f, 0.f, 0.f};                  // (key g | g + 8) x (head 2t | 2t + 1)
 #pragma unroll
-        for (int n = 0; n < 2; ++n)
-#pragma unroll
-            for (int e = 0; e < 4; ++e) {
-                const int j = st * BN + kr0 + n * 8 + 2 * t + (e & 1);
-                const float v = (j >= c0 && j < c1) ? s[n][e] * scale_log2 : -INFINITY;
-                s[n][e] = v;
-                mx[e >> 1] = fmaxf(mx[e >> 1], v);
+            for (int ks = 0; ks < KSTEPS; ++ks) {
+                unsigned ka[4];
+                ldmatrix_x4(ka, Kt + (size_t)((lane & 7) + 8 * ((lane >> 3) & 1)) * LDS + ks * 16 + 8 * (lane >> 4));
+                mma16816(sT, ka, qb[ks][0], qb[ks][1]);
             }
-        float corr[2], base[2];
+            const int j0 = st * BN + warp * 16 + g;              // this lane's keys: j0 and j0 + 8
+            const bool in0 = j0 >= c0 && j0 < c1, in1 = j0 + 8 >= c0 && j0 + 8 < c1;
+            sT[0] = in0 ? sT[0] * scale_log2 : -INFINITY; sT[1] = in0 ? sT[1] * scale_log2 : -INFINITY;
+            sT[2] = in1 ? sT[2] * scale_log2 : -INFINITY; sT[3] = in1 ? sT[3] * scale_log2 : -INFINITY;
+            float mx[2] = {fmaxf(sT[0], sT[2]), fmaxf(sT[1], sT[3])}, corr[2], base[2];
+#pragma unroll
+            for (int r = 0; r < 2; ++r) {                        // over the 16 keys: the lanes of equal t
+                mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 4));
+                mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 8));
+                mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 16));
+                const float mn = fmaxf(m_run[r], mx[r]);
+                base[r] = (mn == -INFINITY) ? 0.f : mn;
+                corr[r] = exp2_mufu(m_run[r] - base[r]);
+                m_run[r] = mn;
+                l_run[r] *= corr[r];
+            }
+            const float p0 = exp2_mufu(sT[0] - base[0]), p1 = exp2_mufu(sT[1] - base[1]);
+            const float p2 = exp2_mufu(sT[2] - base[0]), p3 = exp2_mufu(sT[3] - base[1]);
+            l_run[0] += p0 + p2;
+            l_run[1] += p1 + p3;
+            // P^T as the 16 x 8 operand of the second product: keys 2t.., 2t + 8.. of head g = the transposes of
+            // the two 8 x 8 blocks (keys g | g + 8, heads 2t..) that this lane's probabilities are rows of
+            unsigned pb0, pb1;
+            asm volatile("movmatrix.sync.aligned.m8n8.trans.b16 %0, %1;" : "=r"(pb0) : "r"(pack_bf16(p0, p1)));
+            asm volatile("movmatrix.sync.aligned.m8n8.trans.b16 %0, %1;" : "=r"(pb1) : "r"(pack_bf16(p2, p3)));
+#pragma unroll
+            for (int d = 0; d < MT; ++d) {
+                unsigned va[4];                                  // V^T: features 16 d + (g | g + 8) x keys (2t.. | 2t + 8..)
+                ldmatrix_x4_trans(va, Vt + (size_t)((lane & 7) + 8 * (lane >> 4)) * LDS + d * 16 + 8 * ((lane >> 3) & 1));
+                oT[d][0] *= corr[0]; oT[d][1] *= corr[1]; oT[d][2] *= corr[0]; oT[d][3] *= corr[1];
+                mma16816(oT[d], va, pb0, pb1);
+            }
+        }
+        cp_async_wait<0>();
+        __syncthreads();                                         // the ring is free: it now carries the warps' outputs
 #pragma unroll
         for (int r = 0; r < 2; ++r) {
-            mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 1));
-            mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 2));
-            const float mn = fmaxf(m_run[r], mx[r]);
-            base[r] = (mn == -INFINITY) ? 0.f : mn;
-            corr[r] = exp2_mufu(m_run[r] - base[r]);
-            m_run[r] = mn;
-            l_run[r] *= corr[r];
-        }
-        unsigned pf[4];
-        {
-            const float p00 = exp2_mufu(s[0][0] - base[0]), p01 = exp2_mufu(s[0][1] - base[0]);
-            const float p02 = exp2_mufu(s[0][2] - base[1]), p03 = exp2_mufu(s[0][3] - base[1]);
-            const float p10 = exp2_mufu(s[1][0] - base[0]), p11 = exp2_mufu(s[1][1] - base[0]);
-            const float p12 = exp2_mufu(s[1][2] - base[1]), p13 = exp2_mufu(s[1][3] - base[1]);
-            l_run[0] += p00 + p01 + p10 + p11;
-            l_run[1] += p02 + p03 + p12 + p13;
-            pf[0] = pack_bf16(p00, p01); pf[1] = pack_bf16(p02, p03);
-            pf[2] = pack_bf16(p10, p11); pf[3] = pack_bf16(p12, p13);
+            l_run[r] += __shfl_xor_sync(0xffffffffu, l_run[r], 4);
+            l_run[r] += __shfl_xor_sync(0xffffffffu, l_run[r], 8);
+            l_run[r] += __shfl_xor_sync(0xffffffffu, l_run[r], 16);
         }
 #pragma unroll
-        for (int dp = 0; dp < DTILES / 2; ++dp) {
-            unsigned vb[4];
-            ldmatrix_x4_trans(vb, Vt + (size_t)((lane & 7) + 8 * ((lane >> 3) & 1)) * LDS + dp * 16 + 8 * (lane >> 4));
-            o[2 * dp][0] *= corr[0]; o[2 * dp][1] *= corr[0]; o[2 * dp][2] *= corr[1]; o[2 * dp][3] *= corr[1];
-            o[2 * dp + 1][0] *= corr[0]; o[2 * dp + 1][1] *= corr[0]; o[2 * dp + 1][2] *= corr[1]; o[2 * dp + 1][3] *= corr[1];
-            mma16816(o[2 * dp], pf, vb[0], vb[1]);
-            mma16816(o[2 * dp + 1], pf, vb[2], vb[3]);
+        for (int d = 0; d < MT; ++d) {
+            float* pa = sO + ((size_t)warp * DEC_ROWS + 2 * t) * OLD + d * 16 + g;
+            pa[0] = oT[d][0]; pa[OLD] = oT[d][1];
+            pa[8] = oT[d][2]; pa[OLD + 8] = oT[d][3];
         }
-    }
-    cp_async_wait<0>();
-    __syncthreads();                                             // the ring is free: it now carries the warps' outputs
+        if (g == 0) {
+            s_m[warp][2 * t] = m_run[0]; s_l[warp][2 * t] = l_run[0];
+            s_m[warp][2 * t + 1] = m_run[1]; s_l[warp][2 * t + 1] = l_run[1];
+        }
+    } else {
+        float o[DTILES][4], m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};
 #pragma unroll
-    for (int r = 0; r < 2; ++r) {
-        l_run[r] += __shfl_xor_sync(0xffffffffu, l_run[r], 1);
-        l_run[r] += __shfl_xor_sync(0xffffffffu, l_run[r], 2);
-    }
-    float* sO = reinterpret_cast<float*>(ring);                  // [4][16][HD + 4]
-    constexpr int OLD = HD + 4;
+        for (int d = 0; d < DTILES; ++d) { o[d][0] = o[d][1] = o[d][2] = o[d][3] = 0.f; }
+        unsigned qf[KSTEPS][4];
+        cp_async_wait<DEC_NST - 1>();                                // this thread's share of the query rows has landed ...
+        __syncthreads();                                             // ... and so has everybody's
 #pragma unroll
-    for (int d = 0; d < DTILES; ++d) {
-        float* pa = sO + ((size_t)warp * DEC_ROWS + g) * OLD + d * 8 + 2 * t;
-        pa[0] = o[d][0]; pa[1] = o[d][1];
-        pa[8 * OLD] = o[d][2]; pa[8 * OLD + 1] = o[d][3];
-    }
-    if (t == 0) {
-        s_m[warp][g] = m_run[0]; s_l[warp][g] = l_run[0];
-        s_m[warp][g + 8] = m_run[1]; s_l[warp][g + 8] = l_run[1];
+        for (int ks = 0; ks < KSTEPS; ++ks)
+            ldmatrix_x4(qf[ks], Qs + (size_t)((lane & 7) + 8 * ((lane >> 3) & 1)) * LDS + ks * 16 + 8 * (lane >> 4));
+
+        for (int st = st0; st <= st1; ++st) {
+            const int it = st - st0;
+            cp_async_wait<DEC_NST - 2>();
+            __syncwarp();                                            // the tile has landed for every lane; the tile before is read
+            if (st + DEC_NST - 1 <= st1) load_tile(st + DEC_NST - 1, (it + DEC_NST - 1) % DEC_NST);
+            cp_async_commit();
+            const bf16* Kt = wring + (size_t)(it % DEC_NST) * 2 * 16 * LDS;
+            const bf16* Vt = Kt + 16 * LDS;
+            const int kr0 = warp * 16;                               // this warp's 16 keys of every 64
+            float s[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
+#pragma unroll
+            for (int ks = 0; ks < KSTEPS; ++ks) {
+                unsigned kb[4];
+                ldmatrix_x4(kb, Kt + (size_t)((lane & 7) + 8 * (lane >> 4)) * LDS + ks * 16 + 8 * ((lane >> 3) & 1));
+                mma16816(s[0], qf[ks], kb[0], kb[1]);
+                mma16816(s[1], qf[ks], kb[2], kb[3]);
+            }
+            float mx[2] = {-INFINITY, -INFINITY};
+#pragma unroll
+            for (int n = 0; n < 2; ++n)
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    const int j = st * BN + kr0 + n * 8 + 2 * t + (e & 1);
+                    const float v = (j >= c0 && j < c1) ? s[n][e] * scale_log2 : -INFINITY;
+                    s[n][e] = v;
+                    mx[e >> 1] = fmaxf(mx[e >> 1], v);
+                }
+            float corr[2], base[2];
+#pragma unroll
+            for (int r = 0; r < 2; ++r) {
+                mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 1));
+                mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 2));
+                const float mn = fmaxf(m_run[r], mx[r]);
+                base[r] = (mn == -INFINITY) ? 0.f : mn;
+                corr[r] = exp2_mufu(m_run[r] - base[r]);
+                m_run[r] = mn;
+                l_run[r] *= corr[r];
+            }
+            unsigned pf[4];
+            {
+                const float p00 = exp2_mufu(s[0][0] - base[0]), p01 = exp2_mufu(s[0][1] - base[0]);
+                const float p02 = exp2_mufu(s[0][2] - base[1]), p03 = exp2_mufu(s[0][3] - base[1]);
+                const float p10 = exp2_mufu(s[1][0] - base[0]), p11 = exp2_mufu(s[1][1] - base[0]);
+                const float p12 = exp2_mufu(s[1][2] - base[1]), p13 = exp2_mufu(s[1][3] - base[1]);
+                l_run[0] += p00 + p01 + p10 + p11;
+                l_run[1] += p02 + p03 + p12 + p13;
+                pf[0] = pack_bf16(p00, p01); pf[1] = pack_bf16(p02, p03);
+                pf[2] = pack_bf16(p10, p11); pf[3] = pack_bf16(p12, p13);
+            }
+#pragma unroll
+            for (int dp = 0; dp < DTILES / 2; ++dp) {
+                unsigned vb[4];
+                ldmatrix_x4_trans(vb, Vt + (size_t)((lane & 7) + 8 * ((lane >> 3) & 1)) * LDS + dp * 16 + 8 * (lane >> 4));
+                o[2 * dp][0] *= corr[0]; o[2 * dp][1] *= corr[0]; o[2 * dp][2] *= corr[1]; o[2 * dp][3] *= corr[1];
+                o[2 * dp + 1][0] *= corr[0]; o[2 * dp + 1][1] *= corr[0]; o[2 * dp + 1][2] *= corr[1]; o[2 * dp + 1][3] *= corr[1];
+                mma16816(o[2 * dp], pf, vb[0], vb[1]);
+                mma16816(o[2 * dp + 1], pf, vb[2], vb[3]);
+            }
+        }
+        cp_async_wait<0>();
+        __syncthreads();                                             // the ring is free: it now carries the warps' outputs
+#pragma unroll
+        for (int r = 0; r < 2; ++r) {
+            l_run[r] += __shfl_xor_sync(0xffffffffu, l_run[r], 1);
+            l_run[r] += __shfl_xor_sync(0xffffffffu, l_run[r], 2);
+        }
+#pragma unroll
+        for (int d = 0; d < DTILES; ++d) {
+            float* pa = sO + ((size_t)warp * DEC_ROWS + g) * OLD + d * 8 + 2 * t;
+            pa[0] = o[d][0]; pa[1] = o[d][1];
+            pa[8 * OLD] = o[d][2]; pa[8 * OLD + 1] = o[d][3];
+        }
+        if (t == 0) {
+            s_m[warp][g] = m_run[0]; s_l[warp][g] = l_run[0];
+            s_m[warp][g + 8] = m_run[1]; s_l[warp][g + 8] = l_run[1];
+        }
     }
     __syncthreads();
     for (int idx = tid; idx < nvalid * HD; idx += NTHREADS) {
@@ -625,7 +712,8 @@ static int decode_max_cluster() {
     static int v = 0;
     if (!v) {
         v = 8;
-        if (cudaFuncSetAttribute(flash_decode_kernel, cudaFuncAttributeNonPortableClusterSizeAllowed, 1) == cudaSuccess) {
+        if (cudaFuncSetAttribute(flash_decode_kernel<false>, cudaFuncAttributeNonPortableClusterSizeAllowed, 1) == cudaSuccess &&
+            cudaFuncSetAttribute(flash_decode_kernel<true>, cudaFuncAttributeNonPortableClusterSizeAllowed, 1) == cudaSuccess) {
             const size_t ring = (size_t)DEC_NST * 2 * BN * LDS * sizeof(bf16);
             const size_t merge = (size_t)(4 * DEC_ROWS * (HD + 4) + DEC_ROWS * HD) * sizeof(float);
             const size_t smem = (size_t)DEC_ROWS * LDS * sizeof(bf16) + (ring > merge ? ring : merge);
@@ -639,8 +727,10 @@ static int decode_max_cluster() {
             cfg.attrs = attr;
             cfg.numAttrs = 1;
             int clusters = 0;
-            if (cudaFuncSetAttribute(flash_decode_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) == cudaSuccess &&
-                cudaOccupancyMaxActiveClusters(&clusters, flash_decode_kernel, &cfg) == cudaSuccess && clusters >= 8)
+            if (cudaFuncSetAttribute(flash_decode_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) == cudaSuccess &&
+                cudaFuncSetAttribute(flash_decode_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) == cudaSuccess &&
+                cudaOccupancyMaxActiveClusters(&clusters, flash_decode_kernel<false>, &cfg) == cudaSuccess && clusters >= 8 &&
+                cudaOccupancyMaxActiveClusters(&clusters, flash_decode_kernel<true>, &cfg) == cudaSuccess && clusters >= 8)
                 v = 16;
         }
         cudaGetLastError();                                      // a refusal above is an answer, not an error of the step
@@ -680,7 +770,8 @@ extern "C" int vl_flash_decode(const void* q, int q_stride, const void* kcache, 
     const size_t ring = (size_t)DEC_NST * 2 * BN * LDS * sizeof(bf16);
     const size_t merge = (size_t)(4 * DEC_ROWS * (HD + 4) + DEC_ROWS * HD) * sizeof(float);
     const size_t smem = (size_t)DEC_ROWS * LDS * sizeof(bf16) + (ring > merge ? ring : merge);
-    cudaError_t e = cudaFuncSetAttribute(flash_decode_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    cudaError_t e = cudaFuncSetAttribute(flash_decode_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e == cudaSuccess) e = cudaFuncSetAttribute(flash_decode_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return (int)e;
     // A cluster starts when all its blocks find room at once: good while the whole grid is resident at
     // the same time (measured at 8 requests of 4,096 keys: 33.4 -> 29.5 us), a loss when blocks queue for
@@ -690,7 +781,7 @@ extern "C" int vl_flash_decode(const void* q, int q_stride, const void* kcache, 
         int dev = 0, sms = 0, per_sm = 0;
         cudaGetDevice(&dev);
         if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms <= 0) sms = 148;
-        if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, flash_decode_kernel, NTHREADS, smem) != cudaSuccess || per_sm < 1)
+        if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, flash_decode_kernel<true>, NTHREADS, smem) != cudaSuccess || per_sm < 1)
             per_sm = 1;
         resident = sms * per_sm;
     }
@@ -714,7 +805,8 @@ extern "C" int vl_flash_decode(const void* q, int q_stride, const void* kcache, 
     }
     cfg.attrs = attr;
     cfg.numAttrs = na;
-    return (int)cudaLaunchKernelEx(&cfg, flash_decode_kernel, (const bf16*)q, q_stride, (const bf16*)kcache, (const bf16*)vcache,
+    // groups of up to 8 query heads: keys as the rows of the tensor-core tiles, heads as their 8 columns
+    return (int)cudaLaunchKernelEx(&cfg, grp <= 8 ? flash_decode_kernel<true> : flash_decode_kernel<false>, (const bf16*)q, q_stride, (const bf16*)kcache, (const bf16*)vcache,
                                    block_table, max_blocks, req_index, positions, nq, nkv, page_size, num_pages,
                                    scale * 1.4426950408889634f, window, chunk, S, part_acc, part_ml, err, token_index,
                                    (bf16*)out, arrivals, in_cluster);
