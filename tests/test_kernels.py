@@ -181,6 +181,37 @@ def test_gemm_small_m_with_fused_norms(M, H, K, N2, swiglu):
     assert float((out.double() - y).abs().max()) <= 2e-2 * float(y.abs().max()) + 1e-3
 
 
+def pair_width_cases():
+    plain = [(256, 512, 64), (2048, 4096, 4096), (300, 1000, 264), (1, 333, 96), (130, 128, 72), (513, 1100, 520)]
+    cases = [(M, N, K, False, dt) for M, N, K in plain for dt in (torch.bfloat16, torch.float32)]
+    return cases + [(300, 1024, 200, True, torch.bfloat16), (2048, 3200, 1024, True, torch.bfloat16)]   # the activation writes bfloat16
+
+
+@pytest.mark.parametrize("width", ["256", "512"])
+@pytest.mark.parametrize("M,N,K,swiglu,out_dtype", pair_width_cases())
+def test_gemm_bf16_pair_widths(M, N, K, swiglu, out_dtype, width, monkeypatch):
+    """The paired product with tiles of 256 x 256 (two accumulators) and of 256 x 512 (one accumulator of all 512
+    columns of tensor memory, two products per 16 columns of K): both widths forced in turn, ragged M, N and K,
+    several tiles per pair of SMs, the activation in the epilogue."""
+    monkeypatch.setenv("VLLM_LITE_B200_PAIR_WIDTH", width)
+    torch.manual_seed(M + N + K)
+    a = torch.randn(M, K, device=DEV).to(torch.bfloat16)
+    w = (torch.randn(N, K, device=DEV) * 0.05).to(torch.bfloat16)
+    out = torch.full((M, N // 2 if swiglu else N), float("nan"), device=DEV, dtype=out_dtype)
+    e = err_word()
+    ops().gemm_bf16_tc5_pair(a, w, out, e, swiglu=swiglu)
+    assert int(e.item()) == 0
+    ref = a.double() @ w.double().T
+    if swiglu:
+        ref = ref.view(M, N // 16, 2, 8)
+        ref = (torch.nn.functional.silu(ref[:, :, 0]) * ref[:, :, 1]).reshape(M, N // 2)
+    scale = float(ref.abs().max())
+    if out_dtype == torch.float32:
+        assert float((out.double() - ref).abs().max()) <= 1e-5 * scale * (K ** 0.5)
+    else:
+        assert float((out.double() - ref).abs().max()) <= 2 ** -7 * scale + 1e-6
+
+
 @pytest.mark.parametrize("kernel,M", [("small_m", 1), ("small_m", 8), ("small_m", 13), ("tc5", 128), ("tc5", 300), ("tc5", 2048),
                                       ("tc5_pair", 300), ("tc5_pair", 2048)])
 @pytest.mark.parametrize("I,K", [(160, 96), (12288, 4096), (24, 64)])

@@ -28,11 +28,23 @@
 using namespace tc5;
 
 namespace {
-constexpr int BM_CTA = 128, BM = 256, BN = 256, BN_CTA = 128, BK = 64, UMMA_K = 16;
-constexpr int STAGES = 6;
+constexpr int BM_CTA = 128, BM = 256, BK = 64, UMMA_K = 16;
+constexpr int BN_MMA = 256, BN_CTA = 128;    // one product: 256 columns of the tile, 128 rows of W from each block
 constexpr int NUM_THREADS = 192;
-constexpr unsigned A_BYTES = BM_CTA * BK * 2, W_BYTES = BN_CTA * BK * 2, STAGE_BYTES = A_BYTES + W_BYTES;
-constexpr unsigned TMEM_COLS = 2 * BN;
+constexpr unsigned A_BYTES = BM_CTA * BK * 2, W_BYTES = BN_CTA * BK * 2;
+constexpr unsigned TMEM_COLS = 512;
+
+// The tile's width.  256: two accumulators in TMEM, 6 stages of 32 KB; a stage feeds 512 cycles of the tensor
+// core with 32 KB, more than an SM takes in (about 52 bytes a cycle), so the tensor pipe is busy 74 to 83 % of
+// a tile's time.  512: one accumulator of all 512 columns, 4 stages of 48 KB (A once for two products per 16
+// columns of K): 48 KB per 1,024 cycles, the tensor pipe no longer waits, but the epilogue of a tile no
+// longer runs beside the products of the next.  The launcher picks by the rounds of tiles either needs.
+template <int BN> struct Shape {
+    static constexpr int HALVES = BN / BN_MMA;                                 // products per 16 columns of K
+    static constexpr int STAGES = BN == 256 ? 6 : 4;
+    static constexpr int ACCS = BN == 256 ? 2 : 1;                              // accumulators in TMEM
+    static constexpr unsigned STAGE_BYTES = A_BYTES + HALVES * W_BYTES;
+};
 
 __device__ __forceinline__ unsigned cluster_rank() {
     unsigned r;
@@ -78,6 +90,7 @@ __device__ __forceinline__ void commit_pair(unsigned long long* bar) {
                  ::"r"(smem_u32(bar)), "h"(mask) : "memory");
 }
 
+template <int BN>
 __device__ __forceinline__ void tile_corner(int tile, int tiles_m, int tiles_n, int& m0, int& n0) {
     constexpr int BAND = 8;                                  // pairs that run together share tiles of W in L2
     const int band = tile / (BAND * tiles_n), in_band = tile - band * BAND * tiles_n;
@@ -87,10 +100,12 @@ __device__ __forceinline__ void tile_corner(int tile, int tiles_m, int tiles_n, 
 }
 }  // namespace
 
-template <typename TO>
+template <typename TO, int BN>
 __global__ void __launch_bounds__(NUM_THREADS)
 gemm_tc5_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w,
                      TO* __restrict__ C, int M, int N, int K, int ldc, unsigned* err, int tiles_m, int tiles_n, int swiglu) {
+    constexpr int STAGES = Shape<BN>::STAGES, ACCS = Shape<BN>::ACCS, HALVES = Shape<BN>::HALVES;
+    constexpr unsigned STAGE_BYTES = Shape<BN>::STAGE_BYTES;
     extern __shared__ unsigned char pair_smem_raw[];
     unsigned char* smem = reinterpret_cast<unsigned char*>(((uintptr_t)pair_smem_raw + 1023) & ~(uintptr_t)1023);
     __shared__ __align__(8) unsigned long long full_bar[STAGES], empty_bar[STAGES], acc_full_bar[2], acc_empty_bar[2];
@@ -104,7 +119,7 @@ gemm_tc5_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_con
 
     if (threadIdx.x == 0) {
         for (int i = 0; i < STAGES; ++i) { mbar_init(&full_bar[i], 1); mbar_init(&empty_bar[i], 1); }
-        for (int i = 0; i < 2; ++i) { mbar_init(&acc_full_bar[i], 1); mbar_init(&acc_empty_bar[i], 2 * 128); }
+        for (int i = 0; i < ACCS; ++i) { mbar_init(&acc_full_bar[i], 1); mbar_init(&acc_empty_bar[i], 2 * 128); }
         mbar_fence_init();
         failed = 0;
     }
@@ -127,7 +142,7 @@ gemm_tc5_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_con
             bool ok = true;
             for (int tile = pair; tile < total_tiles && ok; tile += num_pairs) {
                 int m0, n0;
-                tile_corner(tile, tiles_m, tiles_n, m0, n0);
+                tile_corner<BN>(tile, tiles_m, tiles_n, m0, n0);
                 for (int kb = 0; kb < k_blocks; ++kb, ++it) {
                     const int s = it % STAGES;
                     if (it >= STAGES && !mbar_wait_bounded(&empty_bar[s], (unsigned)((it / STAGES - 1) & 1))) {
@@ -139,18 +154,20 @@ gemm_tc5_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_con
                     const unsigned bar = map_to_rank(smem_u32(&full_bar[s]), 0);
                     unsigned char* st = smem + (size_t)s * STAGE_BYTES;
                     tma_load_2d_pair(st, &map_a, kb * BK, m0 + (int)rank * BM_CTA, bar);
-                    tma_load_2d_pair(st + A_BYTES, &map_w, kb * BK, n0 + (int)rank * BN_CTA, bar);
+#pragma unroll
+                    for (int h = 0; h < HALVES; ++h)     // this block's 128 rows of W for each product of 256 columns
+                        tma_load_2d_pair(st + A_BYTES + h * W_BYTES, &map_w, kb * BK, n0 + h * BN_MMA + (int)rank * BN_CTA, bar);
                 }
             }
         }
     } else if (warp == 1) {
         if (lane == 0 && rank == 0) {                        // ---- MMA issuer of the pair ----
-            constexpr unsigned idesc = make_idesc(BM, BN);
+            constexpr unsigned idesc = make_idesc(BM, BN_MMA);
             int it = 0, local = 0;
             bool ok = true;
             for (int tile = pair; tile < total_tiles && ok; tile += num_pairs, ++local) {
-                const int acc = local & 1;
-                if (local >= 2 && !mbar_wait_bounded(&acc_empty_bar[acc], (unsigned)((local / 2 - 1) & 1))) {
+                const int acc = local % ACCS;
+                if (local >= ACCS && !mbar_wait_bounded(&acc_empty_bar[acc], (unsigned)((local / ACCS - 1) & 1))) {
                     atomicOr(&failed, 2);
                     break;
                 }
@@ -165,11 +182,15 @@ gemm_tc5_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_con
                     }
                     tc5_fence_after();
                     const unsigned char* st = smem + (size_t)s * STAGE_BYTES;
-                    const unsigned long long adesc = make_smem_desc(st), bdesc = make_smem_desc(st + A_BYTES);
+                    const unsigned long long adesc = make_smem_desc(st);
 #pragma unroll
-                    for (int k = 0; k < BK / UMMA_K; ++k)
-                        mma_pair(tmem_c, adesc + (unsigned long long)(k * 2), bdesc + (unsigned long long)(k * 2), idesc,
-                                 (kb > 0 || k > 0) ? 1u : 0u);
+                    for (int h = 0; h < HALVES; ++h) {
+                        const unsigned long long bdesc = make_smem_desc(st + A_BYTES + h * W_BYTES);
+#pragma unroll
+                        for (int k = 0; k < BK / UMMA_K; ++k)
+                            mma_pair(tmem_c + (unsigned)(h * BN_MMA), adesc + (unsigned long long)(k * 2),
+                                     bdesc + (unsigned long long)(k * 2), idesc, (kb > 0 || k > 0) ? 1u : 0u);
+                    }
                     commit_pair(&empty_bar[s]);              // both blocks' stages are free once these MMAs have read them
                 }
                 if (ok) commit_pair(&acc_full_bar[acc]);     // both halves of this accumulator are complete
@@ -180,14 +201,14 @@ gemm_tc5_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_con
         const unsigned freed = map_to_rank(smem_u32(&acc_empty_bar[0]), 0);
         int local = 0;
         for (int tile = pair; tile < total_tiles; tile += num_pairs, ++local) {
-            const int acc = local & 1;
-            if (!mbar_wait_bounded(&acc_full_bar[acc], (unsigned)((local / 2) & 1))) {
+            const int acc = local % ACCS;
+            if (!mbar_wait_bounded(&acc_full_bar[acc], (unsigned)((local / ACCS) & 1))) {
                 atomicOr(&failed, 8);
                 break;
             }
             tc5_fence_after();
             int m0, n0;
-            tile_corner(tile, tiles_m, tiles_n, m0, n0);
+            tile_corner<BN>(tile, tiles_m, tiles_n, m0, n0);
             const int row = m0 + (int)rank * BM_CTA + quarter * 32 + lane;
             for (int c0 = 0; c0 < BN; c0 += 32) {
                 unsigned v[32];
@@ -207,16 +228,18 @@ gemm_tc5_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_con
         atomicOr(err, VL_DEV_WAIT_EXPIRED | VL_DEV_IN_GEMM_TC5_PAIR | ((unsigned)failed << VL_DEV_ROLE_SHIFT));
 }
 
-template <typename TO>
+template <typename TO, int BN>
 static int launch_pair(const void* A, const void* W, TO* C, int M, int N, int K, int lda, int ldw, int ldc,
                        unsigned* err, int swiglu, cudaStream_t s) {
+    constexpr int STAGES = Shape<BN>::STAGES;
+    constexpr unsigned STAGE_BYTES = Shape<BN>::STAGE_BYTES;
     CUtensorMap map_a, map_w;
     int rc = tc5_make_map(&map_a, A, M, K, lda, BM_CTA);
     if (rc) return rc;
     rc = tc5_make_map(&map_w, W, N, K, ldw, BN_CTA);
     if (rc) return rc;
     const size_t smem = (size_t)STAGES * STAGE_BYTES + 1024;
-    auto kern = gemm_tc5_pair_kernel<TO>;
+    auto kern = gemm_tc5_pair_kernel<TO, BN>;
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return (int)e;
     const int tiles_m = (M + BM - 1) / BM, tiles_n = (N + BN - 1) / BN;
@@ -252,7 +275,31 @@ extern "C" int vl_gemm_bf16_tc5_pair(const void* A, const void* W, void* C, int 
     if (lda < K || ldw < K) return VL_ERR_ARGUMENT;
     if (((uintptr_t)A | (uintptr_t)W) & 15) return VL_ERR_UNSUPPORTED;
     cudaStream_t s = (cudaStream_t)stream;
-    if (out_dtype == VL_BF16) return launch_pair<bf16>(A, W, (bf16*)C, M, N, K, lda, ldw, ldc, err, swiglu, s);
-    if (out_dtype == VL_F32) return launch_pair<float>(A, W, (float*)C, M, N, K, lda, ldw, ldc, err, swiglu, s);
+    // Which width.  A tile of 512 columns costs about 1.8 tiles of 256 (measured: neither keeps the tensor pipe
+    // busier than about 80 %, what the shared memory of an SM moves bounds both) plus an epilogue that nothing
+    // hides, and loses more when a pair walks many tiles (4,096 x 24,576 x 4,096: 560 us against 624).  It wins
+    // where it saves a round of the pairs of SMs and the rounds are few: at 2,048 rows of Qwen3-8B o 53.9 ->
+    // 50.1 us and down 155.5 -> 142.0 (one round of 64 tiles instead of two of 128), at 4,096 rows down 341 ->
+    // 320; q/k/v and gate/up stay at 256 (80.2 against 100.5, 295.8 against 312.7).
+    static int pairs = 0;
+    if (!pairs) {
+        int dev = 0, sms = 0;
+        cudaGetDevice(&dev);
+        if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms <= 0) sms = 148;
+        pairs = sms / 2;
+    }
+    const long long kb = (K + BK - 1) / BK, tm = (M + BM - 1) / BM;
+    const long long r256 = (tm * ((N + 255) / 256) + pairs - 1) / pairs, r512 = (tm * ((N + 511) / 512) + pairs - 1) / pairs;
+    int wide = N > 256 && r512 <= 2 && r512 * (18 * kb + 60) < r256 * 10 * kb;
+    if (const char* v = getenv("VLLM_LITE_B200_PAIR_WIDTH")) {      // 256 or 512: for tests and measurements
+        const int w = atoi(v);
+        if (w == 256 || w == 512) wide = w == 512;
+    }
+    if (out_dtype == VL_BF16)
+        return wide ? launch_pair<bf16, 512>(A, W, (bf16*)C, M, N, K, lda, ldw, ldc, err, swiglu, s)
+                    : launch_pair<bf16, 256>(A, W, (bf16*)C, M, N, K, lda, ldw, ldc, err, swiglu, s);
+    if (out_dtype == VL_F32)
+        return wide ? launch_pair<float, 512>(A, W, (float*)C, M, N, K, lda, ldw, ldc, err, swiglu, s)
+                    : launch_pair<float, 256>(A, W, (float*)C, M, N, K, lda, ldw, ldc, err, swiglu, s);
     return VL_ERR_UNSUPPORTED;
 }
