@@ -94,9 +94,32 @@ sample_kernel(const float* __restrict__ logits, long long row_stride, int V,
 
     // ---- argmax of the cleaned row (also the fallback of a degenerate row) ----
     ArgBest best{-INFINITY, 0x7fffffff};
-    for (int i = tid; i < V; i += SMP_THREADS) {
+    // 16 bytes a load, four loads in flight (a row of 152 thousand logits: 20 -> measured below us); a thread
+    // sees its elements in rising order, so the first of equal values stays
+    const int V4 = (((uintptr_t)l & 15) == 0) ? (V & ~3) : 0;
+    for (int i0 = 4 * tid; i0 < V4; i0 += 16 * SMP_THREADS) {
+        float4 q[4];
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+            const int i = i0 + u * 4 * SMP_THREADS;
+            q[u] = i < V4 ? *reinterpret_cast<const float4*>(l + i) : make_float4(-INFINITY, -INFINITY, -INFINITY, -INFINITY);
+        }
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+            const int i = i0 + u * 4 * SMP_THREADS;
+            if (i < V4) {
+                const float e[4] = {q[u].x, q[u].y, q[u].z, q[u].w};
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    const float v = clean(e[j], 1.f);
+                    if (best.i == 0x7fffffff || v > best.v) best = ArgBest{v, i + j};
+                }
+            }
+        }
+    }
+    for (int i = V4 + tid; i < V; i += SMP_THREADS) {
         const float v = clean(l[i], 1.f);
-        if (best.i == 0x7fffffff || v > best.v) best = ArgBest{v, i};
+        best = better(best, ArgBest{v, i});
     }
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) {
