@@ -564,6 +564,53 @@ def test_decode_attention_merges_up_to_16_chunks_in_a_cluster(nq, nkv, hd, page)
     _decode_attention_split("flash_decode64own", torch.bfloat16, nq, nkv, hd, page, 400, lens, seqs, "in a row")
 
 
+@pytest.mark.parametrize("nq,nkv,hd,page,rot,norm,chunk,window,write", [
+    (32, 8, 128, 64, 128, True, 1024, 0, True), (8, 2, 128, 16, 128, True, 256, 0, True), (6, 3, 64, 16, 32, True, 64, 0, True),
+    (4, 1, 32, 8, 32, False, 64, 300, True), (40, 2, 32, 16, 0, True, 256, 0, True), (7, 1, 64, 16, 64, True, 512, 0, False),
+    (16, 2, 256, 32, 256, True, 256, 0, True), (5, 5, 16, 16, 16, True, 64, 0, True)])
+def test_decode_attention_with_the_norm_and_rotation_folded_in(nq, nkv, hd, page, rot, norm, chunk, window, write):
+    """A decode step two ways: the kernel that norms and rotates the heads and writes the cache, then the decode
+    attention; and the decode attention doing all of it on the way.  The same bits: the output rows, and the
+    key and value that the step leaves in the cache (requests of one token, of a page's last and first row,
+    of a chunk's edges, a padded place; groups of more than 8 and more than 16 heads; a call that writes no cache)."""
+    torch.manual_seed(nq * hd + page)
+    lens = [1, page, page + 1, 255, 256, 257, 700, 1030]
+    seqs = [(torch.randn(n, nkv, hd), torch.randn(n, nkv, hd)) for n in lens]
+    kc, vc, table = build_paged(seqs, nkv, hd, page, torch.bfloat16)
+    T = len(lens) + 1
+    req = torch.tensor(list(range(len(lens))) + [0], dtype=torch.int32, device=DEV)
+    pos = torch.tensor([n - 1 for n in lens] + [-1], dtype=torch.int32, device=DEV)
+    slots = torch.tensor([int(table[b, (n - 1) // page]) * page + (n - 1) % page for b, n in enumerate(lens)] + [-1],
+                         dtype=torch.int32, device=DEV)
+    raw = (torch.randn(T, (nq + 2 * nkv) * hd) * 1.5).to(DEV).to(torch.bfloat16)
+    qw = (1 + 0.1 * torch.randn(hd)).to(DEV) if norm else None
+    kw = (1 + 0.1 * torch.randn(hd)).to(DEV) if norm else None
+    inv_freq = (10000.0 ** (-torch.arange(0, rot, 2).float() / rot)).to(DEV) if rot else None
+    eps, scale, ctx = 1e-5, hd ** -0.5, max(lens)
+    S, n_acc, n_ml = ops().decode_attention_scratch(T, nq, hd, ctx, chunk)
+    results = []
+    for fold in (False, True):
+        k2, v2, qkv = kc.clone(), vc.clone(), raw.clone()
+        out = torch.full((T, nq * hd), 5.0, device=DEV, dtype=torch.bfloat16)
+        pa, pm = torch.full((n_acc,), float("nan"), device=DEV), torch.full((n_ml,), float("nan"), device=DEV)
+        arrivals = torch.zeros(ops().flash_decode_arrivals(T, nq, nkv), dtype=torch.int32, device=DEV)
+        e = err_word()
+        the_slots = slots if write else None
+        if not fold:
+            ops().qk_norm_rope_write(qkv, pos, the_slots, qw, kw, eps, inv_freq, rot, k2, v2, nq, nkv, hd, e)
+        ops().flash_decode(qkv, out, k2, v2, table, req, pos, nq, nkv, hd, scale, window, ctx, pa, pm, e, chunk=chunk,
+                           stream_kernel=False, arrivals=arrivals,
+                           fold=(qw, kw, eps, inv_freq, rot, the_slots) if fold else None)
+        assert int(e.item()) == 0 and int(arrivals.abs().sum()) == 0
+        results.append((out, k2, v2))
+    (o0, k0, v0), (o1, k1, v1) = results
+    same = lambda a, b: torch.equal(a.view(torch.int16), b.view(torch.int16))        # bit for bit, NaN fill included
+    assert same(k0, k1) and same(v0, v1) and same(o0, o1)
+    if not write:                               # the cache is as it was: the token's key is what another call left there
+        assert same(k1, kc) and same(v1, vc)
+    assert bool((o1[T - 1] == 0).all())
+
+
 @pytest.mark.parametrize("kernel,dtype", attention_cases())
 @pytest.mark.parametrize("far,window", [(3, 0), (640, 0), (15, 0), (16, 0), (63, 0), (64, 0), (255, 0), (256, 0),
                                         (700, 300), (699, 300)])

@@ -17,7 +17,7 @@
 //   layout as vl_decode_attention's and are merged by vl_decode_attention_merge.
 // Rows of shared-memory tiles are padded by 16 bytes, which makes every 8-row ldmatrix access
 // hit 8 different banks groups for any head size.
-#include "common.cuh"
+#include "rope_head.cuh"
 
 #ifndef FA_HD
 #define FA_HD 128
@@ -349,6 +349,21 @@ __device__ __forceinline__ void decode_cluster_merge(const float* bO, const floa
 }
 }  // namespace
 
+// What the decode kernel does on the way when the step's head norm, rotation and cache write are folded into it
+// (on != 0): q, the new token's k and its v are then still as the projection left them.  A block norms and
+// rotates its own query heads while it brings them into shared memory; the block whose chunk holds the token's
+// own position does the same for the token's key, copies its value, writes both to their slot of the cache
+// (slots == null: a call that reads another call's cache writes nothing) and lays them over the row of the
+// tile that its copy of the cache brought, which may not hold them yet.  The arithmetic is HeadRegs
+// (csrc/rope_head.cuh), as in the kernel that serves whole steps: the same bits.
+struct DecodeFusion {
+    const float* qw; const float* kw; float eps;         // head norm weights (null: none)
+    const float* inv_freq; int rot;                      // rotary frequencies (null: none), rotated features
+    const int* slots; long long num_slots;               // cache slot of every token of the step
+    bf16* kcache; bf16* vcache;                          // the cache again, to write
+    int on;
+};
+
 // TR: the products are taken the other way round, S^T = K Q^T and O^T = V^T P^T: the 16 keys of a warp's tile are
 // the 16 rows of the tensor-core tile and the query heads of the KV head its 8 columns (for groups of up
 // to 8 heads; with heads as rows, 16 of them, a group of 4 wastes three quarters of every product): half the
@@ -356,16 +371,19 @@ __device__ __forceinline__ void decode_cluster_merge(const float* bO, const floa
 template <bool TR>
 __global__ void __launch_bounds__(NTHREADS)
 flash_decode_kernel(const bf16* __restrict__ q, int q_stride,
-                    const bf16* __restrict__ kcache, const bf16* __restrict__ vcache,
+                    const bf16* kcache, const bf16* vcache,
                     const int* __restrict__ block_table, int max_blocks,
                     const int* __restrict__ req_index, const int* __restrict__ positions,
                     int nq, int nkv, int page_size, int num_pages, float scale_log2, int window,
                     int chunk, int S, float* __restrict__ part_acc, float* __restrict__ part_ml, unsigned* err,
                     const int* __restrict__ token_index, bf16* __restrict__ out, int* __restrict__ arrivals,
-                    int in_cluster) {
+                    int in_cluster, DecodeFusion fz) {
     extern __shared__ __align__(128) unsigned char fa_smem[];
     bf16* Qs = reinterpret_cast<bf16*>(fa_smem);                 // [16][LDS]
     bf16* ring = Qs + DEC_ROWS * LDS;                            // [NST][2][BN][LDS]
+    constexpr int RMAX = HD <= 128 ? 128 : 256;                  // HeadRegs is built for head sizes up to this
+    __shared__ float s_cos[RMAX / 2], s_sin[RMAX / 2];           // (fz.on) the token's rotation
+    __shared__ __align__(16) bf16 s_new[2][HD];                  // (fz.on) the token's own key and value, finished
     __shared__ float s_m[4][DEC_ROWS], s_l[4][DEC_ROWS];
     __shared__ float s_bm[DEC_ROWS], s_bl[DEC_ROWS];             // (in_cluster) the block's maxima and sums
     float* bO = reinterpret_cast<float*>(ring) + 4 * DEC_ROWS * (HD + 4);    // ... and its output sums [rows][HD]
@@ -414,15 +432,24 @@ flash_decode_kernel(const bf16* __restrict__ q, int q_stride,
 
     for (int i = tid; i < (st1 - st0 + 1) * BN; i += NTHREADS)
         s_rows[i] = cache_row(table, max_blocks, st0 * BN + i, c0, pos, kvh, nkv, page_size, num_pages, err);
+    // (c0 <= pos always) this chunk holds the token's own position, and this call owns the cache (a call that
+    // reads another call's cache finds the token's key there: the owner ran before it)
+    const bool has_new = fz.on && fz.slots && pos < c1;
+    if (fz.on && fz.inv_freq)                                    // positions are part of the step's description: no wait needed
+        for (int i = tid; i < fz.rot / 2; i += NTHREADS) sincosf((float)pos * fz.inv_freq[i], &s_sin[i], &s_cos[i]);
     pdl_wait();
-    for (int idx = tid; idx < DEC_ROWS * CPR; idx += NTHREADS) {
-        const int r = idx / CPR, c = idx - r * CPR;
-        const bool valid = r < nvalid;
-        const bf16* src = valid ? q + (size_t)tok * q_stride + (size_t)(h0 + r) * HD + c * 8 : q;
-        cp_async16(Qs + (size_t)r * LDS + c * 8, src, valid);
+    if (!fz.on) {
+        for (int idx = tid; idx < DEC_ROWS * CPR; idx += NTHREADS) {
+            const int r = idx / CPR, c = idx - r * CPR;
+            const bool valid = r < nvalid;
+            const bf16* src = valid ? q + (size_t)tok * q_stride + (size_t)(h0 + r) * HD + c * 8 : q;
+            cp_async16(Qs + (size_t)r * LDS + c * 8, src, valid);
+        }
     }
     cp_async_commit();                                           // the query rows: this thread's oldest group
-    __syncthreads();                                             // s_rows
+    __syncthreads();                                             // s_rows, the rotation's table
+    // the tile and the row in it that the token's own key and value are laid over once its copy has landed
+    const int new_st = pos / BN, new_warp = (pos % BN) / 16, new_row = pos % 16;
     // Every warp runs a pipeline of its own: of each 64 keys it takes 16 (warp w the keys 16 w .. 16 w + 15),
     // copies their K and V rows itself into a ring of DEC_NST tiles that belongs to it, and waits for
     // nobody but its own copies.  No barrier of the block stands in the loop, and of a warp's ring all
@@ -442,10 +469,58 @@ flash_decode_kernel(const bf16* __restrict__ q, int q_stride,
             cp_async16(kt + (size_t)(16 + r) * LDS + c * 8, vcache + off, row >= 0);
         }
     };
+    auto lay_new_over = [&](int st, int buf) {                   // (after the tile's copies have landed)
+        if (has_new && st == new_st && warp == new_warp) {
+            bf16* kt = wring + (size_t)buf * 2 * 16 * LDS;
+            for (int c = lane; c < 2 * CPR; c += 32) {
+                const int which = c / CPR, cc = c - which * CPR;
+                *reinterpret_cast<uint4*>(kt + (size_t)(which * 16 + new_row) * LDS + cc * 8) =
+                    *reinterpret_cast<const uint4*>(s_new[which] + cc * 8);
+            }
+            __syncwarp();
+        }
+    };
 #pragma unroll
     for (int i = 0; i < DEC_NST - 1; ++i) {
         if (st0 + i <= st1) load_tile(st0 + i, i);
         cp_async_commit();
+    }
+    if (fz.on) {                                                 // the head work, while the first tiles are on their way
+        for (int idx = tid; idx < (DEC_ROWS - nvalid) * CPR; idx += NTHREADS)     // rows that no head uses are zero
+            *reinterpret_cast<uint4*>(Qs + (size_t)(nvalid + idx / CPR) * LDS + (idx % CPR) * 8) = make_uint4(0u, 0u, 0u, 0u);
+        const bf16* row = q + (size_t)tok * q_stride;
+        // a warp per head; with the token's own key and value (warps 0 and 1 first) one pass more at most
+        for (int r = warp - (has_new ? 2 : 0); r < nvalid; r += 4) {
+            HeadRegs<bf16, RMAX> hr;
+            hr.live = true;
+            if (r >= 0) {
+                hr.src = row + (size_t)(h0 + r) * HD; hr.out = Qs + (size_t)r * LDS;
+                hr.w = fz.qw; hr.rot = fz.inv_freq ? fz.rot : 0;
+            } else if (r == -2) {
+                hr.src = row + (size_t)(nq + kvh) * HD; hr.out = s_new[0];
+                hr.w = fz.kw; hr.rot = fz.inv_freq ? fz.rot : 0;
+            } else {
+                hr.src = row + (size_t)(nq + nkv + kvh) * HD; hr.out = s_new[1];
+                hr.w = nullptr; hr.rot = 0;
+            }
+            hr.load(lane, HD);
+            hr.finish(lane, HD, fz.eps, s_cos, s_sin);
+        }
+        if (has_new && htile == 0) {                             // (uniform) one block per token and KV head writes the cache
+            __syncthreads();
+            const int slot = fz.slots[tok];
+            if (slot >= 0 && (long long)slot < fz.num_slots) {
+                const int page = slot / page_size, off = slot - page * page_size;
+                const size_t at = (((size_t)page * nkv + kvh) * page_size + off) * HD;
+                for (int c = tid; c < 2 * CPR; c += NTHREADS) {
+                    const int which = c / CPR, cc = c - which * CPR;
+                    *reinterpret_cast<uint4*>((which ? fz.vcache : fz.kcache) + at + cc * 8) =
+                        *reinterpret_cast<const uint4*>(s_new[which] + cc * 8);
+                }
+            } else if (slot >= 0 && tid == 0 && err) {
+                atomicOr(err, VL_DEV_BAD_SLOT);
+            }
+        }
     }
     float* sO = reinterpret_cast<float*>(ring);                  // [4][16][HD + 4]: the warps' outputs, once the ring is free
     constexpr int OLD = HD + 4;
@@ -467,6 +542,7 @@ flash_decode_kernel(const bf16* __restrict__ q, int q_stride,
             const int it = st - st0;
             cp_async_wait<DEC_NST - 2>();
             __syncwarp();                                        // the tile has landed for every lane; the tile before is read
+            lay_new_over(st, it % DEC_NST);
             if (st + DEC_NST - 1 <= st1) load_tile(st + DEC_NST - 1, (it + DEC_NST - 1) % DEC_NST);
             cp_async_commit();
             const bf16* Kt = wring + (size_t)(it % DEC_NST) * 2 * 16 * LDS;
@@ -544,6 +620,7 @@ flash_decode_kernel(const bf16* __restrict__ q, int q_stride,
             const int it = st - st0;
             cp_async_wait<DEC_NST - 2>();
             __syncwarp();                                            // the tile has landed for every lane; the tile before is read
+            lay_new_over(st, it % DEC_NST);
             if (st + DEC_NST - 1 <= st1) load_tile(st + DEC_NST - 1, (it + DEC_NST - 1) % DEC_NST);
             cp_async_commit();
             const bf16* Kt = wring + (size_t)(it % DEC_NST) * 2 * 16 * LDS;
@@ -754,11 +831,11 @@ extern "C" int vl_flash_decode_own_merge_cap() {
 // kernel merges the chunks itself: up to 8 chunks as the blocks of a cluster, through their shared
 // memory; more through the scratch, by the block that arrives last.  With both null, follow with
 // vl_decode_attention_merge.
-extern "C" int vl_flash_decode(const void* q, int q_stride, const void* kcache, const void* vcache,
+static int launch_flash_decode(const void* q, int q_stride, const void* kcache, const void* vcache,
                                const int* block_table, int max_blocks, const int* req_index, const int* positions,
                                int T, int nq, int nkv, int hd, int page_size, int num_pages, float scale, int window,
                                int chunk, int S, float* part_acc, float* part_ml, unsigned* err,
-                               const int* token_index, void* out, int* arrivals, void* stream) {
+                               const int* token_index, void* out, int* arrivals, DecodeFusion fz, void* stream) {
     if (T <= 0) return VL_OK;
     if (hd != HD) return VL_ERR_UNSUPPORTED;
     if (nq <= 0 || nkv <= 0 || nq % nkv || page_size <= 0 || max_blocks <= 0 || q_stride % 8) return VL_ERR_ARGUMENT;
@@ -809,5 +886,38 @@ extern "C" int vl_flash_decode(const void* q, int q_stride, const void* kcache, 
     return (int)cudaLaunchKernelEx(&cfg, grp <= 8 ? flash_decode_kernel<true> : flash_decode_kernel<false>, (const bf16*)q, q_stride, (const bf16*)kcache, (const bf16*)vcache,
                                    block_table, max_blocks, req_index, positions, nq, nkv, page_size, num_pages,
                                    scale * 1.4426950408889634f, window, chunk, S, part_acc, part_ml, err, token_index,
-                                   (bf16*)out, arrivals, in_cluster);
+                                   (bf16*)out, arrivals, in_cluster, fz);
+}
+
+extern "C" int vl_flash_decode(const void* q, int q_stride, const void* kcache, const void* vcache,
+                               const int* block_table, int max_blocks, const int* req_index, const int* positions,
+                               int T, int nq, int nkv, int hd, int page_size, int num_pages, float scale, int window,
+                               int chunk, int S, float* part_acc, float* part_ml, unsigned* err,
+                               const int* token_index, void* out, int* arrivals, void* stream) {
+    DecodeFusion fz = {};
+    return launch_flash_decode(q, q_stride, kcache, vcache, block_table, max_blocks, req_index, positions, T, nq, nkv, hd,
+                               page_size, num_pages, scale, window, chunk, S, part_acc, part_ml, err, token_index, out,
+                               arrivals, fz, stream);
+}
+
+// The same with the step's head norm, rotation and cache write folded in (DecodeFusion): q [T, q_stride] holds
+// the rows q | k | v as the projection left them, qw / kw are the norm weights of a q and a k head (both null:
+// no norm), inv_freq [rot / 2] the rotary frequencies (null: no rotation), slots [tokens of the step] each
+// token's place in the cache, page * page_size + offset (null: this call writes no cache: it reads another
+// call's).  Every token of the launch must be the LAST position of its request (pos = the position the slot
+// stands for), which is what a decode step is.
+extern "C" int vl_flash_decode_fused(const void* q, int q_stride, void* kcache, void* vcache,
+                                     const int* block_table, int max_blocks, const int* req_index, const int* positions,
+                                     int T, int nq, int nkv, int hd, int page_size, int num_pages, float scale, int window,
+                                     int chunk, int S, float* part_acc, float* part_ml, unsigned* err,
+                                     const int* token_index, void* out, int* arrivals,
+                                     const float* qw, const float* kw, float eps, const float* inv_freq, int rot,
+                                     const int* slots, void* stream) {
+    if ((qw == nullptr) != (kw == nullptr) || rot < 0 || rot > hd || (rot & 1)) return VL_ERR_ARGUMENT;
+    if (q_stride < (nq + 2 * nkv) * hd) return VL_ERR_ARGUMENT;
+    DecodeFusion fz = {qw, kw, eps, inv_freq, inv_freq ? rot : 0, slots, (long long)num_pages * page_size,
+                       (bf16*)kcache, (bf16*)vcache, 1};
+    return launch_flash_decode(q, q_stride, kcache, vcache, block_table, max_blocks, req_index, positions, T, nq, nkv, hd,
+                               page_size, num_pages, scale, window, chunk, S, part_acc, part_ml, err, token_index, out,
+                               arrivals, fz, stream);
 }

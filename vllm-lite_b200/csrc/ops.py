@@ -54,6 +54,10 @@ _SIGNATURES = {
     ("flash_attn", "vl_flash_decode"): [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p,
                                         c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_int, c_int,
                                         c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p],
+    ("flash_attn", "vl_flash_decode_fused"): [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p,
+                                              c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_int, c_int,
+                                              c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+                                              c_void_p, c_void_p, c_float, c_void_p, c_int, c_void_p, c_void_p],
     ("flash_decode_tma", "vl_flash_decode_tma"): [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p,
                                                   c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_int, c_int,
                                                   c_void_p, c_void_p, c_void_p, c_void_p, c_void_p],
@@ -396,9 +400,19 @@ def flash_decode_arrivals(num_tokens, num_heads, num_kv_heads) -> int:
 STREAM_DECODE_MIN_KEYS = 8 * 49152      # tokens x KV heads x context bound from which the persistent TMA kernel is used
 
 
+def flash_decode_streams(dtype, num_tokens, num_kv_heads, head_dim, page_size, max_context) -> bool:
+    """Whether `flash_decode` left to itself serves such a step with the persistent TMA kernel (else a block per chunk).
+    Measured (Qwen3-8B heads, pages of 64): it wins from 64-position pages on (TMA boxes of 8 KB, not 2 KB) when
+    the step streams enough keys to keep every SM's block busy: 16 tokens x 4,096 keys 55.8 us against 60.0 for a
+    block per chunk, 64 x 4,096: 170 against 188, 8 x 16,384: 96 against 108; at 8 x 4,096 and below the block per
+    chunk, which merges in the same launch, is level or ahead."""
+    return (flash_tc5_supported(dtype, head_dim, page_size) and page_size >= 64
+            and num_tokens * num_kv_heads * int(max_context) >= STREAM_DECODE_MIN_KEYS)
+
+
 def flash_decode(qkv, out, k_cache, v_cache, block_table, req_index, positions, num_heads, num_kv_heads,
                  head_dim, scale, window, max_context, part_acc, part_ml, err, chunk=DECODE_CHUNK, token_index=None,
-                 stream_kernel=None, arrivals=None):
+                 stream_kernel=None, arrivals=None, fold=None):
     """Tensor-core version of `decode_attention` (bfloat16): every block takes a chunk of a token's
     keys; the chunks are merged by the block that finishes last (`arrivals`: int32 counters,
     `flash_decode_arrivals` of them, zero before the first call and left zero) or, without
@@ -407,7 +421,11 @@ def flash_decode(qkv, out, k_cache, v_cache, block_table, req_index, positions, 
     least 64 positions and the step reads STREAM_DECODE_MIN_KEYS keys or more (`stream_kernel`: None =
     that rule, True / False to force; it always merges with the second kernel), else a block per chunk.
     `token_index` (int32) restricts the launch to some tokens of the step (the others' rows of `out`
-    are left alone); the scratch is then sized for that many tokens."""
+    are left alone); the scratch is then sized for that many tokens.
+    `fold` = (q_weight, k_weight, eps, inv_freq, rotary_dim, slots) folds the step's `qk_norm_rope_write`
+    into the block-per-chunk kernel (the TMA kernel does not take it): qkv then holds the rows as the
+    projection left them, every token is the last of its request, and the token's key and value are
+    written to the cache by this launch (slots None: not written).  The same bits as the two kernels in turn."""
     _flash_checks(qkv, k_cache, v_cache, block_table, num_heads, num_kv_heads, head_dim)
     _need(out, torch.bfloat16, "out", 2)
     _need(req_index, torch.int32, "req_index", 1); _need(positions, torch.int32, "positions", 1)
@@ -422,12 +440,9 @@ def flash_decode(qkv, out, k_cache, v_cache, block_table, req_index, positions, 
     if part_acc.numel() < need_acc or part_ml.numel() < need_ml:
         raise KernelError(f"flash_decode: scratch too small ({part_acc.numel()} < {need_acc})")
     if stream_kernel is None:
-        # measured (Qwen3-8B heads, pages of 64): it wins from 64-position pages on (TMA boxes of 8 KB, not 2 KB)
-        # when the step streams enough keys to keep every SM's block busy: 16 tokens x 4,096 keys 55.8 us
-        # against 60.0 for a block per chunk, 64 x 4,096: 170 against 188, 8 x 16,384: 96 against 108; at
-        # 8 x 4,096 and below the block per chunk, which merges in the same launch, is level or ahead
-        stream_kernel = (flash_tc5_supported(qkv.dtype, head_dim, k_cache.shape[2]) and k_cache.shape[2] >= 64
-                         and T * num_kv_heads * int(max_context) >= STREAM_DECODE_MIN_KEYS)
+        stream_kernel = fold is None and flash_decode_streams(qkv.dtype, T, num_kv_heads, head_dim, k_cache.shape[2], max_context)
+    if fold is not None and (stream_kernel or token_index is not None):
+        raise KernelError("flash_decode: the folded norm and rotation go with the block-per-chunk kernel and whole steps")
     args = (_ptr(qkv), qkv.shape[1], _ptr(k_cache), _ptr(v_cache), _ptr(block_table), block_table.shape[1],
             _ptr(req_index), _ptr(positions), T, num_heads, num_kv_heads, head_dim, k_cache.shape[2], k_cache.shape[0],
             float(scale), int(window or 0), chunk, S, _ptr(part_acc), _ptr(part_ml), _ptr(err), _ptr(token_index))
@@ -440,8 +455,28 @@ def flash_decode(qkv, out, k_cache, v_cache, block_table, req_index, positions, 
             _need(arrivals, torch.int32, "arrivals", 1)
             if arrivals.numel() < flash_decode_arrivals(T, num_heads, num_kv_heads):
                 raise KernelError("flash_decode: too few arrival counters")
-        _check(_fn("flash_attn", "vl_flash_decode", {"FA_HD": head_dim})(
-            *args, _ptr(out) if arrivals is not None else None, _ptr(arrivals), _stream()), "vl_flash_decode")
+        if fold is None:
+            _check(_fn("flash_attn", "vl_flash_decode", {"FA_HD": head_dim})(
+                *args, _ptr(out) if arrivals is not None else None, _ptr(arrivals), _stream()), "vl_flash_decode")
+        else:
+            qw, kw, eps, inv_freq, rot, slots = fold
+            for t, n in ((qw, "q_weight"), (kw, "k_weight"), (inv_freq, "inv_freq")):
+                if t is not None:
+                    _need(t, torch.float32, n, 1)
+            if (qw is None) != (kw is None) or (qw is not None and (qw.shape[0] != head_dim or kw.shape[0] != head_dim)):
+                raise KernelError("flash_decode: the head norm's weights do not match the head size")
+            if inv_freq is not None and inv_freq.shape[0] * 2 != rot:
+                raise KernelError("flash_decode: inv_freq does not match the rotary dimension")
+            if slots is not None:
+                _need(slots, torch.int32, "slots", 1)
+                if slots.shape[0] < T:
+                    raise KernelError("flash_decode: fewer slots than tokens")
+            if qkv.shape[1] < (num_heads + 2 * num_kv_heads) * head_dim:
+                raise KernelError("flash_decode: the rows do not hold q, k and v")
+            _check(_fn("flash_attn", "vl_flash_decode_fused", {"FA_HD": head_dim})(
+                *args, _ptr(out) if arrivals is not None else None, _ptr(arrivals),
+                _ptr(qw), _ptr(kw), float(eps), _ptr(inv_freq), int(rot if inv_freq is not None else 0), _ptr(slots),
+                _stream()), "vl_flash_decode_fused")
         if arrivals is not None:
             return out
     _check(_fn("attention", "vl_decode_attention_merge")(

@@ -113,12 +113,16 @@ class GqaAttention:
             self.q_norm.apply_heads(qkv, 0, s.num_heads, s.head_dim, step)
             self.k_norm.apply_heads(qkv, s.num_heads, s.num_kv_heads, s.head_dim, step)
         qw, kw, eps = self.fused_head_norm if self.fused_head_norm is not None else (None, None, 0.0)
-        ops.qk_norm_rope_write(
-            qkv, step.positions, group.slots if cache.writes else None, qw, kw, eps,
-            inv_freq, rot, cache.k, cache.v, s.num_heads, s.num_kv_heads, s.head_dim, step.err)
-        out = step.workspace.get(step.tag + "attn.out", (qkv.shape[0], s.num_heads * s.head_dim), self.dtype)
+        slots = group.slots if cache.writes else None
         from . import attention_dispatch
-        attention_dispatch.run(qkv, out, cache, group, step, s, self.scale)
+        fold = None
+        if attention_dispatch.folds_head_work(qkv.dtype, step, s, group, qkv.shape[0]):
+            fold = (qw, kw, eps, inv_freq, rot, slots)          # the attention kernel does it on the way
+        else:
+            ops.qk_norm_rope_write(qkv, step.positions, slots, qw, kw, eps, inv_freq, rot, cache.k, cache.v,
+                                   s.num_heads, s.num_kv_heads, s.head_dim, step.err)
+        out = step.workspace.get(step.tag + "attn.out", (qkv.shape[0], s.num_heads * s.head_dim), self.dtype)
+        attention_dispatch.run(qkv, out, cache, group, step, s, self.scale, fold=fold)
         if sink is not None:
             return self.o_proj.into_stream(out, sink, step, "attn.o")
         return self.o_proj(out, step, "attn.o")
