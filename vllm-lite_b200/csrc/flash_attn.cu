@@ -378,8 +378,8 @@ flash_decode_kernel(const bf16* __restrict__ q, int q_stride,
                     int chunk, int S, float* __restrict__ part_acc, float* __restrict__ part_ml, unsigned* err,
                     const int* __restrict__ token_index, bf16* __restrict__ out, int* __restrict__ arrivals,
                     int in_cluster, DecodeFusion fz) {
-    extern __shared__ __align__(128) unsigned char fa_smem[];
-    bf16* Qs = reinterpret_cast<bf16*>(fa_smem);                 // [16][LDS]
+    extern __shared__ __align__(128) unsigned char fa_dec_smem[];
+    bf16* Qs = reinterpret_cast<bf16*>(fa_dec_smem);             // [16][LDS]
     bf16* ring = Qs + DEC_ROWS * LDS;                            // [NST][2][BN][LDS]
     constexpr int RMAX = HD <= 128 ? 128 : 256;                  // HeadRegs is built for head sizes up to this
     __shared__ float s_cos[RMAX / 2], s_sin[RMAX / 2];           // (fz.on) the token's rotation
