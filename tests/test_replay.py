@@ -268,8 +268,8 @@ def test_real_layer_sizes_against_the_plain_implementation(dtype):
 @pytest.mark.parametrize("which,dtype", [(w, d) for w in ("B", "C") for d in ("float32", "bfloat16")])
 def test_many_requests_decode_in_one_step(which, dtype, live):
     """Decode steps of more than 8 requests: the batch is padded to 16, 64 or 128 places and replayed
-    from a graph, the bfloat16 products of that many rows run in the library, and the decode attention
-    picks other chunk sizes.  The requests' prompts are of unequal length and arrive several to a step,
+    from a graph, the bfloat16 products of 16 rows run in the weight-streaming kernel with its second row
+    tile, those of 64 and 128 rows in the library, and the decode attention picks other chunk sizes.  The requests' prompts are of unequal length and arrive several to a step,
     on pages that earlier requests held; then every request decodes, all in one step, six times."""
     ps = H.TINY[which]["page_size"]
     lens = [3 + (7 * i) % 41 for i in range(live)]
