@@ -355,3 +355,29 @@ def test_decoding_across_the_context_bounds_of_the_graphs(dtype, ahead):
     assert runner.step_ahead(["r", "s"], torch.zeros(2, dtype=torch.int32, device="cuda:0"), before) is None
     assert runner.cached_tokens("r") == before
     runner.cache.check_invariants()
+
+
+def test_decode_steps_fold_the_head_work_into_the_attention(monkeypatch):
+    """bfloat16, few chunks per token: a decode step launches no kernel for the head norm, the rotation and the cache
+    write (the decode attention does them on the way), a prompt portion does; the logits agree with the plain
+    implementation either way, and with the fold switched off the same steps give the same bits."""
+    from vllm_lite_b200.csrc import ops
+    from vllm_lite_b200.parts import attention_dispatch
+    which, dtype = "B", "bfloat16"
+    toks = H.tokens_for(which, 60, 77)
+    schedule = [([("r", toks[:40], [39])], [])] + [([("r", [toks[p]], [0])], []) for p in range(40, 60)]
+    schedule[-1] = (schedule[-1][0], ["r"])
+    calls = []
+    real = ops.qk_norm_rope_write
+    monkeypatch.setattr(ops, "qk_norm_rope_write", lambda qkv, *a, **k: (calls.append(qkv.shape[0]), real(qkv, *a, **k))[1])
+    runner = H.make_runner(which, dtype, num_pages=12)
+    rows = H.run_schedule(runner, schedule)
+    layers = H.TINY[which]["config"]["num_hidden_layers"]
+    assert calls == [40] * layers, calls                         # the prompt portion only (decode steps: none, eager or in a graph)
+    H.assert_rows_match(rows, which, {"r": toks}, dtype, "head work folded into the decode attention")
+    monkeypatch.setattr(attention_dispatch, "FOLD_MAX_CHUNKS", 0)
+    del calls[:]
+    plain_way = H.run_schedule(H.make_runner(which, dtype, num_pages=12), schedule)
+    assert len(calls) > layers                                   # now every step that is not replayed from a graph calls it
+    for key, row in rows.items():
+        assert torch.equal(row, plain_way[key]), key
