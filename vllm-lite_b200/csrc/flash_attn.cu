@@ -11,10 +11,13 @@
 //   (4 warps x 16 rows) and walks that request's keys in tiles of 64, K and V tiles double
 //   buffered in shared memory by cp.async.  The host passes the list of token tiles; a tile of
 //   more than 64 tokens is shared out among several blocks.
-// vl_flash_decode: a block owns one token, one KV head with all its query heads as rows, and one
-//   chunk of `chunk` key positions; its 4 warps take 16 keys each of every 64-key tile and their
-//   partial results are merged in warp order.  The per-chunk partials go to the same scratch
-//   layout as vl_decode_attention's and are merged by vl_decode_attention_merge.
+// vl_flash_decode: a block owns one token, one KV head with all its query heads, and one chunk of
+//   `chunk` key positions; its 4 warps take 16 keys each of every 64-key tile, each through a copy
+//   ring of its own, and their partial results are merged in warp order.  For groups of up to 8
+//   query heads the keys are the rows of the tensor-core tiles and the heads their columns.  The
+//   chunks of a token are merged by the blocks of a cluster (up to 16), by the block that arrives
+//   last, or (scratch layout of vl_decode_attention) by vl_decode_attention_merge.
+// vl_flash_decode_fused: the same, doing the step's head norm, rotation and cache write on the way.
 // Rows of shared-memory tiles are padded by 16 bytes, which makes every 8-row ldmatrix access
 // hit 8 different banks groups for any head size.
 #include "rope_head.cuh"
